@@ -1,0 +1,62 @@
+// Python bindings: thin wrappers that unpack torch tensors and call the C launchers.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "gemm/gemm_api.h"
+#include "ops_api.h"
+
+namespace {
+
+using torch::Tensor;
+using OptT = c10::optional<Tensor>;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+template <typename T>
+T* ptr_or_null(const OptT& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+}
+
+int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, int64_t M, int64_t N, int64_t K,
+             int64_t num_experts, int64_t m_fast, int64_t beta, int64_t n_half, const Tensor& A, int64_t lda,
+             int64_t a_inner, int64_t a_rows, const Tensor& B, int64_t ldb, int64_t b_expert_stride, int64_t b_inner,
+             int64_t b_rows, int64_t b_experts, const OptT& tile_expert, const OptT& num_m_tiles,
+             const OptT& seg_off, const Tensor& C, int64_t ldc, int64_t c_expert_stride, const OptT& aux0,
+             int64_t ld_aux0, const OptT& aux1, int64_t ld_aux1, const Tensor& status) {
+  check_cuda(A, "A");
+  check_cuda(B, "B");
+  check_cuda(C, "C");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "A and B must be bf16");
+  c10::cuda::CUDAGuard guard(A.device());
+  B200GemmDesc d;
+  d.mode = (int)mode; d.epi = (int)epi; d.bn = (int)bn; d.a_mn = (int)a_mn; d.b_mn = (int)b_mn;
+  d.M = (int)M; d.N = (int)N; d.K = (int)K;
+  d.num_experts = (int)num_experts; d.m_fast = (int)m_fast; d.beta = (int)beta; d.n_half = (int)n_half;
+  d.A = A.data_ptr(); d.lda = lda; d.a_inner = a_inner; d.a_rows = a_rows;
+  d.B = B.data_ptr(); d.ldb = ldb; d.b_expert_stride = b_expert_stride; d.b_inner = b_inner; d.b_rows = b_rows;
+  d.b_experts = (int)b_experts;
+  d.tile_expert = ptr_or_null<const int>(tile_expert);
+  d.num_m_tiles = ptr_or_null<const int>(num_m_tiles);
+  d.seg_off = ptr_or_null<const int>(seg_off);
+  d.C = C.data_ptr(); d.ldc = ldc; d.c_expert_stride = c_expert_stride;
+  d.aux0 = ptr_or_null<void>(aux0); d.ld_aux0 = ld_aux0;
+  d.aux1 = ptr_or_null<void>(aux1); d.ld_aux1 = ld_aux1;
+  d.status = reinterpret_cast<int*>(status.data_ptr());
+  const int rc = b200_gemm(&d, cur_stream());
+  TORCH_CHECK(rc == 0, "b200_gemm failed with host code ", rc);
+  return rc;
+}
+
+}  // namespace
+
+void bind_ops(pybind11::module_& m);  // bind_ops.cpp
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, "tcgen05 GEMM family (dense / grouped)");
+  bind_ops(m);
+}

@@ -1,0 +1,47 @@
+// C interface of the tcgen05 GEMM family (implemented in gemm_sm100.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Problem modes / epilogues: numeric values match b200::GemmMode / b200::GemmEpi.
+typedef struct B200GemmDesc {
+  int mode;  // 0 dense, 1 grouped by rows (padded expert segments), 2 grouped by contraction (per-expert dW)
+  int epi;   // 0 bf16, 1 fp32 (beta), 2 swiglu, 3 swiglu backward, 4 bf16 + softmax partials
+  int bn;    // tile width: 256, 128 or 64
+  int a_mn;  // A stored with the M index contiguous (rows = contraction index)
+  int b_mn;  // B stored with the N index contiguous (rows = contraction index)
+  int M, N, K;
+  int num_experts;
+  int m_fast;
+  int beta;
+  int n_half;
+  // A tensor (bf16): `a_inner` contiguous elements per row, `a_rows` rows, row pitch lda (elements)
+  const void* A;
+  long long lda;
+  long long a_inner, a_rows;
+  // B tensor (bf16): [b_experts][b_rows][b_inner], row pitch ldb, expert pitch b_expert_stride (elements)
+  const void* B;
+  long long ldb, b_expert_stride;
+  long long b_inner, b_rows;
+  int b_experts;
+  const int* tile_expert;
+  const int* num_m_tiles;
+  const int* seg_off;
+  void* C;
+  long long ldc, c_expert_stride;
+  void* aux0;
+  long long ld_aux0;
+  void* aux1;
+  long long ld_aux1;
+  int* status;  // device int, 0 = ok; a bounded wait that ran out writes its code here
+} B200GemmDesc;
+
+// Enqueue one GEMM on `stream`. Returns 0 on success, a negative code on a host-side error.
+int b200_gemm(const B200GemmDesc* desc, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,162 @@
+// Host side of the tcgen05 GEMM family: tensor-map construction and kernel dispatch.
+#include "gemm_api.h"
+#include "gemm_sm100.cuh"
+
+#include <cudaTypedefs.h>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+namespace b200 {
+
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  uint64_t d0, d1, d2, s1, s2;
+  uint32_t b0, b1;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    const uint64_t* p = reinterpret_cast<const uint64_t*>(&k);
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return static_cast<size_t>(h);
+  }
+};
+
+// bf16 tensor, up to 3 dims (inner first), 128B swizzle, zero fill out of bounds.
+static int make_map(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes,
+                    uint64_t s2_bytes, uint32_t b0, uint32_t b1) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.d0 = d0; key.d1 = d1; key.d2 = d2; key.s1 = s1_bytes; key.s2 = s2_bytes; key.b0 = b0; key.b1 = b1;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  auto fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (s1_bytes & 15u) != 0 || (s2_bytes & 15u) != 0) return -2;
+  const int rank = d2 > 0 ? 3 : 2;
+  cuuint64_t dims[3] = {d0, d1, d2 > 0 ? d2 : 1};
+  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -3;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int grid,
+                      cudaStream_t stream) {
+  auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES) !=
+        cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(ma, mb, args);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
+  const int bn = d->bn;
+  if (bn != 256 && bn != 128 && bn != 64) return -20;
+  GemmArgs a;
+  a.mode = d->mode;
+  a.M = d->M; a.N = d->N; a.K = d->K;
+  a.num_experts = d->num_experts;
+  a.m_fast = d->m_fast;
+  a.beta = d->beta;
+  a.n_half = d->n_half;
+  a.tile_expert = d->tile_expert;
+  a.num_m_tiles = d->num_m_tiles;
+  a.seg_off = d->seg_off;
+  a.C = d->C; a.ldc = d->ldc; a.c_expert_stride = d->c_expert_stride;
+  a.aux0 = d->aux0; a.ld_aux0 = d->ld_aux0;
+  a.aux1 = d->aux1; a.ld_aux1 = d->ld_aux1;
+  a.status = d->status;
+
+  CUtensorMap ma, mb;
+  int rc;
+  // A: 2-D. K-major: dims {K, rows}; MN-major: dims {M extent, contraction rows}.
+  rc = make_map(&ma, d->A, d->a_inner, d->a_rows, 0, static_cast<uint64_t>(d->lda) * 2, 0, 64, d->a_mn ? 64 : 128);
+  if (rc) return rc;
+  const uint32_t b_box_rows = d->b_mn ? 64u : (d->epi == EPI_SWIGLU ? bn / 2 : bn);
+  rc = make_map(&mb, d->B, d->b_inner, d->b_rows, d->b_experts > 0 ? d->b_experts : 1,
+                static_cast<uint64_t>(d->ldb) * 2,
+                static_cast<uint64_t>(d->b_expert_stride > 0 ? d->b_expert_stride : d->ldb * (long long)d->b_rows) * 2,
+                64, b_box_rows);
+  if (rc) return rc - 3;
+
+  const int bn_out = d->epi == EPI_SWIGLU ? bn / 2 : bn;
+  long long tiles = static_cast<long long>((d->M + GEMM_BM - 1) / GEMM_BM) * ((d->N + bn_out - 1) / bn_out);
+  if (d->mode == MODE_GROUPED_K) tiles *= d->num_experts;
+  int grid = sm_count();
+  if (tiles < grid) grid = static_cast<int>(tiles);
+  if (grid <= 0) return 0;
+
+#define B200_CASE(BN_, AMN_, BMN_, EPI_)                                                     \
+  if (bn == BN_ && d->a_mn == AMN_ && d->b_mn == BMN_ && d->epi == EPI_)                    \
+    return launch_one<BN_, AMN_ != 0, BMN_ != 0, EPI_>(ma, mb, a, grid, stream);
+  B200_CASE(256, 0, 0, EPI_BF16)
+  B200_CASE(128, 0, 0, EPI_BF16)
+  B200_CASE(64, 0, 0, EPI_BF16)
+  B200_CASE(256, 0, 1, EPI_BF16)
+  B200_CASE(128, 0, 1, EPI_BF16)
+  B200_CASE(256, 1, 1, EPI_F32)
+  B200_CASE(128, 1, 1, EPI_F32)
+  B200_CASE(256, 0, 0, EPI_F32)
+  B200_CASE(128, 0, 0, EPI_F32)
+  B200_CASE(64, 0, 0, EPI_F32)
+  B200_CASE(256, 0, 0, EPI_SWIGLU)
+  B200_CASE(128, 0, 0, EPI_SWIGLU)
+  B200_CASE(256, 0, 1, EPI_SWIGLU_BWD)
+  B200_CASE(128, 0, 1, EPI_SWIGLU_BWD)
+  B200_CASE(256, 0, 0, EPI_LSE)
+#undef B200_CASE
+  return -21;
+}

@@ -1,0 +1,189 @@
+"""Python front end of the tcgen05 GEMM family (`csrc/gemm`).
+
+Naming: `nt` = both operands K-major (`A[M,K] @ B[N,K]^T`), `nn` = B stored
+`[K,N]` (MN-major), `tn` = both operands stored with the contraction index as
+rows (`A[Kc,M]^T @ B[Kc,N]`).  No operand is ever transposed in memory; the
+kernel reads each layout directly through TMA and the tcgen05 descriptors.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+
+MODE_DENSE, MODE_GROUPED_M, MODE_GROUPED_K = 0, 1, 2
+EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD, EPI_LSE = 0, 1, 2, 3, 4
+
+_status_words: dict[int, torch.Tensor] = {}
+
+STATUS_NAMES = {1: "producer wait ran out", 2: "mma wait ran out", 3: "epilogue wait ran out",
+                4: "peer wait ran out", 5: "bad argument"}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels write when a bounded wait gives up."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status_words.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = t
+    return t
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronising check of the status word; raises if any kernel reported a timeout."""
+    devs = [device.index] if device is not None else list(_status_words)
+    for idx in devs:
+        t = _status_words.get(idx)
+        if t is None:
+            continue
+        v = int(t.item())
+        if v != 0:
+            t.zero_()
+            raise RuntimeError(f"moe_b200 kernel status {v}: {STATUS_NAMES.get(v, 'unknown')}")
+
+
+def _pick_bn(n: int) -> int:
+    if n <= 64:
+        return 64
+    if n <= 128:
+        return 128
+    return 256
+
+
+def _launch(*, mode, epi, bn, a_mn, b_mn, M, N, K, A, lda, a_inner, a_rows, B, ldb, b_expert_stride, b_inner,
+            b_rows, b_experts, C, ldc, num_experts=1, m_fast=1, beta=0, n_half=0, tile_expert=None,
+            num_m_tiles=None, seg_off=None, c_expert_stride=0, aux0=None, ld_aux0=0, aux1=None, ld_aux1=0):
+    ext = _ext.load()
+    ext.gemm(mode, epi, bn, a_mn, b_mn, M, N, K, num_experts, m_fast, beta, n_half, A, lda, a_inner, a_rows, B, ldb,
+             b_expert_stride, b_inner, b_rows, b_experts, tile_expert, num_m_tiles, seg_off, C, ldc,
+             c_expert_stride, aux0, ld_aux0, aux1, ld_aux1, status_word(A.device))
+
+
+def _check2d(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be a 2-D bf16 tensor with unit inner stride")
+    if t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        raise ValueError(f"{name}: row pitch must be a multiple of 8 elements and the base 16-byte aligned")
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=torch.bfloat16,
+            beta: int = 0, bn: int | None = None, m_fast: int = 1) -> torch.Tensor:
+    """`a[M,K] @ b[N,K]^T` -> `[M,N]` (bf16, or fp32 with optional accumulate)."""
+    _check2d(a, "a"); _check2d(b, "b")
+    M, K = a.shape
+    N = b.shape[0]
+    assert b.shape[1] == K
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    epi = EPI_BF16 if out.dtype == torch.bfloat16 else EPI_F32
+    _launch(mode=MODE_DENSE, epi=epi, bn=bn or _pick_bn(N), a_mn=0, b_mn=0, M=M, N=N, K=K, A=a, lda=a.stride(0),
+            a_inner=K, a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=K, b_rows=N, b_experts=1, C=out,
+            ldc=out.stride(0), beta=beta, m_fast=m_fast)
+    return out
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, bn: int | None = None,
+            m_fast: int = 0) -> torch.Tensor:
+    """`a[M,K] @ b[K,N]` -> bf16 `[M,N]`; `b` is read in place (N contiguous)."""
+    _check2d(a, "a"); _check2d(b, "b")
+    M, K = a.shape
+    N = b.shape[1]
+    assert b.shape[0] == K
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    bn = bn or (128 if N <= 128 else 256)
+    _launch(mode=MODE_DENSE, epi=EPI_BF16, bn=bn, a_mn=0, b_mn=1, M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K,
+            a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N, b_rows=K, b_experts=1, C=out,
+            ldc=out.stride(0), m_fast=m_fast)
+    return out
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, beta: int = 0, bn: int | None = None
+            ) -> torch.Tensor:
+    """`out[M,N] (+)= a[Kc,M]^T @ b[Kc,N]`, fp32 output (weight-gradient shape)."""
+    _check2d(a, "a"); _check2d(b, "b")
+    Kc, M = a.shape
+    N = b.shape[1]
+    assert b.shape[0] == Kc and out.dtype == torch.float32 and out.stride(1) == 1
+    bn = bn or (128 if N <= 128 else 256)
+    _launch(mode=MODE_DENSE, epi=EPI_F32, bn=bn, a_mn=1, b_mn=1, M=M, N=N, K=Kc, A=a, lda=a.stride(0), a_inner=M,
+            a_rows=Kc, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N, b_rows=Kc, b_experts=1, C=out,
+            ldc=out.stride(0), beta=beta, m_fast=0)
+    return out
+
+
+def gemm_nt_lse(a: torch.Tensor, b: torch.Tensor, logits: torch.Tensor | None = None
+                ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Vocabulary projection: bf16 logits plus per-(row, 256-column tile) `(max, sum exp)` partials."""
+    _check2d(a, "a"); _check2d(b, "b")
+    M, K = a.shape
+    N = b.shape[0]
+    if logits is None:
+        logits = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    n_tiles = (N + 255) // 256
+    part = torch.empty(M, n_tiles, 2, dtype=torch.float32, device=a.device)
+    _launch(mode=MODE_DENSE, epi=EPI_LSE, bn=256, a_mn=0, b_mn=0, M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K,
+            a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=K, b_rows=N, b_experts=1, C=logits,
+            ldc=logits.stride(0), aux0=part, m_fast=1)
+    return logits, part
+
+
+# ------------------------------------------------------------------ grouped (MoE)
+def grouped_up_swiglu(xs: torch.Tensor, w_gate_up: torch.Tensor, tile_expert: torch.Tensor,
+                      num_m_tiles: torch.Tensor, act: torch.Tensor, gu: torch.Tensor, bn: int = 256) -> None:
+    """`xs[R,H]` (expert-sorted, 128-row padded) x `w_gate_up[E,2I,H]` -> `act[R,I]`, pre-activations `gu[R,2I]`."""
+    R, H = xs.shape
+    E, I2, _ = w_gate_up.shape
+    I = I2 // 2
+    _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU, bn=bn, a_mn=0, b_mn=0, M=R, N=I, K=H, A=xs, lda=xs.stride(0),
+            a_inner=H, a_rows=R, B=w_gate_up, ldb=w_gate_up.stride(1), b_expert_stride=w_gate_up.stride(0),
+            b_inner=H, b_rows=I2, b_experts=E, C=act, ldc=act.stride(0), n_half=I, tile_expert=tile_expert,
+            num_m_tiles=num_m_tiles, aux0=gu, ld_aux0=gu.stride(0), m_fast=0)
+
+
+def grouped_nt(xs: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, num_m_tiles: torch.Tensor,
+               out: torch.Tensor, bn: int | None = None) -> None:
+    """`out[R,N] = xs[R,K] @ w[e(row)][N,K]^T` (down projection)."""
+    R, K = xs.shape
+    E, N, _ = w.shape
+    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=0, M=R, N=N, K=K,
+            A=xs, lda=xs.stride(0), a_inner=K, a_rows=R, B=w, ldb=w.stride(1), b_expert_stride=w.stride(0),
+            b_inner=K, b_rows=N, b_experts=E, C=out, ldc=out.stride(0), tile_expert=tile_expert,
+            num_m_tiles=num_m_tiles, m_fast=0)
+
+
+def grouped_nn(xs: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, num_m_tiles: torch.Tensor,
+               out: torch.Tensor, bn: int | None = None) -> None:
+    """`out[R,N] = xs[R,K] @ w[e(row)][K,N]` (input gradients; weights read in place)."""
+    R, K = xs.shape
+    E, _, N = w.shape
+    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=1, M=R, N=N, K=K,
+            A=xs, lda=xs.stride(0), a_inner=K, a_rows=R, B=w, ldb=w.stride(1), b_expert_stride=w.stride(0),
+            b_inner=N, b_rows=K, b_experts=E, C=out, ldc=out.stride(0), tile_expert=tile_expert,
+            num_m_tiles=num_m_tiles, m_fast=0)
+
+
+def grouped_nn_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, tile_expert: torch.Tensor,
+                          num_m_tiles: torch.Tensor, gu: torch.Tensor, dgu: torch.Tensor,
+                          bn: int | None = None) -> None:
+    """`d(act) = dy[R,H] @ w_down[e][H,I]`, fused with the SwiGLU backward: writes `dgu[R,2I]`."""
+    R, H = dy.shape
+    E, _, I = w_down.shape
+    _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU_BWD, bn=bn or (128 if I <= 128 else 256), a_mn=0, b_mn=1, M=R, N=I,
+            K=H, A=dy, lda=dy.stride(0), a_inner=H, a_rows=R, B=w_down, ldb=w_down.stride(1),
+            b_expert_stride=w_down.stride(0), b_inner=I, b_rows=H, b_experts=E, C=dgu, ldc=dgu.stride(0),
+            n_half=I, tile_expert=tile_expert, num_m_tiles=num_m_tiles, aux0=gu, ld_aux0=gu.stride(0), aux1=dgu,
+            ld_aux1=dgu.stride(0), m_fast=0)
+
+
+def grouped_tn(a: torch.Tensor, b: torch.Tensor, seg_off: torch.Tensor, out: torch.Tensor, beta: int = 0,
+               bn: int | None = None) -> None:
+    """Per-expert weight gradient: `out[e][M,N] (+)= a[seg_e, M]^T @ b[seg_e, N]`, fp32."""
+    R, M = a.shape
+    N = b.shape[1]
+    E = out.shape[0]
+    _launch(mode=MODE_GROUPED_K, epi=EPI_F32, bn=bn or (128 if N <= 128 else 256), a_mn=1, b_mn=1, M=M, N=N, K=0,
+            A=a, lda=a.stride(0), a_inner=M, a_rows=R, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N, b_rows=R,
+            b_experts=1, C=out, ldc=out.stride(1), c_expert_stride=out.stride(0), num_experts=E, seg_off=seg_off,
+            beta=beta, m_fast=0)
