@@ -1,8 +1,232 @@
-// Bindings of the non-GEMM kernels.
+// Bindings of the non-GEMM kernels. Shapes and dtypes are validated here; the launchers only
+// see raw pointers.
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
 #include "ops_api.h"
 
-void bind_ops(pybind11::module_& m) { (void)m; }
+namespace {
+
+using torch::Tensor;
+using OptT = c10::optional<Tensor>;
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+template <typename T>
+T* optp(const OptT& t) {
+  return t.has_value() && t->defined() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+void need(bool ok, const char* what) { TORCH_CHECK(ok, "moe_b200: ", what); }
+void bf16c(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), n, ": contiguous CUDA bf16 expected");
+}
+void f32c(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), n, ": contiguous CUDA fp32 expected");
+}
+void i32c(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), n, ": contiguous CUDA int32 expected");
+}
+void rc_ok(int rc, const char* fn) { TORCH_CHECK(rc == 0, fn, " rejected its arguments (code ", rc, ")"); }
+
+// ------------------------------------------------------------------ rmsnorm
+void rmsnorm_fwd(const Tensor& x, const OptT& res, const Tensor& w, const OptT& h_out, Tensor& y, const OptT& rstd,
+                 double eps) {
+  bf16c(x, "x"); f32c(w, "w"); bf16c(y, "y");
+  c10::cuda::CUDAGuard g(x.device());
+  const int H = (int)x.size(-1);
+  const int T = (int)(x.numel() / H);
+  need(w.numel() == H, "rmsnorm weight size");
+  rc_ok(b200_rmsnorm_fwd(x.data_ptr(), optp<const void>(res), w.data_ptr<float>(), optp<void>(h_out), y.data_ptr(),
+                         optp<float>(rstd), T, H, (float)eps, stream()), "rmsnorm_fwd");
+}
+int64_t rmsnorm_bwd_blocks(int64_t T) { return b200_rmsnorm_bwd_blocks((int)T); }
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& rstd, const Tensor& w, const OptT& dres, Tensor& dx,
+                 Tensor& dw_part, Tensor& dw_out, bool accumulate) {
+  bf16c(dy, "dy"); bf16c(x, "x"); f32c(rstd, "rstd"); f32c(w, "w"); bf16c(dx, "dx"); f32c(dw_part, "dw_part");
+  f32c(dw_out, "dw_out");
+  c10::cuda::CUDAGuard g(x.device());
+  const int H = (int)x.size(-1);
+  const int T = (int)(x.numel() / H);
+  need(dw_part.numel() >= (int64_t)b200_rmsnorm_bwd_blocks(T) * H, "rmsnorm dw scratch too small");
+  rc_ok(b200_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), rstd.data_ptr<float>(), w.data_ptr<float>(),
+                         optp<const void>(dres), dx.data_ptr(), dw_part.data_ptr<float>(), dw_out.data_ptr<float>(),
+                         accumulate ? 1 : 0, T, H, stream()), "rmsnorm_bwd");
+}
+
+// ------------------------------------------------------------- qknorm + rope
+int64_t qknorm_rope_blocks(int64_t items) { return b200_qknorm_rope_blocks(items); }
+void qknorm_rope_fwd(const Tensor& qkv, const Tensor& qw, const Tensor& kw, const Tensor& cs, Tensor& q, Tensor& k,
+                     Tensor& v, Tensor& rstd, int64_t S, int64_t nh, int64_t nkv, int64_t hd, double eps) {
+  bf16c(qkv, "qkv"); f32c(qw, "qw"); f32c(kw, "kw"); f32c(cs, "cs"); bf16c(q, "q"); bf16c(k, "k"); bf16c(v, "v"); f32c(rstd, "rstd");
+  c10::cuda::CUDAGuard g(qkv.device());
+  const int ld = (int)qkv.size(-1);
+  const int T = (int)(qkv.numel() / ld);
+  need(ld == (nh + 2 * nkv) * hd, "qkv width");
+  need(cs.numel() >= S * hd, "rope table too small");
+  rc_ok(b200_qknorm_rope_fwd(qkv.data_ptr(), ld, qw.data_ptr<float>(), kw.data_ptr<float>(), cs.data_ptr<float>(),
+                             q.data_ptr(), k.data_ptr(), v.data_ptr(), rstd.data_ptr<float>(), T, (int)S, (int)nh, (int)nkv,
+                             (int)hd, (float)eps, stream()), "qknorm_rope_fwd");
+}
+void qknorm_rope_bwd(const Tensor& dq, const Tensor& dk, const Tensor& dv, const Tensor& qkv, const Tensor& rstd,
+                     const Tensor& qw, const Tensor& kw, const Tensor& cs, Tensor& dqkv, Tensor& dw_part, Tensor& dqw,
+                     Tensor& dkw, bool accumulate, int64_t S, int64_t nh, int64_t nkv, int64_t hd) {
+  bf16c(dq, "dq"); bf16c(dk, "dk"); bf16c(dv, "dv"); bf16c(qkv, "qkv"); bf16c(dqkv, "dqkv");
+  f32c(dw_part, "dw_part"); f32c(dqw, "dqw"); f32c(dkw, "dkw");
+  c10::cuda::CUDAGuard g(qkv.device());
+  const int ld = (int)qkv.size(-1);
+  const int T = (int)(qkv.numel() / ld);
+  need(dw_part.numel() >= b200_qknorm_rope_blocks((int64_t)T * (nh + 2 * nkv)) * 2 * hd, "qk dw scratch too small");
+  rc_ok(b200_qknorm_rope_bwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), qkv.data_ptr(), ld, rstd.data_ptr<float>(),
+                             qw.data_ptr<float>(), kw.data_ptr<float>(), cs.data_ptr<float>(), dqkv.data_ptr(),
+                             dw_part.data_ptr<float>(), dqw.data_ptr<float>(), dkw.data_ptr<float>(),
+                             accumulate ? 1 : 0, T, (int)S, (int)nh, (int)nkv, (int)hd, stream()), "qknorm_rope_bwd");
+}
+
+// ------------------------------------------------------------------- router
+void router_fwd(const Tensor& logits, const OptT& bias, Tensor& scores, Tensor& topk_w, Tensor& topk_idx, int64_t K,
+                int64_t mode, bool norm, double scale, int64_t num_groups, int64_t group_topk) {
+  f32c(logits, "logits"); f32c(scores, "scores"); f32c(topk_w, "topk_w"); i32c(topk_idx, "topk_idx");
+  c10::cuda::CUDAGuard g(logits.device());
+  const int T = (int)logits.size(0), E = (int)logits.size(1);
+  rc_ok(b200_router_fwd(logits.data_ptr<float>(), optp<const float>(bias), scores.data_ptr<float>(),
+                        topk_w.data_ptr<float>(), topk_idx.data_ptr<int>(), T, E, (int)K, (int)mode, norm ? 1 : 0,
+                        (float)scale, (int)num_groups, (int)group_topk, stream()), "router_fwd");
+}
+void router_bwd(const OptT& dscores, const Tensor& dtopk_w, const Tensor& scores, const Tensor& topk_idx,
+                Tensor& dlogits, int64_t K, int64_t mode, bool norm, double scale) {
+  f32c(dtopk_w, "dtopk_w"); f32c(scores, "scores"); i32c(topk_idx, "topk_idx"); bf16c(dlogits, "dlogits");
+  c10::cuda::CUDAGuard g(scores.device());
+  const int T = (int)scores.size(0), E = (int)scores.size(1);
+  rc_ok(b200_router_bwd(optp<const float>(dscores), dtopk_w.data_ptr<float>(), scores.data_ptr<float>(),
+                        topk_idx.data_ptr<int>(), dlogits.data_ptr(), T, E, (int)K, (int)mode, norm ? 1 : 0,
+                        (float)scale, stream()), "router_bwd");
+}
+
+// ----------------------------------------------------------------- dispatch
+int64_t moe_plan_blocks(int64_t n) { return b200_moe_plan_blocks((int)n); }
+void moe_plan(const Tensor& idx, int64_t E, Tensor& scratch, Tensor& counts, Tensor& seg_off, Tensor& tile_expert,
+              Tensor& num_m_tiles, Tensor& pos, Tensor& row_slot) {
+  i32c(idx, "idx"); i32c(scratch, "scratch"); i32c(counts, "counts"); i32c(seg_off, "seg_off");
+  i32c(tile_expert, "tile_expert"); i32c(num_m_tiles, "num_m_tiles"); i32c(pos, "pos"); i32c(row_slot, "row_slot");
+  c10::cuda::CUDAGuard g(idx.device());
+  const int n = (int)idx.numel();
+  const int cap = (int)row_slot.numel();
+  need(scratch.numel() >= (int64_t)b200_moe_plan_blocks(n) * E, "plan scratch too small");
+  need(seg_off.numel() >= E + 1 && counts.numel() >= E && tile_expert.numel() >= cap / 128 && pos.numel() >= n,
+       "plan output sizes");
+  rc_ok(b200_moe_plan(idx.data_ptr<int>(), n, (int)E, scratch.data_ptr<int>(), counts.data_ptr<int>(),
+                      seg_off.data_ptr<int>(), tile_expert.data_ptr<int>(), num_m_tiles.data_ptr<int>(),
+                      pos.data_ptr<int>(), row_slot.data_ptr<int>(), cap, stream()), "moe_plan");
+}
+void moe_gather(const Tensor& x, const Tensor& row_slot, const Tensor& seg_off, int64_t E, int64_t K, Tensor& xs) {
+  bf16c(x, "x"); bf16c(xs, "xs"); i32c(row_slot, "row_slot"); i32c(seg_off, "seg_off");
+  c10::cuda::CUDAGuard g(x.device());
+  rc_ok(b200_moe_gather(x.data_ptr(), row_slot.data_ptr<int>(), seg_off.data_ptr<int>(), (int)E, (int)K,
+                        (int)x.size(1), xs.data_ptr(), (int)xs.size(0), stream()), "moe_gather");
+}
+void moe_combine(const Tensor& ys, const Tensor& pos, const OptT& w, const OptT& res, Tensor& out, int64_t K) {
+  bf16c(ys, "ys"); i32c(pos, "pos"); bf16c(out, "out");
+  c10::cuda::CUDAGuard g(ys.device());
+  rc_ok(b200_moe_combine(ys.data_ptr(), pos.data_ptr<int>(), optp<const float>(w), optp<const void>(res),
+                         (int)out.size(0), (int)K, (int)out.size(1), out.data_ptr(), stream()), "moe_combine");
+}
+void moe_combine_bwd(const Tensor& dout, const Tensor& ys, const Tensor& row_slot, const Tensor& seg_off,
+                     const Tensor& w, int64_t E, int64_t K, Tensor& dys, Tensor& dw) {
+  bf16c(dout, "dout"); bf16c(ys, "ys"); bf16c(dys, "dys"); f32c(w, "w"); f32c(dw, "dw");
+  c10::cuda::CUDAGuard g(ys.device());
+  rc_ok(b200_moe_combine_bwd(dout.data_ptr(), ys.data_ptr(), row_slot.data_ptr<int>(), seg_off.data_ptr<int>(),
+                             w.data_ptr<float>(), (int)E, (int)K, (int)dout.size(1), dys.data_ptr(),
+                             dw.data_ptr<float>(), (int)dys.size(0), stream()), "moe_combine_bwd");
+}
+
+// ---------------------------------------------------------------------- lce
+void lse_loss(const Tensor& part, const Tensor& logits, const Tensor& labels, int64_t ignore_index, Tensor& lse,
+              Tensor& loss_acc) {
+  f32c(part, "part"); f32c(lse, "lse"); f32c(loss_acc, "loss_acc");
+  need(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.is_contiguous(), "labels must be int64");
+  c10::cuda::CUDAGuard g(logits.device());
+  const int T = (int)logits.size(0), V = (int)logits.size(1);
+  rc_ok(b200_lse_loss(part.data_ptr<float>(), (int)part.size(1), logits.data_ptr(), logits.stride(0),
+                      reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), (int)ignore_index, T, V,
+                      lse.data_ptr<float>(), loss_acc.data_ptr<float>(), stream()), "lse_loss");
+}
+void dlogits_(Tensor& logits, const Tensor& lse, const Tensor& labels, int64_t ignore_index, const Tensor& loss_acc,
+              double upstream) {
+  c10::cuda::CUDAGuard g(logits.device());
+  const int T = (int)logits.size(0), V = (int)logits.size(1);
+  rc_ok(b200_dlogits(logits.data_ptr(), logits.stride(0), lse.data_ptr<float>(),
+                     reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), (int)ignore_index, T, V,
+                     loss_acc.data_ptr<float>(), (float)upstream, stream()), "dlogits");
+}
+void embed_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
+  bf16c(table, "table"); bf16c(out, "out");
+  need(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids must be int64");
+  c10::cuda::CUDAGuard g(table.device());
+  rc_ok(b200_embed_fwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), table.data_ptr(),
+                       (int)ids.numel(), (int)table.size(1), (int)table.size(0), out.data_ptr(), stream()),
+        "embed_fwd");
+}
+void embed_bwd(const Tensor& ids, const Tensor& dout, Tensor& grad) {
+  bf16c(dout, "dout"); f32c(grad, "grad");
+  c10::cuda::CUDAGuard g(grad.device());
+  rc_ok(b200_embed_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), dout.data_ptr(),
+                       (int)ids.numel(), (int)grad.size(1), (int)grad.size(0), grad.data_ptr<float>(), stream()),
+        "embed_bwd");
+}
+
+// -------------------------------------------------------------------- optim
+int64_t sumsq_blocks(int64_t n) { return b200_sumsq_blocks(n); }
+void sumsq(const Tensor& g, Tensor& scratch, Tensor& out, bool accumulate) {
+  f32c(g, "g"); f32c(scratch, "scratch"); f32c(out, "out");
+  c10::cuda::CUDAGuard gd(g.device());
+  need(scratch.numel() >= b200_sumsq_blocks(g.numel()), "sumsq scratch too small");
+  rc_ok(b200_sumsq(g.data_ptr<float>(), g.numel(), scratch.data_ptr<float>(), out.data_ptr<float>(),
+                   accumulate ? 1 : 0, stream()), "sumsq");
+}
+void clip_coef(const Tensor& ss, double max_norm, Tensor& coef) {
+  f32c(ss, "sumsq"); f32c(coef, "coef");
+  c10::cuda::CUDAGuard gd(ss.device());
+  rc_ok(b200_clip_coef(ss.data_ptr<float>(), (float)max_norm, coef.data_ptr<float>(), stream()), "clip_coef");
+}
+void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptT& p16, double lr, double beta1, double beta2,
+           double eps, double wd, int64_t step, const OptT& grad_coef) {
+  f32c(p, "p"); f32c(g, "g"); f32c(m, "m"); f32c(v, "v");
+  c10::cuda::CUDAGuard gd(p.device());
+  need(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw sizes");
+  rc_ok(b200_adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                   optp<void>(p16), p.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
+                   optp<const float>(grad_coef), stream()), "adamw");
+}
+void cast_bf16(const Tensor& src, Tensor& dst) {
+  f32c(src, "src"); bf16c(dst, "dst");
+  c10::cuda::CUDAGuard gd(src.device());
+  rc_ok(b200_cast_bf16(src.data_ptr<float>(), dst.data_ptr(), src.numel(), stream()), "cast_bf16");
+}
+
+}  // namespace
+
+void bind_ops(pybind11::module_& m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd_blocks", &rmsnorm_bwd_blocks);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("qknorm_rope_blocks", &qknorm_rope_blocks);
+  m.def("qknorm_rope_fwd", &qknorm_rope_fwd);
+  m.def("qknorm_rope_bwd", &qknorm_rope_bwd);
+  m.def("router_fwd", &router_fwd);
+  m.def("router_bwd", &router_bwd);
+  m.def("moe_plan_blocks", &moe_plan_blocks);
+  m.def("moe_plan", &moe_plan);
+  m.def("moe_gather", &moe_gather);
+  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine_bwd", &moe_combine_bwd);
+  m.def("lse_loss", &lse_loss);
+  m.def("dlogits_", &dlogits_);
+  m.def("embed_fwd", &embed_fwd);
+  m.def("embed_bwd", &embed_bwd);
+  m.def("sumsq_blocks", &sumsq_blocks);
+  m.def("sumsq", &sumsq);
+  m.def("clip_coef", &clip_coef);
+  m.def("adamw", &adamw);
+  m.def("cast_bf16", &cast_bf16);
+}

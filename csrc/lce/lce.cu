@@ -1,0 +1,167 @@
+// Cross-entropy pieces around the vocabulary GEMM.
+//   1. lse_loss: combine the per-(row, n-tile) (max, sum exp) partials written by the GEMM epilogue into
+//      the row log-sum-exp, pick the label logit, and reduce the summed loss / valid-token count.
+//   2. dlogits: turn the stored bf16 logits into d(loss)/d(logits) in place:
+//      (softmax - onehot) * upstream / n_valid, rows with an ignored label become zero.
+#include "../common/ptx.cuh"
+#include "../ops_api.h"
+
+namespace b200 {
+
+// One warp per row.  loss_acc[0] += sum of row losses, loss_acc[1] += number of valid rows.
+__global__ void lse_loss_kernel(const float2* __restrict__ part, int n_tiles, const __nv_bfloat16* __restrict__ logits,
+                                long long ld, const long long* __restrict__ labels, int ignore_index, int T, int V,
+                                float* __restrict__ lse_out, float* __restrict__ loss_acc) {
+  __shared__ float s_loss[8], s_cnt[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  float loss = 0.f, cnt = 0.f;
+  if (row < T) {
+    const float2* pr = part + static_cast<size_t>(row) * n_tiles;
+    float mx = -INFINITY;
+    for (int i = lane; i < n_tiles; i += 32) mx = fmaxf(mx, pr[i].x);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = lane; i < n_tiles; i += 32) {
+      const float2 p = pr[i];
+      sum += p.y * __expf(p.x - mx);
+    }
+    sum = warp_sum(sum);
+    const float lse = mx + __logf(sum);
+    if (lane == 0) {
+      lse_out[row] = lse;
+      const long long lab = labels[row];
+      if (lab != ignore_index && lab >= 0 && lab < V) {
+        loss = lse - __bfloat162float(logits[static_cast<size_t>(row) * ld + lab]);
+        cnt = 1.f;
+      }
+    }
+  }
+  if (lane == 0) {
+    s_loss[warp] = loss;
+    s_cnt[warp] = cnt;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a += s_loss[i];
+      b += s_cnt[i];
+    }
+    if (b > 0.f) {
+      atomicAdd(&loss_acc[0], a);
+      atomicAdd(&loss_acc[1], b);
+    }
+  }
+}
+
+// In place over [T, V] bf16; 8 elements per thread step.  V must be a multiple of 8.
+__global__ void dlogits_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const float* __restrict__ lse,
+                               const long long* __restrict__ labels, int ignore_index, int T, int V,
+                               const float* __restrict__ loss_acc, float upstream) {
+  const int vch = V >> 3;
+  const long long total = static_cast<long long>(T) * vch;
+  const float nvalid = loss_acc[1];
+  const float sc = nvalid > 0.f ? upstream / nvalid : 0.f;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / vch);
+    const int c = static_cast<int>(i - static_cast<long long>(row) * vch);
+    uint4* p = reinterpret_cast<uint4*>(logits + static_cast<size_t>(row) * ld + c * 8);
+    const long long lab = labels[row];
+    if (lab == ignore_index || lab < 0 || lab >= V) {
+      *p = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const float l = lse[row];
+    const uint4 q = *p;
+    const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[4];
+    const int col0 = c * 8;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]);
+      float g0 = __expf(f.x - l), g1 = __expf(f.y - l);
+      if (col0 + 2 * j == lab) g0 -= 1.f;
+      if (col0 + 2 * j + 1 == lab) g1 -= 1.f;
+      o[j] = pack_bf16x2(g0 * sc, g1 * sc);
+    }
+    *p = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table, int T,
+                                 int H, int V, __nv_bfloat16* __restrict__ out) {
+  const int nch = H >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int t = blockIdx.x * wpb + warp; t < T; t += gridDim.x * wpb) {
+    long long id = ids[t];
+    if (id < 0 || id >= V) id = 0;
+    const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * H);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+    for (int c = lane; c < nch; c += 32) dst[c] = src[c];
+  }
+}
+
+// grad[ids[t]] += dout[t]  (fp32 accumulation buffer; float atomics, order not fixed)
+__global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout, int T,
+                                 int H, int V, float* __restrict__ grad) {
+  const int nch = H >> 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int t = blockIdx.x * wpb + warp; t < T; t += gridDim.x * wpb) {
+    const long long id = ids[t];
+    if (id < 0 || id >= V) continue;
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(dout + static_cast<size_t>(t) * H);
+    float* dst = grad + static_cast<size_t>(id) * H;
+    for (int c = lane; c < nch; c += 32) {
+      const float2 f = unpack_bf16x2(src[c]);
+      atomicAdd(dst + 2 * c, f.x);
+      atomicAdd(dst + 2 * c + 1, f.y);
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_lse_loss(const float* part, int n_tiles, const void* logits, long long ld, const long long* labels,
+                             int ignore_index, int T, int V, float* lse, float* loss_acc, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  lse_loss_kernel<<<(T + 7) / 8, 256, 0, stream>>>(reinterpret_cast<const float2*>(part), n_tiles,
+                                                   reinterpret_cast<const __nv_bfloat16*>(logits), ld, labels,
+                                                   ignore_index, T, V, lse, loss_acc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_dlogits(void* logits, long long ld, const float* lse, const long long* labels, int ignore_index,
+                            int T, int V, const float* loss_acc, float upstream, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (V % 8 != 0) return -1;
+  dlogits_kernel<<<148 * 16, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(logits), ld, lse, labels,
+                                               ignore_index, T, V, loss_acc, upstream);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_embed_fwd(const long long* ids, const void* table, int T, int H, int V, void* out,
+                              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return -1;
+  int grid = (T + 7) / 8;
+  if (grid > 1184) grid = 1184;
+  embed_fwd_kernel<<<grid, 256, 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(table), T, H, V,
+                                             reinterpret_cast<__nv_bfloat16*>(out));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, float* grad,
+                              cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 2 != 0) return -1;
+  int grid = (T + 7) / 8;
+  if (grid > 1184) grid = 1184;
+  embed_bwd_kernel<<<grid, 256, 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(dout), T, H, V, grad);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

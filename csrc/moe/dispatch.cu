@@ -1,0 +1,254 @@
+// Token dispatch plan for the grouped expert GEMMs, and the row movers around them.
+//
+// The (token, slot) -> expert assignment is turned into an expert-sorted row layout in which every
+// expert's segment is padded to a multiple of 128 rows, so that a 128-row GEMM tile never straddles
+// two experts.  The sort is a deterministic counting sort (stable in token order): block histograms,
+// a scan, and a ranked scatter - no atomics on the ordering path, no host synchronisation.
+#include "../common/ptx.cuh"
+#include "../ops_api.h"
+
+namespace b200 {
+
+constexpr int PLAN_CHUNK = 512;  // assignments per block
+
+// block_hist[b][e] = number of assignments to expert e among entries [b*CHUNK, (b+1)*CHUNK)
+__global__ void plan_hist_kernel(const int* __restrict__ idx, int n, int E, int* __restrict__ block_hist) {
+  extern __shared__ int sh[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * PLAN_CHUNK;
+  for (int i = threadIdx.x; i < PLAN_CHUNK; i += blockDim.x) {
+    const int g = base + i;
+    if (g < n) {
+      const int e = idx[g];
+      if (e >= 0 && e < E) atomicAdd(&sh[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) block_hist[static_cast<size_t>(blockIdx.x) * E + e] = sh[e];
+}
+
+// Single block: per-expert exclusive scan over blocks (in place), counts, padded segment offsets,
+// tile -> expert map and live tile count.
+__global__ void plan_scan_kernel(int* __restrict__ block_hist, int nblocks, int E, int* __restrict__ counts,
+                                 int* __restrict__ seg_off, int* __restrict__ tile_expert, int max_tiles,
+                                 int* __restrict__ num_m_tiles) {
+  extern __shared__ int sh[];  // [E] padded sizes -> offsets
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int b = 0; b < nblocks; ++b) {
+      const size_t o = static_cast<size_t>(b) * E + e;
+      const int c = block_hist[o];
+      block_hist[o] = run;
+      run += c;
+    }
+    counts[e] = run;
+    sh[e] = (run + 127) / 128 * 128;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int p = sh[e];
+      seg_off[e] = run;
+      sh[e] = run;
+      run += p;
+    }
+    seg_off[E] = run;
+    int nt = run / 128;
+    if (nt > max_tiles) nt = max_tiles;
+    *num_m_tiles = nt;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int t0 = seg_off[e] / 128, t1 = seg_off[e + 1] / 128;
+    for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = e;
+  }
+}
+
+// One warp per chunk walks its entries in order; rank within (chunk, expert) from match/popc.
+__global__ void plan_scatter_kernel(const int* __restrict__ idx, int n, int E, const int* __restrict__ block_off,
+                                    const int* __restrict__ seg_off, int* __restrict__ pos,
+                                    int* __restrict__ row_slot, int capacity) {
+  extern __shared__ int cnt[];  // [E] running count inside this chunk
+  const int lane = threadIdx.x;
+  for (int e = lane; e < E; e += 32) cnt[e] = 0;
+  __syncwarp();
+  const int base = blockIdx.x * PLAN_CHUNK;
+  for (int i = 0; i < PLAN_CHUNK; i += 32) {
+    const int g = base + i + lane;
+    int e = -1;
+    if (g < n) {
+      e = idx[g];
+      if (e < 0 || e >= E) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int start = 0;
+    if (e >= 0) start = cnt[e];
+    __syncwarp();
+    if (e >= 0 && rank == 0) cnt[e] = start + __popc(peers);
+    __syncwarp();
+    if (e >= 0) {
+      const int p = seg_off[e] + block_off[static_cast<size_t>(blockIdx.x) * E + e] + start + rank;
+      if (p < capacity) {
+        pos[g] = p;
+        row_slot[p] = g;
+      } else {
+        pos[g] = -1;
+      }
+    } else if (g < n) {
+      pos[g] = -1;
+    }
+  }
+}
+
+// xs[r] = x[row_slot[r] / K] for live rows, 0 for padding rows; rows past the live region untouched.
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_slot,
+                                  const int* __restrict__ seg_off, int E, int K, int H,
+                                  __nv_bfloat16* __restrict__ xs, int capacity) {
+  int live = seg_off[E];
+  if (live > capacity) live = capacity;
+  const int nch = H >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int r = blockIdx.x * wpb + warp; r < live; r += gridDim.x * wpb) {
+    const int s = row_slot[r];
+    uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(r) * H);
+    if (s >= 0) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(s / K) * H);
+      for (int c = lane; c < nch; c += 32) dst[c] = src[c];
+    } else {
+      for (int c = lane; c < nch; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+// out[t] = sum_k w[t,k] * ys[pos[t,k]] (+ res[t]);  w == null -> plain sum.  Fixed k order.
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos,
+                                   const float* __restrict__ w, const __nv_bfloat16* __restrict__ res, int T, int K,
+                                   int H, __nv_bfloat16* __restrict__ out) {
+  const int nch = H >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int t = blockIdx.x * wpb + warp; t < T; t += gridDim.x * wpb) {
+    for (int c = lane; c < nch; c += 32) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      if (res) {
+        const uint4 q = *reinterpret_cast<const uint4*>(res + static_cast<size_t>(t) * H + c * 8);
+        const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(u[j]);
+          acc[2 * j] = f.x;
+          acc[2 * j + 1] = f.y;
+        }
+      }
+      for (int k = 0; k < K; ++k) {
+        const int p = pos[static_cast<size_t>(t) * K + k];
+        if (p < 0) continue;
+        const float wk = w ? w[static_cast<size_t>(t) * K + k] : 1.f;
+        const uint4 q = *reinterpret_cast<const uint4*>(ys + static_cast<size_t>(p) * H + c * 8);
+        const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(u[j]);
+          acc[2 * j] += wk * f.x;
+          acc[2 * j + 1] += wk * f.y;
+        }
+      }
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + c * 8) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                     pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+}
+
+// Backward of the weighted combine, per sorted row r (slot s = row_slot[r], token t = s / K):
+//   dys[r] = w[s] * dout[t]        dw[s] = <dout[t], ys[r]>        padding rows -> 0
+__global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ ys,
+                                       const int* __restrict__ row_slot, const int* __restrict__ seg_off,
+                                       const float* __restrict__ w, int E, int K, int H,
+                                       __nv_bfloat16* __restrict__ dys, float* __restrict__ dw, int capacity) {
+  int live = seg_off[E];
+  if (live > capacity) live = capacity;
+  const int nch = H >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int r = blockIdx.x * wpb + warp; r < live; r += gridDim.x * wpb) {
+    const int s = row_slot[r];
+    uint4* dst = reinterpret_cast<uint4*>(dys + static_cast<size_t>(r) * H);
+    if (s < 0) {
+      for (int c = lane; c < nch; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const float wk = w[s];
+    const uint4* g = reinterpret_cast<const uint4*>(dout + static_cast<size_t>(s / K) * H);
+    const uint4* y = reinterpret_cast<const uint4*>(ys + static_cast<size_t>(r) * H);
+    float dot = 0.f;
+    for (int c = lane; c < nch; c += 32) {
+      const uint4 gq = g[c], yq = y[c];
+      const uint32_t gu[4] = {gq.x, gq.y, gq.z, gq.w}, yu[4] = {yq.x, yq.y, yq.z, yq.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 gf = unpack_bf16x2(gu[j]), yf = unpack_bf16x2(yu[j]);
+        dot += gf.x * yf.x + gf.y * yf.y;
+        o[j] = pack_bf16x2(wk * gf.x, wk * gf.y);
+      }
+      dst[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) dw[s] = dot;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_moe_plan_blocks(int n) { return (n + PLAN_CHUNK - 1) / PLAN_CHUNK; }
+
+// scratch: int32[plan_blocks(n) * E].  row_slot must hold `capacity` ints; it is reset to -1 here.
+extern "C" int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* seg_off, int* tile_expert,
+                             int* num_m_tiles, int* pos, int* row_slot, int capacity, cudaStream_t stream) {
+  if (n <= 0 || E <= 0 || capacity % 128 != 0) return -1;
+  if (static_cast<size_t>(E) * sizeof(int) > 48 * 1024) return -1;
+  const int nb = b200_moe_plan_blocks(n);
+  const size_t sm = static_cast<size_t>(E) * sizeof(int);
+  cudaMemsetAsync(row_slot, 0xff, static_cast<size_t>(capacity) * sizeof(int), stream);
+  plan_hist_kernel<<<nb, 256, sm, stream>>>(idx, n, E, scratch);
+  plan_scan_kernel<<<1, 1024, sm, stream>>>(scratch, nb, E, counts, seg_off, tile_expert, capacity / 128,
+                                            num_m_tiles);
+  plan_scatter_kernel<<<nb, 32, sm, stream>>>(idx, n, E, scratch, seg_off, pos, row_slot, capacity);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_moe_gather(const void* x, const int* row_slot, const int* seg_off, int E, int K, int H, void* xs,
+                               int capacity, cudaStream_t stream) {
+  if (H % 8 != 0) return -1;
+  moe_gather_kernel<<<1184, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), row_slot, seg_off, E, K, H,
+                                              reinterpret_cast<__nv_bfloat16*>(xs), capacity);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_moe_combine(const void* ys, const int* pos, const float* w, const void* res, int T, int K, int H,
+                                void* out, cudaStream_t stream) {
+  if (H % 8 != 0) return -1;
+  if (T <= 0) return 0;
+  int grid = (T + 7) / 8;
+  if (grid > 1184) grid = 1184;
+  moe_combine_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(ys), pos, w,
+                                               reinterpret_cast<const __nv_bfloat16*>(res), T, K, H,
+                                               reinterpret_cast<__nv_bfloat16*>(out));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_moe_combine_bwd(const void* dout, const void* ys, const int* row_slot, const int* seg_off,
+                                    const float* w, int E, int K, int H, void* dys, float* dw, int capacity,
+                                    cudaStream_t stream) {
+  if (H % 8 != 0) return -1;
+  moe_combine_bwd_kernel<<<1184, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
+                                                   reinterpret_cast<const __nv_bfloat16*>(ys), row_slot, seg_off, w,
+                                                   E, K, H, reinterpret_cast<__nv_bfloat16*>(dys), dw, capacity);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -1,4 +1,6 @@
 // C launchers of the non-GEMM kernels (implemented in the .cu files under csrc/).
+// All pointers are device pointers; bf16 tensors are passed as void*. Every function only
+// enqueues work on `stream` and returns 0, or a negative code for a rejected argument.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -6,6 +8,55 @@
 #ifdef __cplusplus
 extern "C" {
 #endif
+
+// ---- norm/rmsnorm.cu
+int b200_rmsnorm_fwd(const void* x, const void* res, const float* w, void* h_out, void* y, float* rstd, int T, int H,
+                     float eps, cudaStream_t stream);
+int b200_rmsnorm_bwd_blocks(int T);  // rows of the dw scratch: float[blocks * H]
+int b200_rmsnorm_bwd(const void* dy, const void* x, const float* rstd, const float* w, const void* dres, void* dx,
+                     float* dw_part, float* dw_out, int dw_accumulate, int T, int H, cudaStream_t stream);
+
+// ---- rope/qknorm_rope.cu
+int b200_qknorm_rope_blocks(long long items);  // dw scratch: float[blocks * 2 * hd]
+int b200_qknorm_rope_fwd(const void* qkv, int ld, const float* qw, const float* kw, const float* cs, void* q_out,
+                         void* k_out, void* v_out, float* rstd, int T, int S, int nh, int nkv, int hd, float eps,
+                         cudaStream_t stream);
+int b200_qknorm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, int ld, const float* rstd,
+                         const float* qw, const float* kw, const float* cs, void* dqkv, float* dw_part, float* dqw,
+                         float* dkw, int dw_accumulate, int T, int S, int nh, int nkv, int hd, cudaStream_t stream);
+
+// ---- moe/router.cu
+int b200_router_fwd(const float* logits, const float* bias, float* scores, float* topk_w, int* topk_idx, int T, int E,
+                    int K, int mode, int norm, float scale, int num_groups, int group_topk, cudaStream_t stream);
+int b200_router_bwd(const float* dscores, const float* dtopk_w, const float* scores, const int* topk_idx,
+                    void* dlogits, int T, int E, int K, int mode, int norm, float scale, cudaStream_t stream);
+
+// ---- moe/dispatch.cu
+int b200_moe_plan_blocks(int n);  // plan scratch: int[blocks * E]
+int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* seg_off, int* tile_expert,
+                  int* num_m_tiles, int* pos, int* row_slot, int capacity, cudaStream_t stream);
+int b200_moe_gather(const void* x, const int* row_slot, const int* seg_off, int E, int K, int H, void* xs,
+                    int capacity, cudaStream_t stream);
+int b200_moe_combine(const void* ys, const int* pos, const float* w, const void* res, int T, int K, int H, void* out,
+                     cudaStream_t stream);
+int b200_moe_combine_bwd(const void* dout, const void* ys, const int* row_slot, const int* seg_off, const float* w,
+                         int E, int K, int H, void* dys, float* dw, int capacity, cudaStream_t stream);
+
+// ---- lce/lce.cu
+int b200_lse_loss(const float* part, int n_tiles, const void* logits, long long ld, const long long* labels,
+                  int ignore_index, int T, int V, float* lse, float* loss_acc, cudaStream_t stream);
+int b200_dlogits(void* logits, long long ld, const float* lse, const long long* labels, int ignore_index, int T, int V,
+                 const float* loss_acc, float upstream, cudaStream_t stream);
+int b200_embed_fwd(const long long* ids, const void* table, int T, int H, int V, void* out, cudaStream_t stream);
+int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, float* grad, cudaStream_t stream);
+
+// ---- optim/optim.cu
+int b200_sumsq_blocks(long long n);  // scratch: float[blocks]
+int b200_sumsq(const float* g, long long n, float* scratch, float* out, int accumulate, cudaStream_t stream);
+int b200_clip_coef(const float* sumsq, float max_norm, float* coef, cudaStream_t stream);
+int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, float lr, float beta1,
+               float beta2, float eps, float wd, int step, const float* grad_coef, cudaStream_t stream);
+int b200_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

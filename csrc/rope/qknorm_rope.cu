@@ -1,0 +1,200 @@
+// Per-head QK RMSNorm (weight shared across heads) fused with rotate-half RoPE, forward and backward.
+// Input is the fused QKV projection output [T, (nh + 2 nkv) * hd]; one warp handles one (token, head).
+#include "../common/ptx.cuh"
+#include "../ops_api.h"
+
+namespace b200 {
+
+template <int EPL>  // elements per lane = hd / 32
+__device__ __forceinline__ void load_lane(const __nv_bfloat16* p, int lane, float (&f)[EPL]) {
+  if constexpr (EPL == 4) {
+    const uint2 q = *reinterpret_cast<const uint2*>(p + lane * 4);
+    const float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  } else if constexpr (EPL == 2) {
+    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p + lane * 2));
+    f[0] = a.x; f[1] = a.y;
+  } else {
+    f[0] = __bfloat162float(p[lane]);
+  }
+}
+template <int EPL>
+__device__ __forceinline__ void store_lane(__nv_bfloat16* p, int lane, const float (&f)[EPL]) {
+  if constexpr (EPL == 4) {
+    *reinterpret_cast<uint2*>(p + lane * 4) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+  } else if constexpr (EPL == 2) {
+    *reinterpret_cast<uint32_t*>(p + lane * 2) = pack_bf16x2(f[0], f[1]);
+  } else {
+    p[lane] = __float2bfloat16(f[0]);
+  }
+}
+
+template <int EPL>
+__global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, const float* __restrict__ qw,
+                                       const float* __restrict__ kw, const float* __restrict__ cs,  // [S, hd/2, 2]
+                                       __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
+                                       __nv_bfloat16* __restrict__ v_out, float* __restrict__ rstd_out, int T, int S,
+                                       int nh, int nkv, float eps) {
+  constexpr int HD = EPL * 32, HALF = HD / 2;
+  const int lane = threadIdx.x & 31;
+  const int nqk = nh + nkv, nall = nh + 2 * nkv;
+  const long long total = static_cast<long long>(T) * nall;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long it = wid; it < total; it += nw) {
+    const int t = static_cast<int>(it / nall), h = static_cast<int>(it - static_cast<long long>(t) * nall);
+    const bool is_q = h < nh;
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * HD;
+    float x[EPL];
+    load_lane<EPL>(src, lane, x);
+    if (h >= nqk) {  // v head: plain copy into the attention layout
+      store_lane<EPL>(v_out + (static_cast<size_t>(t) * nkv + (h - nqk)) * HD, lane, x);
+      continue;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / HD + eps);
+    if (lane == 0) rstd_out[static_cast<long long>(t) * nqk + h] = rstd;
+    const float* w = is_q ? qw : kw;
+    const float* csr = cs + static_cast<size_t>(t % S) * HALF * 2;
+    float y[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = lane * EPL + i;
+      const float xn = w[e] * __bfloat162float(__float2bfloat16(x[i] * rstd));
+      const float other = __shfl_xor_sync(0xffffffffu, xn, 16);
+      const int j = e % HALF;
+      const float c = csr[2 * j], s = csr[2 * j + 1];
+      y[i] = xn * c + (e < HALF ? -other : other) * s;
+    }
+    __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(t) * nh + h) * HD
+                              : k_out + (static_cast<size_t>(t) * nkv + (h - nh)) * HD;
+    store_lane<EPL>(dst, lane, y);
+  }
+}
+
+// dq/dk -> d(qkv) for the q and k heads, dv copied into the v slice; dw partials [grid, 2, hd].
+template <int EPL>
+__global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
+                                       const __nv_bfloat16* __restrict__ dv, const __nv_bfloat16* __restrict__ qkv,
+                                       int ld, const float* __restrict__ rstd_in, const float* __restrict__ qw,
+                                       const float* __restrict__ kw, const float* __restrict__ cs,
+                                       __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dw_part, int T, int S,
+                                       int nh, int nkv) {
+  constexpr int HD = EPL * 32, HALF = HD / 2;
+  __shared__ float sm[8][2][HD];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nqk = nh + nkv, nall = nh + 2 * nkv;
+  const long long total = static_cast<long long>(T) * nall;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float dwq[EPL], dwk[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) dwq[i] = dwk[i] = 0.f;
+  for (long long it = wid; it < total; it += nw) {
+    const int t = static_cast<int>(it / nall), h = static_cast<int>(it - static_cast<long long>(t) * nall);
+    __nv_bfloat16* dst = dqkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * HD;
+    if (h >= nqk) {  // v head: plain copy
+      float g[EPL];
+      load_lane<EPL>(dv + (static_cast<size_t>(t) * nkv + (h - nqk)) * HD, lane, g);
+      store_lane<EPL>(dst, lane, g);
+      continue;
+    }
+    const bool is_q = h < nh;
+    const __nv_bfloat16* gsrc = is_q ? dq + (static_cast<size_t>(t) * nh + h) * HD
+                                     : dk + (static_cast<size_t>(t) * nkv + (h - nh)) * HD;
+    float g[EPL], x[EPL];
+    load_lane<EPL>(gsrc, lane, g);
+    load_lane<EPL>(qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * HD, lane, x);
+    const float rstd = rstd_in[static_cast<long long>(t) * nqk + h];
+    const float* w = is_q ? qw : kw;
+    const float* csr = cs + static_cast<size_t>(t % S) * HALF * 2;
+    float dxn[EPL], xh[EPL], wd[EPL];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = lane * EPL + i;
+      const int j = e % HALF;
+      const float c = csr[2 * j], s = csr[2 * j + 1];
+      const float gs = g[i] * s;
+      const float other = __shfl_xor_sync(0xffffffffu, gs, 16);
+      // transpose of the rotation: lower half receives +z[i+HALF], upper half -z[i-HALF]
+      dxn[i] = g[i] * c + (e < HALF ? other : -other);
+      xh[i] = x[i] * rstd;
+      wd[i] = dxn[i] * w[e];
+      dot += wd[i] * xh[i];
+      if (is_q) dwq[i] += dxn[i] * xh[i]; else dwk[i] += dxn[i] * xh[i];
+    }
+    dot = warp_sum(dot) / HD;
+    float o[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) o[i] = rstd * (wd[i] - xh[i] * dot);
+    store_lane<EPL>(dst, lane, o);
+  }
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    sm[warp][0][lane * EPL + i] = dwq[i];
+    sm[warp][1][lane * EPL + i] = dwk[i];
+  }
+  __syncthreads();
+  const int nwarps = blockDim.x >> 5;
+  for (int c = threadIdx.x; c < 2 * HD; c += blockDim.x) {
+    float s = 0.f;
+    for (int wv = 0; wv < nwarps; ++wv) s += sm[wv][c / HD][c % HD];
+    dw_part[static_cast<size_t>(blockIdx.x) * 2 * HD + c] = s;
+  }
+}
+
+__global__ void qk_dw_reduce_kernel(const float* __restrict__ part, int nblocks, int hd, float* __restrict__ dqw,
+                                    float* __restrict__ dkw, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * hd) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += part[static_cast<size_t>(b) * 2 * hd + c];
+  float* out = c < hd ? dqw + c : dkw + (c - hd);
+  *out = accumulate ? *out + s : s;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_qknorm_rope_blocks(long long items) {
+  long long g = (items + 7) / 8;
+  return static_cast<int>(g < 1 ? 1 : (g > 1184 ? 1184 : g));
+}
+
+extern "C" int b200_qknorm_rope_fwd(const void* qkv, int ld, const float* qw, const float* kw, const float* cs,
+                                    void* q_out, void* k_out, void* v_out, float* rstd, int T, int S, int nh, int nkv,
+                                    int hd, float eps, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int grid = b200_qknorm_rope_blocks(static_cast<long long>(T) * (nh + 2 * nkv));
+#define ARGS reinterpret_cast<const __nv_bfloat16*>(qkv), ld, qw, kw, cs, reinterpret_cast<__nv_bfloat16*>(q_out), \
+             reinterpret_cast<__nv_bfloat16*>(k_out), reinterpret_cast<__nv_bfloat16*>(v_out), rstd, T, S, nh, nkv, eps
+  if (hd == 128) qknorm_rope_fwd_kernel<4><<<grid, 256, 0, stream>>>(ARGS);
+  else if (hd == 64) qknorm_rope_fwd_kernel<2><<<grid, 256, 0, stream>>>(ARGS);
+  else if (hd == 32) qknorm_rope_fwd_kernel<1><<<grid, 256, 0, stream>>>(ARGS);
+  else return -1;
+#undef ARGS
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_qknorm_rope_bwd(const void* dq, const void* dk, const void* dv, const void* qkv, int ld,
+                                    const float* rstd, const float* qw, const float* kw, const float* cs, void* dqkv,
+                                    float* dw_part, float* dqw, float* dkw, int dw_accumulate, int T, int S, int nh,
+                                    int nkv, int hd, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int grid = b200_qknorm_rope_blocks(static_cast<long long>(T) * (nh + 2 * nkv));
+#define ARGS reinterpret_cast<const __nv_bfloat16*>(dq), reinterpret_cast<const __nv_bfloat16*>(dk),             \
+             reinterpret_cast<const __nv_bfloat16*>(dv), reinterpret_cast<const __nv_bfloat16*>(qkv), ld, rstd, \
+             qw, kw, cs, reinterpret_cast<__nv_bfloat16*>(dqkv), dw_part, T, S, nh, nkv
+  if (hd == 128) qknorm_rope_bwd_kernel<4><<<grid, 256, 0, stream>>>(ARGS);
+  else if (hd == 64) qknorm_rope_bwd_kernel<2><<<grid, 256, 0, stream>>>(ARGS);
+  else if (hd == 32) qknorm_rope_bwd_kernel<1><<<grid, 256, 0, stream>>>(ARGS);
+  else return -1;
+#undef ARGS
+  qk_dw_reduce_kernel<<<(2 * hd + 127) / 128, 128, 0, stream>>>(dw_part, grid, hd, dqw, dkw, dw_accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

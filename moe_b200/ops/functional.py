@@ -1,0 +1,484 @@
+"""Autograd wrappers around the sm_100a kernels (the CUDA execution path).
+
+Weights are `torch.nn.Parameter`s holding the fp32 master values.  When the
+training engine has attached a bf16 compute copy (`p._bf16`) and an fp32
+gradient accumulator (`p.main_grad`), forward reads the copy and backward lets
+the weight-gradient GEMM epilogue write or accumulate straight into
+`main_grad` (first write of a step overwrites, later ones accumulate,
+tracked by `p._grad_live`) and returns no gradient tensor.  Without an
+engine the same functions cast on the fly and return ordinary gradients.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+from . import gemm as G
+
+BF16 = torch.bfloat16
+
+
+def ext():
+    return _ext.load()
+
+
+# ------------------------------------------------------------ parameter access
+def w16(p: torch.Tensor) -> torch.Tensor:
+    c = getattr(p, "_bf16", None)
+    return c if c is not None else p.detach().to(BF16)
+
+
+def w32(p: torch.Tensor) -> torch.Tensor:
+    return p.detach() if p.dtype == torch.float32 else p.detach().float()
+
+
+class GradSink:
+    """Where a weight gradient goes: the engine's fp32 accumulator, or a fresh tensor."""
+
+    def __init__(self, p: torch.Tensor):
+        self.p = p
+        self.main = getattr(p, "main_grad", None)
+
+    def target(self) -> tuple[torch.Tensor, int]:
+        """Returns (fp32 tensor to write, beta)."""
+        if self.main is not None:
+            beta = 1 if getattr(self.p, "_grad_live", False) else 0
+            return self.main, beta
+        return torch.empty(self.p.shape, dtype=torch.float32, device=self.p.device), 0
+
+    def done(self, t: torch.Tensor):
+        """Value to return from autograd.backward for this parameter."""
+        if self.main is not None:
+            self.p._grad_live = True
+            return None
+        return t.to(self.p.dtype)
+
+
+def _scratch(name: str, numel: int, dtype, device) -> torch.Tensor:
+    key = (name, dtype, device)
+    t = _SCRATCH.get(key)
+    if t is None or t.numel() < numel:
+        t = torch.empty(max(numel, 1), dtype=dtype, device=device)
+        _SCRATCH[key] = t
+    return t
+
+
+_SCRATCH: dict = {}
+
+
+# ------------------------------------------------------------------- embedding
+class EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, weight):
+        table = w16(weight)
+        flat = ids.reshape(-1).contiguous()
+        out = torch.empty(flat.numel(), table.shape[1], dtype=BF16, device=table.device)
+        ext().embed_fwd(flat, table, out)
+        ctx.save_for_backward(flat)
+        ctx.weight = weight
+        ctx.shape = tuple(ids.shape)
+        return out.view(*ids.shape, table.shape[1])
+
+    @staticmethod
+    def backward(ctx, dout):
+        (flat,) = ctx.saved_tensors
+        sink = GradSink(ctx.weight)
+        tgt, beta = sink.target()
+        if beta == 0:
+            tgt.zero_()
+        ext().embed_bwd(flat, dout.reshape(flat.numel(), -1).contiguous(), tgt)
+        return None, sink.done(tgt)
+
+
+# --------------------------------------------------------------------- rmsnorm
+class RMSNormFn(torch.autograd.Function):
+    """y = rmsnorm(x [+ res]); returns (h, y) where h = x + res is the new residual stream."""
+
+    @staticmethod
+    def forward(ctx, x, res, weight, eps):
+        x = x.contiguous()
+        H = x.shape[-1]
+        T = x.numel() // H
+        w = w32(weight)
+        y = torch.empty_like(x)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        if res is not None:
+            h = torch.empty_like(x)
+            ext().rmsnorm_fwd(x, res.contiguous(), w, h, y, rstd, eps)
+        else:
+            h = x
+            ext().rmsnorm_fwd(x, None, w, None, y, rstd, eps)
+        ctx.save_for_backward(h, rstd)
+        ctx.weight = weight
+        ctx.has_res = res is not None
+        return h, y
+
+    @staticmethod
+    def backward(ctx, dh, dy):
+        h, rstd = ctx.saved_tensors
+        H = h.shape[-1]
+        T = h.numel() // H
+        e = ext()
+        sink = GradSink(ctx.weight)
+        tgt, beta = sink.target()
+        part = _scratch("rms_dw", e.rmsnorm_bwd_blocks(T) * H, torch.float32, h.device)
+        dx = torch.empty_like(h)
+        dres = dh.contiguous() if dh is not None else None
+        e.rmsnorm_bwd(dy.contiguous(), h, rstd, w32(ctx.weight), dres, dx, part, tgt.view(-1), bool(beta))
+        return dx, (dx if ctx.has_res else None), sink.done(tgt), None
+
+
+def rmsnorm(x, weight, eps):
+    _, y = RMSNormFn.apply(x, None, weight, eps)
+    return y
+
+
+def add_rmsnorm(x, res, weight, eps):
+    """(x + res, rmsnorm(x + res)) in one pass."""
+    return RMSNormFn.apply(x, res, weight, eps)
+
+
+# ---------------------------------------------------------------------- linear
+class LinearFn(torch.autograd.Function):
+    """y = x @ W^T with W given as one or several row-adjacent parameters (e.g. q, k, v projections)."""
+
+    @staticmethod
+    def forward(ctx, x, fused, *weights):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if x2.dtype != BF16:
+            x2 = x2.to(BF16)
+        x2 = x2.contiguous()
+        if fused is not None:
+            wmat = fused[0]
+        elif len(weights) == 1:
+            wmat = w16(weights[0])
+        else:
+            wmat = torch.cat([w16(w) for w in weights], dim=0)
+        y = G.gemm_nt(x2, wmat)
+        ctx.save_for_backward(x2)
+        ctx.wmat = wmat
+        ctx.fused = fused
+        ctx.weights = weights
+        ctx.in_shape = tuple(x.shape)
+        return y.view(*x.shape[:-1], wmat.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        wmat = ctx.wmat
+        N, K = wmat.shape
+        dy2 = dy.reshape(-1, N)
+        if dy2.dtype != BF16:
+            dy2 = dy2.to(BF16)
+        dy2 = dy2.contiguous()
+        dx = G.gemm_nn(dy2, wmat).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        weights = ctx.weights
+        if ctx.fused is not None:
+            grad_view = ctx.fused[1]
+            beta = 1 if all(getattr(w, "_grad_live", False) for w in weights) else 0
+            if beta == 0 and any(getattr(w, "_grad_live", False) for w in weights):
+                raise RuntimeError("fused weight group has inconsistent gradient state")
+            G.gemm_tn(dy2, x2, grad_view, beta=beta)
+            for w in weights:
+                w._grad_live = True
+            return (dx, None) + (None,) * len(weights)
+        if len(weights) == 1:
+            sink = GradSink(weights[0])
+            tgt, beta = sink.target()
+            G.gemm_tn(dy2, x2, tgt, beta=beta)
+            return dx, None, sink.done(tgt)
+        full = torch.empty(N, K, dtype=torch.float32, device=dy2.device)
+        G.gemm_tn(dy2, x2, full)
+        outs, r = [], 0
+        for w in weights:
+            n = w.shape[0]
+            piece = full[r:r + n]
+            r += n
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                if getattr(w, "_grad_live", False):
+                    mg.add_(piece)
+                else:
+                    mg.copy_(piece)
+                w._grad_live = True
+                outs.append(None)
+            else:
+                outs.append(piece.to(w.dtype))
+        return (dx, None, *outs)
+
+
+def linear(x, *weights, fused=None):
+    return LinearFn.apply(x, fused, *weights)
+
+
+# ------------------------------------------------------------ qk-norm + rope
+_ROPE_TABLES: dict = {}
+
+
+def rope_table(S: int, hd: int, theta: float, device) -> torch.Tensor:
+    """Interleaved (cos, sin) table `[S, hd/2, 2]` in fp32."""
+    key = (S, hd, float(theta), device)
+    t = _ROPE_TABLES.get(key)
+    if t is None:
+        inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32, device=device) / hd))
+        fr = torch.outer(torch.arange(S, dtype=torch.float32, device=device), inv)
+        t = torch.stack([fr.cos(), fr.sin()], dim=-1).contiguous()
+        _ROPE_TABLES[key] = t
+    return t
+
+
+class QKNormRopeFn(torch.autograd.Function):
+    """Fused QKV projection output -> (q, k, v) in `[B, S, heads, hd]`, with per-head RMSNorm and RoPE on q, k."""
+
+    @staticmethod
+    def forward(ctx, qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps):
+        qkv2 = qkv.reshape(B * S, (nh + 2 * nkv) * hd).contiguous()
+        T = B * S
+        dev = qkv2.device
+        cs = rope_table(S, hd, theta, dev)
+        q = torch.empty(B, S, nh, hd, dtype=BF16, device=dev)
+        k = torch.empty(B, S, nkv, hd, dtype=BF16, device=dev)
+        v = torch.empty(B, S, nkv, hd, dtype=BF16, device=dev)
+        rstd = torch.empty(T * (nh + nkv), dtype=torch.float32, device=dev)
+        ext().qknorm_rope_fwd(qkv2, w32(q_w), w32(k_w), cs, q, k, v, rstd, S, nh, nkv, hd, eps)
+        ctx.save_for_backward(qkv2, rstd, cs)
+        ctx.q_w, ctx.k_w = q_w, k_w
+        ctx.dims = (B, S, nh, nkv, hd)
+        ctx.qkv_shape = tuple(qkv.shape)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        qkv2, rstd, cs = ctx.saved_tensors
+        B, S, nh, nkv, hd = ctx.dims
+        T = B * S
+        e = ext()
+        dev = qkv2.device
+        if dq is None:
+            dq = torch.zeros(B, S, nh, hd, dtype=BF16, device=dev)
+        if dk is None:
+            dk = torch.zeros(B, S, nkv, hd, dtype=BF16, device=dev)
+        if dv is None:
+            dv = torch.zeros(B, S, nkv, hd, dtype=BF16, device=dev)
+        sq, sk = GradSink(ctx.q_w), GradSink(ctx.k_w)
+        tq, bq = sq.target()
+        tk, bk = sk.target()
+        if bq != bk:  # keep one accumulate flag for the fused kernel
+            (tq if bq == 0 else tk).zero_()
+            bq = bk = 1
+        part = _scratch("qk_dw", e.qknorm_rope_blocks(T * (nh + 2 * nkv)) * 2 * hd, torch.float32, dev)
+        dqkv = torch.empty_like(qkv2)
+        e.qknorm_rope_bwd(dq.contiguous(), dk.contiguous(), dv.contiguous(), qkv2, rstd, w32(ctx.q_w), w32(ctx.k_w), cs,
+                          dqkv, part, tq, tk, bool(bq), S, nh, nkv, hd)
+        return dqkv.view(ctx.qkv_shape), sq.done(tq), sk.done(tk), None, None, None, None, None, None, None
+
+
+def qk_norm_rope(qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps):
+    return QKNormRopeFn.apply(qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps)
+
+
+# ------------------------------------------------------------------- attention
+def attention(q, k, v):
+    """Causal GQA attention, `[B,S,h,hd]` layout.  Library kernel (cuDNN / flash via SDPA) for now."""
+    o = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True)
+    return o.transpose(1, 2).contiguous()
+
+
+# ---------------------------------------------------------------------- router
+class RouterFn(torch.autograd.Function):
+    """Router GEMM (fp32 logits) + scoring / top-k kernel.  Returns (scores fp32, weights fp32, idx int32)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, K, mode, norm, scale, num_groups, group_topk):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        wmat = w16(weight)
+        E = wmat.shape[0]
+        T = x2.shape[0]
+        logits = G.gemm_nt(x2, wmat, out_dtype=torch.float32)
+        scores = torch.empty(T, E, dtype=torch.float32, device=x2.device)
+        tw = torch.empty(T, K, dtype=torch.float32, device=x2.device)
+        ti = torch.empty(T, K, dtype=torch.int32, device=x2.device)
+        b = bias.detach().float().contiguous() if bias is not None else None
+        ext().router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
+                         int(group_topk or 0))
+        ctx.save_for_backward(x2, scores, ti)
+        ctx.weight = weight
+        ctx.wmat = wmat
+        ctx.cfg = (K, mode, bool(norm), float(scale))
+        ctx.in_shape = tuple(x.shape)
+        ctx.mark_non_differentiable(ti)
+        return scores, tw, ti
+
+    @staticmethod
+    def backward(ctx, dscores, dtw, _):
+        x2, scores, ti = ctx.saved_tensors
+        K, mode, norm, scale = ctx.cfg
+        T, E = scores.shape
+        if dtw is None:
+            dtw = torch.zeros(T, K, dtype=torch.float32, device=x2.device)
+        dlogits = torch.empty(T, E, dtype=BF16, device=x2.device)
+        ds = dscores.contiguous().float() if dscores is not None else None
+        ext().router_bwd(ds, dtw.contiguous().float(), scores, ti, dlogits, K, mode, norm, scale)
+        dx = G.gemm_nn(dlogits, ctx.wmat).view(ctx.in_shape)
+        sink = GradSink(ctx.weight)
+        tgt, beta = sink.target()
+        G.gemm_tn(dlogits, x2, tgt, beta=beta)
+        return dx, sink.done(tgt), None, None, None, None, None, None, None
+
+
+def router(x, weight, bias, K, mode, norm, scale, num_groups, group_topk):
+    return RouterFn.apply(x, weight, bias, K, mode, norm, 1.0 if scale is None else scale, num_groups, group_topk)
+
+
+# --------------------------------------------------------------------- experts
+def moe_capacity(T: int, K: int, E: int) -> int:
+    """Rows of the expert-sorted layout in the worst case (every expert segment padded to 128)."""
+    return (T * K + E * 127 + 127) // 128 * 128
+
+
+class MoEPlan:
+    """Device-side dispatch plan: no host synchronisation, sizes are worst-case."""
+
+    def __init__(self, idx32: torch.Tensor, E: int):
+        e = ext()
+        dev = idx32.device
+        T, K = idx32.shape
+        self.T, self.K, self.E = T, K, E
+        self.cap = moe_capacity(T, K, E)
+        n = T * K
+        self.counts = torch.empty(E, dtype=torch.int32, device=dev)
+        self.seg_off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        self.tile_expert = torch.empty(self.cap // 128, dtype=torch.int32, device=dev)
+        self.num_m_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        self.pos = torch.empty(n, dtype=torch.int32, device=dev)
+        self.row_slot = torch.empty(self.cap, dtype=torch.int32, device=dev)
+        scratch = _scratch("moe_plan", e.moe_plan_blocks(n) * E, torch.int32, dev)
+        e.moe_plan(idx32.reshape(-1), E, scratch, self.counts, self.seg_off, self.tile_expert, self.num_m_tiles,
+                   self.pos, self.row_slot)
+
+
+class MoEExpertsFn(torch.autograd.Function):
+    """out[t] = sum_k w[t,k] * down_e(silu(gate_e x_t) * up_e x_t): plan, gather, two grouped GEMMs, combine."""
+
+    @staticmethod
+    def forward(ctx, x, topk_w, topk_idx, gate_up, down):
+        e = ext()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        T, H = x2.shape
+        K = topk_idx.shape[-1]
+        w1, w2 = w16(gate_up), w16(down)
+        E, I2, _ = w1.shape
+        I = I2 // 2
+        idx32 = topk_idx.reshape(T, K).to(torch.int32).contiguous()
+        tw = topk_w.reshape(T, K).float().contiguous()
+        plan = MoEPlan(idx32, E)
+        cap, dev = plan.cap, x2.device
+        xs = torch.empty(cap, H, dtype=BF16, device=dev)
+        e.moe_gather(x2, plan.row_slot, plan.seg_off, E, K, xs)
+        act = torch.empty(cap, I, dtype=BF16, device=dev)
+        gu = torch.empty(cap, I2, dtype=BF16, device=dev)
+        G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu)
+        ys = torch.empty(cap, H, dtype=BF16, device=dev)
+        G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys)
+        out = torch.empty(T, H, dtype=BF16, device=dev)
+        e.moe_combine(ys, plan.pos, tw, None, out, K)
+        ctx.save_for_backward(xs, gu, act, ys, tw)
+        ctx.plan = plan
+        ctx.params = (gate_up, down)
+        ctx.w = (w1, w2)
+        ctx.in_shape = tuple(x.shape)
+        ctx.counts = plan.counts
+        return out.view(ctx.in_shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        e = ext()
+        xs, gu, act, ys, tw = ctx.saved_tensors
+        plan = ctx.plan
+        w1, w2 = ctx.w
+        gate_up, down = ctx.params
+        T, K, E, cap = plan.T, plan.K, plan.E, plan.cap
+        H = xs.shape[1]
+        dev = xs.device
+        d2 = dout.reshape(T, H)
+        if d2.dtype != BF16:
+            d2 = d2.to(BF16)
+        d2 = d2.contiguous()
+        dys = torch.empty(cap, H, dtype=BF16, device=dev)
+        dw = torch.zeros(T * K, dtype=torch.float32, device=dev)
+        e.moe_combine_bwd(d2, ys, plan.row_slot, plan.seg_off, tw.view(-1), E, K, dys, dw)
+        dgu = torch.empty_like(gu)
+        G.grouped_nn_swiglu_bwd(dys, w2, plan.tile_expert, plan.num_m_tiles, gu, dgu)
+        s2 = GradSink(down)
+        t2, b2 = s2.target()
+        G.grouped_tn(dys, act, plan.seg_off, t2, beta=b2)
+        dxs = dys  # reuse: dys is dead after the two GEMMs above
+        G.grouped_nn(dgu, w1, plan.tile_expert, plan.num_m_tiles, dxs)
+        s1 = GradSink(gate_up)
+        t1, b1 = s1.target()
+        G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1)
+        dx = torch.empty(T, H, dtype=BF16, device=dev)
+        e.moe_combine(dxs, plan.pos, None, None, dx, K)
+        return dx.view(ctx.in_shape), dw.view(T, K), None, s1.done(t1), s2.done(t2)
+
+
+def moe_experts(x, topk_idx, topk_w, gate_up, down):
+    return MoEExpertsFn.apply(x, topk_w, topk_idx, gate_up, down)
+
+
+# --------------------------------------------------- fused linear + cross entropy
+class LinearCrossEntropyFn(torch.autograd.Function):
+    """Mean cross entropy of `h @ W^T` against aligned labels.
+
+    The vocabulary GEMM stores bf16 logits once (HBM is large enough) together with softmax
+    partials from its epilogue; the gradient w.r.t. logits is formed in place and the two
+    gradient GEMMs run inside forward, so nothing of size [T, V] survives the call.
+    `upstream` is d(total loss)/d(this loss), which must be known when forward runs.
+    """
+
+    @staticmethod
+    def forward(ctx, h, weight, labels, ignore_index, upstream):
+        e = ext()
+        h2 = h.reshape(-1, h.shape[-1])
+        if h2.dtype != BF16:
+            h2 = h2.to(BF16)
+        h2 = h2.contiguous()
+        T = h2.shape[0]
+        wmat = w16(weight)
+        V = wmat.shape[0]
+        lab = labels.reshape(-1).contiguous()
+        logits, part = G.gemm_nt_lse(h2, wmat)
+        lse = torch.empty(T, dtype=torch.float32, device=h2.device)
+        acc = torch.zeros(2, dtype=torch.float32, device=h2.device)
+        e.lse_loss(part, logits, lab, ignore_index, lse, acc)
+        loss = acc[0] / acc[1].clamp_min(1.0)
+        need_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])
+        ctx.have_grad = need_grad
+        if need_grad:
+            e.dlogits_(logits, lse, lab, ignore_index, acc, float(upstream))
+            dh = G.gemm_nn(logits, wmat, m_fast=0)
+            sink = GradSink(weight)
+            tgt, beta = sink.target()
+            G.gemm_tn(logits, h2, tgt, beta=beta)
+            ctx.dw = sink.done(tgt)
+            ctx.save_for_backward(dh)
+            ctx.in_shape = tuple(h.shape)
+            ctx.upstream = float(upstream)
+        del logits
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        if not ctx.have_grad:
+            return None, None, None, None, None
+        (dh,) = ctx.saved_tensors
+        dw = ctx.dw
+        ctx.dw = None
+        dh = dh * (dloss / ctx.upstream).to(dh.dtype)
+        return dh.view(ctx.in_shape), dw, None, None, None
+
+
+def linear_cross_entropy(h, weight, labels, ignore_index=-100, upstream=1.0):
+    return LinearCrossEntropyFn.apply(h, weight, labels, ignore_index, upstream)

@@ -1,0 +1,326 @@
+"""Training engine: flat parameter / gradient / optimiser-state buffers.
+
+Replaces what the reference borrows from Accelerate + torch DDP + `torch.optim.AdamW`
+(`train.py:398-403,507-509,546-556`, `src/utils/training.py:75-95`):
+
+* every parameter is a view into one fp32 master buffer; on CUDA a bf16 compute copy and an fp32
+  gradient accumulator of the same layout sit beside it.  Weight-gradient GEMM epilogues write
+  into the accumulator directly, so there is no per-parameter `.grad` traffic;
+* data parallelism is an all-reduce (average) over slices of the flat gradient buffer, issued
+  per layer on a side stream while backward is still running;
+* gradient norm, clipping and AdamW run over the flat buffers in a handful of launches with no
+  host synchronisation; the same pass refreshes the bf16 copy.
+
+On CPU the same class runs with plain torch ops (gloo for the all-reduce).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..ops import oracle
+
+ALIGN = 64  # elements; keeps every slice 16-byte aligned in bf16 and 256-byte aligned in fp32
+
+
+def is_no_decay(name: str, p: torch.Tensor) -> bool:
+    """Weight-decay rule of the reference (`src/utils/training.py:79-84`)."""
+    return p.ndim < 2 or "bias" in name or "norm" in name or "embedding" in name
+
+
+@dataclass
+class Slot:
+    name: str
+    param: nn.Parameter
+    offset: int
+    numel: int
+    decay: bool
+
+
+class _LayerBoundary(torch.autograd.Function):
+    """Identity in forward; in backward tells the engine that every gradient produced *after*
+    this point of the forward pass is complete."""
+
+    @staticmethod
+    def forward(ctx, h, y, engine, tag):
+        ctx.engine, ctx.tag = engine, tag
+        return h.view_as(h), y.view_as(y)
+
+    @staticmethod
+    def backward(ctx, gh, gy):
+        ctx.engine._on_boundary(ctx.tag)
+        return gh, gy, None, None
+
+
+class TrainEngine:
+    def __init__(self, model: nn.Module, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.1, max_grad_norm: float = 1.0, process_group=None,
+                 overlap_grad_reduce: bool = True, device: torch.device | str | None = None):
+        self.model = model
+        self.lr, self.betas, self.eps = lr, betas, eps
+        self.weight_decay, self.max_grad_norm = weight_decay, max_grad_norm
+        self.group = process_group
+        self.world = dist.get_world_size(process_group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.step_count = 0
+        if device is not None:
+            model.to(device)
+        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        if not params:
+            raise ValueError("model has no trainable parameters")
+        self.device = params[0][1].device
+        self.cuda = self.device.type == "cuda"
+        self.overlap = overlap_grad_reduce and self.cuda and self.world > 1
+        # ---- layout: decayed parameters first, then the rest; module order inside each part
+        slots: list[Slot] = []
+        off = 0
+        for want_decay in (True, False):
+            for n, p in params:
+                if (not is_no_decay(n, p)) != want_decay:
+                    continue
+                slots.append(Slot(n, p, off, p.numel(), want_decay))
+                off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+            if want_decay:
+                self.decay_end = off
+        self.total = off
+        self.slots = slots
+        self.by_name = {s.name: s for s in slots}
+        dev = self.device
+        self.p32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.g32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.m = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.p16 = torch.zeros(self.total, dtype=torch.bfloat16, device=dev) if self.cuda else None
+        for s in slots:
+            view = self.p32[s.offset:s.offset + s.numel].view(s.param.shape)
+            view.copy_(s.param.data)
+            s.param.data = view
+            gview = self.g32[s.offset:s.offset + s.numel].view(s.param.shape)
+            if self.cuda:
+                s.param._bf16 = self.p16[s.offset:s.offset + s.numel].view(s.param.shape)
+                s.param.main_grad = gview
+                s.param._grad_live = False
+            else:
+                s.param.grad = gview
+        if self.cuda:
+            self._norm_ss = torch.zeros(1, dtype=torch.float32, device=dev)
+            self._coef = torch.ones(2, dtype=torch.float32, device=dev)
+            from ..ops import _ext
+
+            self._ext = _ext.load()
+            self._ss_scratch = torch.empty(self._ext.sumsq_blocks(self.total), dtype=torch.float32, device=dev)
+            self._fuse_adjacent()
+            self.refresh_compute_copy()
+            self._comm_stream = torch.cuda.Stream(device=dev) if self.world > 1 else None
+        self._layer_offs = self.layer_offsets()
+        inner = getattr(self.model, "model", None)
+        if inner is not None and hasattr(inner, "_boundary_fn"):
+            inner._boundary_fn = self.boundary if self.overlap else None
+        self._grad_norm = None
+        self._reduced_upto = self.total  # everything at or above this offset has been handed to the reducer
+        self._pending = []
+        self._boundaries: dict[int, int] = {}
+
+    # ------------------------------------------------------------------ set-up helpers
+    def _fuse_adjacent(self) -> None:
+        """Give attention / dense-MLP modules one matrix view over projections that sit side by side."""
+        from ..models.backbone import Attention, DenseMLP
+
+        def adjacent(ws):
+            ss = [self._slot_of(w) for w in ws]
+            if any(s is None for s in ss):
+                return None
+            for a, b in zip(ss, ss[1:]):
+                if a.offset + a.numel != b.offset:
+                    return None
+            rows = sum(w.shape[0] for w in ws)
+            cols = ws[0].shape[1]
+            o = ss[0].offset
+            return (self.p16[o:o + rows * cols].view(rows, cols), self.g32[o:o + rows * cols].view(rows, cols))
+
+        for mod in self.model.modules():
+            if isinstance(mod, Attention):
+                mod._fused_qkv = adjacent([mod.q_proj.weight, mod.k_proj.weight, mod.v_proj.weight])
+            elif isinstance(mod, DenseMLP):
+                mod._fused_gate_up = adjacent([mod.gate_proj.weight, mod.up_proj.weight])
+
+    def _slot_of(self, p) -> Slot | None:
+        for s in self.slots:
+            if s.param is p:
+                return s
+        return None
+
+    def refresh_compute_copy(self) -> None:
+        if self.cuda:
+            self._ext.cast_bf16(self.p32, self.p16)
+
+    # ---------------------------------------------------------------- backward overlap
+    def boundary(self, h: torch.Tensor, y: torch.Tensor, layer_idx: int):
+        """Called by the decoder at the input of layer `layer_idx` with (residual stream, normed input).
+        Backward reaches this node only after every gradient of layers >= layer_idx is complete."""
+        if not self.overlap or not (h.requires_grad and y.requires_grad):
+            return h, y
+        off = self._layer_offs[layer_idx]
+        if off is None:
+            return h, y
+        return _LayerBoundary.apply(h, y, self, off)
+
+    def layer_offsets(self) -> list[int]:
+        """Lowest flat offset (within the decayed part) owned by each decoder layer, in layer order."""
+        outs = []
+        layers = getattr(getattr(self.model, "model", None), "layers", [])
+        for i, _ in enumerate(layers):
+            pre = f"model.layers.{i}."
+            offs = [s.offset for s in self.slots if s.name.startswith(pre) and s.decay]
+            outs.append(min(offs) if offs else None)
+        return outs
+
+    def _on_boundary(self, first_offset: int) -> None:
+        # decayed region [first_offset, _reduced_upto) is final: reduce it now on the side stream
+        hi = min(self._reduced_upto, self.decay_end)
+        if first_offset < hi:
+            self._launch_reduce(first_offset, hi)
+            self._reduced_upto = first_offset
+
+    def _launch_reduce(self, lo: int, hi: int) -> None:
+        if self.world == 1 or hi <= lo:
+            return
+        self._zero_dead(lo, hi)
+        chunk = self.g32[lo:hi]
+        if self.cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ev)
+                work = dist.all_reduce(chunk, op=dist.ReduceOp.AVG, group=self.group, async_op=True)
+            self._pending.append(work)
+        else:
+            dist.all_reduce(chunk, op=dist.ReduceOp.SUM, group=self.group)
+            chunk.div_(self.world)
+
+    def _zero_dead(self, lo: int, hi: int) -> None:
+        """Parameters that received no gradient this step must contribute zeros."""
+        if not self.cuda:
+            return
+        for s in self.slots:
+            if lo <= s.offset < hi:
+                if s.param.grad is not None:  # a gradient that came through ordinary autograd
+                    if s.param._grad_live:
+                        s.param.main_grad.add_(s.param.grad)
+                    else:
+                        s.param.main_grad.copy_(s.param.grad)
+                    s.param.grad = None
+                    s.param._grad_live = True
+                if not s.param._grad_live:
+                    s.param.main_grad.zero_()
+                    s.param._grad_live = True
+
+    # ------------------------------------------------------------------------- step
+    def zero_grad(self) -> None:
+        if self.cuda:
+            for s in self.slots:
+                s.param._grad_live = False
+                s.param.grad = None
+        else:
+            self.g32.zero_()
+            for s in self.slots:  # autograd may have replaced the view
+                g = self.g32[s.offset:s.offset + s.numel].view(s.param.shape)
+                if s.param.grad is None or s.param.grad.data_ptr() != g.data_ptr():
+                    s.param.grad = g
+        self._reduced_upto = self.total
+        self._pending = []
+
+    def reduce_gradients(self) -> None:
+        """Finish the data-parallel average of whatever has not been reduced during backward."""
+        if not self.cuda:
+            for s in self.slots:
+                g = self.g32[s.offset:s.offset + s.numel].view(s.param.shape)
+                if s.param.grad is not None and s.param.grad.data_ptr() != g.data_ptr():
+                    g.copy_(s.param.grad)
+                    s.param.grad = g
+        if self.world == 1:
+            self._zero_dead(0, self.total)
+            return
+        # the undecayed tail (norm weights) and anything below the last boundary
+        hi = min(self._reduced_upto, self.decay_end)
+        self._launch_reduce(0, hi)
+        self._launch_reduce(self.decay_end, self.total)
+        self._reduced_upto = 0
+        for w in self._pending:
+            w.wait()
+        self._pending = []
+        if self.cuda and self._comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+
+    def step(self, lr: float | None = None) -> torch.Tensor:
+        """Reduce, clip by global norm, AdamW.  Returns the (pre-clip) gradient norm as a tensor."""
+        if lr is not None:
+            self.lr = lr
+        self.reduce_gradients()
+        self.step_count += 1
+        b1, b2 = self.betas
+        if self.cuda:
+            e = self._ext
+            e.sumsq(self.g32, self._ss_scratch, self._norm_ss, False)
+            e.clip_coef(self._norm_ss, float(self.max_grad_norm or 0.0), self._coef)
+            d = self.decay_end
+            if d > 0:
+                e.adamw(self.p32[:d], self.g32[:d], self.m[:d], self.v[:d], self.p16[:d], self.lr, b1, b2, self.eps,
+                        self.weight_decay, self.step_count, self._coef)
+            if self.total > d:
+                e.adamw(self.p32[d:], self.g32[d:], self.m[d:], self.v[d:], self.p16[d:], self.lr, b1, b2, self.eps,
+                        0.0, self.step_count, self._coef)
+            self._grad_norm = self._coef[1]
+        else:
+            norm = self.g32.norm()
+            coef = 1.0
+            if self.max_grad_norm and self.max_grad_norm > 0:
+                coef = float(min(1.0, self.max_grad_norm / (norm.item() + 1e-6)))
+            d = self.decay_end
+            for lo, hi, wd in ((0, d, self.weight_decay), (d, self.total, 0.0)):
+                if hi > lo:
+                    oracle.adamw_step_(self.p32[lo:hi], self.g32[lo:hi], self.m[lo:hi], self.v[lo:hi], lr=self.lr,
+                                       beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd, step=self.step_count,
+                                       grad_scale=coef)
+            self._grad_norm = norm
+        return self._grad_norm
+
+    # ------------------------------------------------------------------------ state
+    def grad_norm(self) -> torch.Tensor | None:
+        return self._grad_norm
+
+    def optimizer_state_dict(self) -> dict:
+        st = {"step": self.step_count, "lr": self.lr, "state": {}}
+        for s in self.slots:
+            sl = slice(s.offset, s.offset + s.numel)
+            st["state"][s.name] = {"exp_avg": self.m[sl].view(s.param.shape).detach().cpu().clone(),
+                                   "exp_avg_sq": self.v[sl].view(s.param.shape).detach().cpu().clone()}
+        return st
+
+    def load_optimizer_state_dict(self, st: dict) -> None:
+        self.step_count = int(st["step"])
+        self.lr = float(st.get("lr", self.lr))
+        for name, d in st["state"].items():
+            s = self.by_name.get(name)
+            if s is None:
+                continue
+            sl = slice(s.offset, s.offset + s.numel)
+            self.m[sl].copy_(d["exp_avg"].reshape(-1))
+            self.v[sl].copy_(d["exp_avg_sq"].reshape(-1))
+
+    def load_model_state_dict(self, sd: dict, strict: bool = True) -> None:
+        self.model.load_state_dict(sd, strict=strict)
+        self.refresh_compute_copy()
+
+    def broadcast_parameters(self, src: int = 0) -> None:
+        """Make rank `src` authoritative (the reference gets this from DDP's initial broadcast)."""
+        if self.world > 1:
+            dist.broadcast(self.p32, src=src, group=self.group)
+            for mod in self.model.modules():
+                for b in mod.buffers(recurse=False):
+                    dist.broadcast(b, src=src, group=self.group)
+            self.refresh_compute_copy()
