@@ -32,6 +32,38 @@ NVCC_FLAGS = [
 
 _module = None
 
+# Kernels enqueued per binding call; `launch_count()` sums them (used by bench.py's gpu_launches).
+KERNELS_PER_CALL = {"gemm": 1, "rmsnorm_fwd": 1, "rmsnorm_bwd": 2, "qknorm_rope_fwd": 1, "qknorm_rope_bwd": 2,
+                    "router_fwd": 1, "router_bwd": 1, "moe_plan": 3, "moe_gather": 1, "moe_combine": 1,
+                    "moe_combine_bwd": 1, "lse_loss": 1, "dlogits_": 1, "embed_fwd": 1, "embed_bwd": 1, "sumsq": 2,
+                    "clip_coef": 1, "adamw": 1, "cast_bf16": 1}
+_launches = 0
+
+
+class _Counting:
+    """Attribute proxy over the extension module that counts kernel launches."""
+
+    def __init__(self, mod):
+        self._mod = mod
+
+    def __getattr__(self, name):
+        fn = getattr(self._mod, name)
+        n = KERNELS_PER_CALL.get(name, 0)
+        if n == 0:
+            return fn
+
+        def call(*a, **k):
+            global _launches
+            _launches += n
+            return fn(*a, **k)
+
+        setattr(self, name, call)
+        return call
+
+
+def launch_count() -> int:
+    return _launches
+
 
 def sources() -> tuple[list[Path], list[Path], list[Path]]:
     cu = sorted(_CSRC.rglob("*.cu"))
@@ -114,8 +146,8 @@ def load(build_if_missing: bool = True):
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     sys.modules[f"moe_b200.{_NAME}"] = mod
-    _module = mod
-    return mod
+    _module = _Counting(mod)
+    return _module
 
 
 def available() -> bool:
