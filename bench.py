@@ -39,6 +39,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=None, help="override per-GPU micro-batch")
     ap.add_argument("--seq", type=int, default=None, help="override sequence length")
     ap.add_argument("--no-overlap", action="store_true", help="reduce gradients after backward, not during")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no whole-step CUDA graph)")
     return ap.parse_args()
 
 
@@ -176,11 +177,12 @@ def run_ours(args) -> dict:
     B, S = tcfg.batch_size, cfg["data"]["seq_len"]
     V = cfg["model"]["vocab_size"]
     model, mcfg = build_model(cfg, seed=42, device=f"cuda:{local}")
-    trainer = Trainer(model, tcfg, is_moe=cfg["model"]["type"] != "dense", overlap_grad_reduce=not args.no_overlap)
+    trainer = Trainer(model, tcfg, is_moe=cfg["model"]["type"] != "dense", overlap_grad_reduce=not args.no_overlap,
+                      cuda_graph=not args.no_graph)
     n_params = sum(p.numel() for p in model.parameters())
     K, W = args.steps, args.warmup
     host = make_batches(W + 2 * K, B, S, V, rank, cfg["data"].get("seed", 0))
-    # ---- warm-up (untimed)
+    # ---- warm-up (untimed); with the CUDA graph on, the first two steps run eagerly, the third captures
     for i in range(W):
         r = trainer.train_step({"input_ids": host[i], "labels": host[i]})
     torch.cuda.synchronize()

@@ -189,14 +189,15 @@ void clip_coef(const Tensor& ss, double max_norm, Tensor& coef) {
   c10::cuda::CUDAGuard gd(ss.device());
   rc_ok(b200_clip_coef(ss.data_ptr<float>(), (float)max_norm, coef.data_ptr<float>(), stream()), "clip_coef");
 }
-void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptT& p16, double lr, double beta1, double beta2,
-           double eps, double wd, int64_t step, const OptT& grad_coef) {
-  f32c(p, "p"); f32c(g, "g"); f32c(m, "m"); f32c(v, "v");
+void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptT& p16, const Tensor& hyper, double beta1,
+           double beta2, double eps, double wd, const OptT& grad_coef) {
+  f32c(p, "p"); f32c(g, "g"); f32c(m, "m"); f32c(v, "v"); f32c(hyper, "hyper");
+  need(hyper.numel() >= 3, "hyper must hold {lr, bc1, bc2}");
   c10::cuda::CUDAGuard gd(p.device());
   need(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw sizes");
   rc_ok(b200_adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
-                   optp<void>(p16), p.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step,
-                   optp<const float>(grad_coef), stream()), "adamw");
+                   optp<void>(p16), p.numel(), hyper.data_ptr<float>(), (float)beta1, (float)beta2, (float)eps,
+                   (float)wd, optp<const float>(grad_coef), stream()), "adamw");
 }
 void cast_bf16(const Tensor& src, Tensor& dst) {
   f32c(src, "src"); bf16c(dst, "dst");

@@ -150,14 +150,23 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
   }
 }
 
-// out[col] (+)= sum_b part[b, col]   (fixed order: deterministic)
+// out[col] (+)= sum_b part[b, col]   (fixed order: deterministic).  Block = 32 columns x 8 row-strided warps.
 __global__ void colsum_kernel(const float* __restrict__ part, float* __restrict__ out, int nblocks, int H,
                               int accumulate) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= H) return;
+  __shared__ float sm[8][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += part[static_cast<size_t>(b) * H + col];
-  out[col] = accumulate ? out[col] + s : s;
+  if (col < H)
+    for (int b = warp; b < nblocks; b += 8) s += part[static_cast<size_t>(b) * H + col];
+  sm[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && col < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sm[w][lane];
+    out[col] = accumulate ? out[col] + t : t;
+  }
 }
 
 }  // namespace b200
@@ -200,6 +209,6 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const float* rstd
   else if (nch32 <= 8) LAUNCH(8);
   else LAUNCH(16);
 #undef LAUNCH
-  colsum_kernel<<<(H + 127) / 128, 128, 0, stream>>>(dw_part, dw_out, grid, H, dw_accumulate);
+  colsum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_part, dw_out, grid, H, dw_accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -54,8 +54,9 @@ int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, 
 int b200_sumsq_blocks(long long n);  // scratch: float[blocks]
 int b200_sumsq(const float* g, long long n, float* scratch, float* out, int accumulate, cudaStream_t stream);
 int b200_clip_coef(const float* sumsq, float max_norm, float* coef, cudaStream_t stream);
-int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, float lr, float beta1,
-               float beta2, float eps, float wd, int step, const float* grad_coef, cudaStream_t stream);
+// hyper: device float[3] = {lr, 1 - beta1^t, 1 - beta2^t}
+int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, const float* hyper, float beta1,
+               float beta2, float eps, float wd, const float* grad_coef, cudaStream_t stream);
 int b200_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 
 #ifdef __cplusplus

@@ -59,9 +59,12 @@ __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm
 
 // AdamW with decoupled weight decay over a flat slice; gradients are scaled by *grad_coef (clip).
 __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
-                             float* __restrict__ v, __nv_bfloat16* __restrict__ p16, long long n, float lr, float beta1,
-                             float beta2, float eps, float wd, float bc1, float bc2,
+                             float* __restrict__ v, __nv_bfloat16* __restrict__ p16, long long n,
+                             const float* __restrict__ hyper, float beta1, float beta2, float eps, float wd,
                              const float* __restrict__ grad_coef) {
+  // hyper = {learning rate, 1 - beta1^t, 1 - beta2^t}: device-resident so that a captured CUDA graph
+  // can be replayed with new values
+  const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2];
   const float gc = grad_coef ? grad_coef[0] : 1.f;
   const float rs_bc2 = rsqrtf(bc2);
   const float step = lr / bc1;
@@ -143,15 +146,14 @@ extern "C" int b200_clip_coef(const float* sumsq, float max_norm, float* coef, c
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-extern "C" int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, float lr, float beta1,
-                          float beta2, float eps, float wd, int step, const float* grad_coef, cudaStream_t stream) {
+extern "C" int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, const float* hyper,
+                          float beta1, float beta2, float eps, float wd, const float* grad_coef,
+                          cudaStream_t stream) {
   if (n <= 0) return 0;
-  const float bc1 = static_cast<float>(1.0 - pow(static_cast<double>(beta1), static_cast<double>(step)));
-  const float bc2 = static_cast<float>(1.0 - pow(static_cast<double>(beta2), static_cast<double>(step)));
   long long b = (n / 4 + 255) / 256;
   const int grid = static_cast<int>(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
-  adamw_kernel<<<grid, 256, 0, stream>>>(p, g, m, v, reinterpret_cast<__nv_bfloat16*>(p16), n, lr, beta1, beta2,
-                                         eps, wd, bc1, bc2, grad_coef);
+  adamw_kernel<<<grid, 256, 0, stream>>>(p, g, m, v, reinterpret_cast<__nv_bfloat16*>(p16), n, hyper, beta1, beta2,
+                                         eps, wd, grad_coef);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

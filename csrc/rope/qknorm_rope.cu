@@ -149,12 +149,22 @@ __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, con
 
 __global__ void qk_dw_reduce_kernel(const float* __restrict__ part, int nblocks, int hd, float* __restrict__ dqw,
                                     float* __restrict__ dkw, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * hd) return;
+  // block = 32 columns of the [nblocks, 2*hd] partials, 8 warps stride over the rows; fixed summation order
+  __shared__ float sm[8][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += part[static_cast<size_t>(b) * 2 * hd + c];
-  float* out = c < hd ? dqw + c : dkw + (c - hd);
-  *out = accumulate ? *out + s : s;
+  if (c < 2 * hd)
+    for (int b = warp; b < nblocks; b += 8) s += part[static_cast<size_t>(b) * 2 * hd + c];
+  sm[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < 2 * hd) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sm[w][lane];
+    float* out = c < hd ? dqw + c : dkw + (c - hd);
+    *out = accumulate ? *out + t : t;
+  }
 }
 
 }  // namespace b200
@@ -195,6 +205,6 @@ extern "C" int b200_qknorm_rope_bwd(const void* dq, const void* dk, const void* 
   else if (hd == 32) qknorm_rope_bwd_kernel<1><<<grid, 256, 0, stream>>>(ARGS);
   else return -1;
 #undef ARGS
-  qk_dw_reduce_kernel<<<(2 * hd + 127) / 128, 128, 0, stream>>>(dw_part, grid, hd, dqw, dkw, dw_accumulate);
+  qk_dw_reduce_kernel<<<(2 * hd + 31) / 32, 256, 0, stream>>>(dw_part, grid, hd, dqw, dkw, dw_accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -65,6 +65,12 @@ def launch_count() -> int:
     return _launches
 
 
+def add_launches(n: int) -> None:
+    """Account for kernels that run without passing through the bindings (CUDA-graph replays)."""
+    global _launches
+    _launches += n
+
+
 def sources() -> tuple[list[Path], list[Path], list[Path]]:
     cu = sorted(_CSRC.rglob("*.cu"))
     cpp = sorted(_CSRC.rglob("*.cpp"))

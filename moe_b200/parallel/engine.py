@@ -109,6 +109,10 @@ class TrainEngine:
         if self.cuda:
             self._norm_ss = torch.zeros(1, dtype=torch.float32, device=dev)
             self._coef = torch.ones(2, dtype=torch.float32, device=dev)
+            # {lr, 1 - beta1^t, 1 - beta2^t}: read by the AdamW kernel from device memory, refreshed by
+            # an async copy from pinned memory before each step (so a captured graph can be replayed)
+            self._hyper = torch.zeros(3, dtype=torch.float32, device=dev)
+            self._hyper_host = torch.zeros(3, dtype=torch.float32).pin_memory()
             from ..ops import _ext
 
             self._ext = _ext.load()
@@ -256,12 +260,28 @@ class TrainEngine:
         if self.cuda and self._comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
 
-    def step(self, lr: float | None = None) -> torch.Tensor:
-        """Reduce, clip by global norm, AdamW.  Returns the (pre-clip) gradient norm as a tensor."""
+    def set_hyper(self, lr: float | None = None) -> None:
+        """Stage the learning rate and Adam bias corrections of the NEXT step on the device."""
         if lr is not None:
             self.lr = lr
+        if self.cuda:
+            t = self.step_count + 1
+            self._hyper_host[0] = self.lr
+            self._hyper_host[1] = 1.0 - self.betas[0] ** t
+            self._hyper_host[2] = 1.0 - self.betas[1] ** t
+            self._hyper.copy_(self._hyper_host, non_blocking=True)
+
+    def step(self, lr: float | None = None, *, update_hyper: bool = True, count: bool = True) -> torch.Tensor:
+        """Reduce, clip by global norm, AdamW.  Returns the (pre-clip) gradient norm as a tensor.
+        `update_hyper=False, count=False` is for CUDA-graph capture: the caller stages the
+        hyper-parameters and advances the step counter around each replay."""
+        if update_hyper:
+            self.set_hyper(lr)
+        elif lr is not None:
+            self.lr = lr
         self.reduce_gradients()
-        self.step_count += 1
+        if count:
+            self.step_count += 1
         b1, b2 = self.betas
         if self.cuda:
             e = self._ext
@@ -269,11 +289,11 @@ class TrainEngine:
             e.clip_coef(self._norm_ss, float(self.max_grad_norm or 0.0), self._coef)
             d = self.decay_end
             if d > 0:
-                e.adamw(self.p32[:d], self.g32[:d], self.m[:d], self.v[:d], self.p16[:d], self.lr, b1, b2, self.eps,
-                        self.weight_decay, self.step_count, self._coef)
+                e.adamw(self.p32[:d], self.g32[:d], self.m[:d], self.v[:d], self.p16[:d], self._hyper, b1, b2, self.eps,
+                        self.weight_decay, self._coef)
             if self.total > d:
-                e.adamw(self.p32[d:], self.g32[d:], self.m[d:], self.v[d:], self.p16[d:], self.lr, b1, b2, self.eps,
-                        0.0, self.step_count, self._coef)
+                e.adamw(self.p32[d:], self.g32[d:], self.m[d:], self.v[d:], self.p16[d:], self._hyper, b1, b2,
+                        self.eps, 0.0, self._coef)
             self._grad_norm = self._coef[1]
         else:
             norm = self.g32.norm()

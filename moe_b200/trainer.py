@@ -15,6 +15,7 @@ from dataclasses import dataclass, field
 import torch
 import torch.distributed as dist
 
+from .ops import _ext
 from .parallel.engine import TrainEngine
 from .utils.training import TrainingConfig, lr_factor
 
@@ -33,7 +34,7 @@ class StepResult:
 
 class Trainer:
     def __init__(self, model, cfg: TrainingConfig, *, device=None, process_group=None, is_moe: bool = True,
-                 overlap_grad_reduce: bool = True):
+                 overlap_grad_reduce: bool = True, cuda_graph: bool = False, graph_warmup_steps: int = 2):
         self.model = model
         self.cfg = cfg
         self.is_moe = is_moe
@@ -44,6 +45,15 @@ class Trainer:
         self.device = self.engine.device
         self.global_step = 0
         self.world = self.engine.world
+        # whole-step CUDA graph: the step is captured once (after a few eager steps have run every
+        # lazy initialisation) and replayed with new inputs / learning rate, which removes the
+        # per-op launch and autograd overhead of several hundred small launches per step
+        self.use_graph = bool(cuda_graph) and self.device.type == "cuda"
+        self._graph = None
+        self._graph_key = None
+        self._graph_warmup = graph_warmup_steps
+        self._capture_stream = None
+        self._eager_steps = 0
         if cfg.gradient_checkpointing and hasattr(model, "gradient_checkpointing_enable"):
             model.gradient_checkpointing_enable()
         model.train()
@@ -61,26 +71,96 @@ class Trainer:
         """`micro_batches`: one dict or a list of dicts with `input_ids` and `labels` `[B, S]` (int64)."""
         if isinstance(micro_batches, dict):
             micro_batches = [micro_batches]
-        n = len(micro_batches)
-        eng = self.engine
-        eng.zero_grad()
+        if self.use_graph and self._eager_steps >= self._graph_warmup:
+            return self._graph_step(micro_batches)
+        self._eager_steps += 1
+        lr = self.current_lr()
+        out, tokens = self._forward_backward([{k: self._to_device(v) for k, v in mb.items()} for mb in micro_batches])
+        gn = self.engine.step(lr)
+        self.global_step += 1
+        return self._result(out, gn, lr, tokens)
+
+    def _forward_backward(self, dev_batches):
+        n = len(dev_batches)
+        self.engine.zero_grad()
         scale = 1.0 / n
-        out = None
-        tokens = 0
-        for mb in micro_batches:
-            ids = self._to_device(mb["input_ids"])
-            labels = self._to_device(mb["labels"])
+        out, tokens = None, 0
+        for mb in dev_batches:
+            ids, labels = mb["input_ids"], mb["labels"]
             tokens += ids.numel()
             kw = {"output_router_logits": True} if self.is_moe else {}
             out = self.model(input_ids=ids, labels=labels, loss_scale=scale, **kw)
             loss = out.loss * scale if n > 1 else out.loss
             loss.backward()
-        lr = self.current_lr()
-        gn = eng.step(lr)
-        self.global_step += 1
+        return out, tokens
+
+    def _result(self, out, gn, lr, tokens) -> StepResult:
         return StepResult(loss=out.loss.detach(), ce_loss=_d(out.ce_loss), aux_loss=_d(out.aux_loss),
-                          seq_aux_loss=_d(out.seq_aux_loss), grad_norm=gn, lr=lr, router_logits=out.router_logits,
+                          seq_aux_loss=_d(out.seq_aux_loss), grad_norm=gn, lr=lr,
+                          router_logits=None if out.router_logits is None else tuple(t.detach() for t in out.router_logits),
                           tokens=tokens * self.world)
+
+    def _graph_step(self, micro_batches) -> StepResult:
+        key = tuple((tuple(mb["input_ids"].shape), tuple(mb["labels"].shape)) for mb in micro_batches)
+        if self._graph is None or key != self._graph_key:
+            self._capture(micro_batches, key)
+        for st, mb in zip(self._static_in, micro_batches):
+            st["input_ids"].copy_(mb["input_ids"], non_blocking=True)
+            st["labels"].copy_(mb["labels"], non_blocking=True)
+        lr = self.current_lr()
+        self.engine.set_hyper(lr)
+        self._graph.replay()
+        _ext.add_launches(self._graph_launches)
+        self.engine.step_count += 1
+        self.global_step += 1
+        out, gn, tokens = self._static_out
+        return self._result(out, gn, lr, tokens)
+
+    def _capture(self, micro_batches, key) -> None:
+        self._graph = None
+        self._static_in = [{"input_ids": torch.empty_like(mb["input_ids"], device=self.device),
+                            "labels": torch.empty_like(mb["labels"], device=self.device)} for mb in micro_batches]
+        for st, mb in zip(self._static_in, micro_batches):  # valid token ids while capturing
+            st["input_ids"].copy_(mb["input_ids"])
+            st["labels"].copy_(mb["labels"])
+        # Libraries keep lazily created per-stream state (workspaces, handles); creating it inside a
+        # capture invalidates the capture.  So run one forward/backward on the capture stream first.
+        # That dry run must leave no trace: gradients are reset by the step's own zero_grad, router
+        # token counters are put back.
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device=self.device)
+        cs = self._capture_stream
+        counters = [b for n, b in self.model.named_buffers() if n.endswith("local_tokens_per_expert")]
+        saved = [c.clone() for c in counters]
+        cs.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(cs):
+            self._forward_backward(self._static_in)
+            for c, sv in zip(counters, saved):
+                c.copy_(sv)
+        torch.cuda.current_stream(self.device).wait_stream(cs)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        l0 = _ext.launch_count()
+        # thread-local capture mode: NCCL's watchdog thread may touch CUDA while this thread captures
+        # no garbage collection while capturing: a collection could free tensors of earlier eager
+        # steps in the middle of the capture, and the allocator's bookkeeping for blocks that were
+        # used on other streams is not capturable
+        import gc
+
+        gc_was_on = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g, stream=cs, capture_error_mode="thread_local"):
+                out, tokens = self._forward_backward(self._static_in)
+                gn = self.engine.step(update_hyper=False, count=False)
+        finally:
+            if gc_was_on:
+                gc.enable()
+        self._graph, self._graph_key = g, key
+        self._graph_launches = _ext.launch_count() - l0  # kernels of ours inside one replay
+        _ext.add_launches(-self._graph_launches)  # capture itself ran nothing
+        self._static_out = (out, gn, tokens)
 
 
 def _d(t):

@@ -122,3 +122,33 @@ def test_gradient_checkpointing_same_grads():
         assert relerr(p.grad, q.grad) < 1e-3, n
     for ra, rb in zip(a.routers(), b.routers()):
         assert torch.equal(ra.local_tokens_per_expert, rb.local_tokens_per_expert)
+
+
+def test_cuda_graph_step_matches_eager():
+    from moe_b200.models import build_model
+    from moe_b200.ops import gemm as G
+    from moe_b200.trainer import Trainer
+    from moe_b200.utils.training import TrainingConfig
+
+    tcfg = TrainingConfig(learning_rate=2e-3, warmup_steps=3, max_steps=20, batch_size=2, gradient_accumulation=1)
+    torch.manual_seed(0)
+    batches = [torch.randint(0, 2048, (2, 128)) for _ in range(7)]
+    runs = []
+    for graph in (False, True):
+        model, _ = build_model(tiny_cfg("deepseek_global_moe"), seed=1, device="cuda")
+        tr = Trainer(model, tcfg, cuda_graph=graph)
+        losses = []
+        for b in batches:
+            r = tr.train_step({"input_ids": b.pin_memory(), "labels": b})
+            losses.append(r.loss.item())
+        torch.cuda.synchronize()
+        G.check_status()
+        runs.append((losses, [p.detach().clone() for p in model.parameters()],
+                     [r.local_tokens_per_expert.clone() for r in model.routers()]))
+        assert (tr._graph is not None) == graph
+    for a, b in zip(runs[0][0], runs[1][0]):
+        assert abs(a - b) < 2e-2 * abs(a), (runs[0][0], runs[1][0])
+    for p, q in zip(runs[0][1], runs[1][1]):
+        assert relerr(q, p) < 2e-2
+    for c, d in zip(runs[0][2], runs[1][2]):
+        assert c.sum() == d.sum() == 7 * 2 * 128 * 2

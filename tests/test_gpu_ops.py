@@ -247,7 +247,8 @@ def test_adamw_and_norm(dev):
     for step in (1, 2, 3):
         e.sumsq(g, scratch, ss, False)
         e.clip_coef(ss, 1.0, coef)
-        e.adamw(p, g, m, v, p16, 1e-3, 0.9, 0.95, 1e-8, 0.1, step, coef)
+        hyper = torch.tensor([1e-3, 1 - 0.9 ** step, 1 - 0.95 ** step], device=dev)
+        e.adamw(p, g, m, v, p16, hyper, 0.9, 0.95, 1e-8, 0.1, coef)
         c = min(1.0, 1.0 / (g.norm().item() + 1e-6))
         oracle.adamw_step_(p2, g, m2, v2, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step,
                            grad_scale=c)
