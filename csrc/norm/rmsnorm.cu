@@ -212,3 +212,66 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const float* rstd
   colsum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_part, dw_out, grid, H, dw_accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// --------------------------------------------------------------------------------------------
+// Allocation-free variant of the backward pass (declared and documented in rmsnorm_noalloc.h).
+// The per-block partial sums live in a file-scope device array instead of caller memory.
+#include "rmsnorm_noalloc.h"
+
+namespace b200 {
+static __device__ __align__(256) float g_noalloc_dw_scratch[B200_NOALLOC_MAX_BLOCKS * B200_NOALLOC_MAX_H];
+}
+
+// In host code the array's name is only a handle: the device address has to be asked for, once per
+// device and with that device current.
+static float* noalloc_scratch_for_current_device() {
+  constexpr int kMaxDevices = 64;
+  static float* cache[kMaxDevices] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (cache[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), b200::g_noalloc_dw_scratch) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    cache[dev] = p;
+  }
+  return cache[dev];
+}
+
+extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float* rstd, const float* w,
+                                        const void* dres, void* dx, float* dw_out, int dw_accumulate, int T, int H,
+                                        cudaStream_t stream) {
+  if (T < 0 || H <= 0 || H % 8 != 0 || H > B200_NOALLOC_MAX_H) return B200_NOALLOC_ERR_SIZE;
+  if (T == 0) return B200_NOALLOC_OK;
+  if (!dy || !x || !rstd || !w || !dx || !dw_out) return B200_NOALLOC_ERR_ARG;
+  float* scratch = noalloc_scratch_for_current_device();
+  if (scratch == nullptr) return B200_NOALLOC_ERR_SETUP;
+  const int grid = b200_rmsnorm_bwd_blocks(T);  // <= B200_NOALLOC_MAX_BLOCKS; rows [0, grid) are rewritten below
+  const size_t smem = static_cast<size_t>(NORM_WARPS) * H * sizeof(float);  // <= 32 KiB for H <= 2048
+  const int nch32 = (H / 8 + 31) / 32;
+#define LAUNCH(MC)                                                                                               \
+  rmsnorm_bwd_kernel<MC><<<grid, NORM_WARPS * 32, smem, stream>>>(                                               \
+      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x), rstd, w,            \
+      reinterpret_cast<const __nv_bfloat16*>(dres), reinterpret_cast<__nv_bfloat16*>(dx), scratch, T, H)
+  if (nch32 <= 1) LAUNCH(1);
+  else if (nch32 <= 2) LAUNCH(2);
+  else if (nch32 <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
+  colsum_kernel<<<(H + 31) / 32, 256, 0, stream>>>(scratch, dw_out, grid, H, dw_accumulate);
+  return cudaGetLastError() == cudaSuccess ? B200_NOALLOC_OK : B200_NOALLOC_ERR_LAUNCH;
+}
+
+extern "C" const char* b200_rmsnorm_bwd_noalloc_strerror(int code) {
+  switch (code) {
+    case B200_NOALLOC_OK: return "ok";
+    case B200_NOALLOC_ERR_SIZE:
+      return "size not supported: H must be a positive multiple of 8 and at most 2048 (B200_NOALLOC_MAX_H), T >= 0";
+    case B200_NOALLOC_ERR_SETUP: return "could not obtain the device address of the built-in scratch array";
+    case B200_NOALLOC_ERR_LAUNCH: return "a kernel launch was refused by the CUDA runtime";
+    case B200_NOALLOC_ERR_ARG: return "a required pointer argument is null";
+    default: return "unknown code";
+  }
+}
