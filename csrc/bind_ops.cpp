@@ -6,6 +6,8 @@
 
 #include "ops_api.h"
 
+#include <vector>
+
 namespace {
 
 using torch::Tensor;
@@ -205,9 +207,39 @@ void cast_bf16(const Tensor& src, Tensor& dst) {
   rc_ok(b200_cast_bf16(src.data_ptr<float>(), dst.data_ptr(), src.numel(), stream()), "cast_bf16");
 }
 
+// --------------------------------------------------------------------- comm
+void allreduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>& flags, const std::vector<int64_t>& norms,
+               int64_t mc_buf, int64_t rank, int64_t world, int64_t off, int64_t n, double scale,
+               const Tensor& epoch_base, int64_t epoch_off, bool final_bucket, bool use_multimem, int64_t blocks,
+               Tensor& state_i, Tensor& state_f, Tensor& status, int64_t limit_ns) {
+  i32c(epoch_base, "epoch_base"); i32c(state_i, "state_i"); f32c(state_f, "state_f"); i32c(status, "status");
+  need((int64_t)bufs.size() >= world && (int64_t)flags.size() >= world && (int64_t)norms.size() >= world,
+       "peer pointer lists shorter than world");
+  c10::cuda::CUDAGuard g(status.device());
+  B200Peers p;
+  for (int r = 0; r < B200_MAX_RANKS; ++r) {
+    p.buf[r] = r < world ? reinterpret_cast<void*>(bufs[r]) : nullptr;
+    p.flags[r] = r < world ? reinterpret_cast<void*>(flags[r]) : nullptr;
+    p.norm[r] = r < world ? reinterpret_cast<void*>(norms[r]) : nullptr;
+  }
+  p.mc_buf = reinterpret_cast<void*>(mc_buf);
+  rc_ok(b200_allreduce(&p, (int)rank, (int)world, off, n, (float)scale, epoch_base.data_ptr<int>(), (int)epoch_off,
+                       final_bucket ? 1 : 0, use_multimem ? 1 : 0, (int)blocks, state_i.data_ptr<int>(),
+                       state_f.data_ptr<float>(), status.data_ptr<int>(), (unsigned long long)limit_ns, stream()),
+        "allreduce");
+}
+void clip_coef_multi(const Tensor& parts, int64_t world, double max_norm, Tensor& coef) {
+  f32c(parts, "parts"); f32c(coef, "coef");
+  c10::cuda::CUDAGuard g(parts.device());
+  rc_ok(b200_clip_coef_multi(parts.data_ptr<float>(), (int)world, (float)max_norm, coef.data_ptr<float>(), stream()),
+        "clip_coef_multi");
+}
+
 }  // namespace
 
 void bind_ops(pybind11::module_& m) {
+  m.def("allreduce", &allreduce);
+  m.def("clip_coef_multi", &clip_coef_multi);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd_blocks", &rmsnorm_bwd_blocks);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

@@ -1,0 +1,173 @@
+// Gradient all-reduce over NVLink peer memory, fused with the data-parallel average and with the
+// squared-norm partials that gradient clipping needs.
+//
+// Every rank's flat fp32 gradient buffer lives in symmetric memory (all ranks have every peer's
+// buffer mapped).  One launch per bucket:
+//   1. arrive barrier : flag words in the peers' signal area tell everybody that this rank's
+//                       gradients for the bucket are complete (they were written by earlier kernels
+//                       on the same stream);
+//   2. two-shot reduce: rank r owns slice r of the bucket: it loads that slice from every peer
+//                       (plain peer loads, or one multimem.ld_reduce through the NVSwitch), scales
+//                       by 1/world, accumulates sum(v^2), and stores the result into every rank's
+//                       buffer (peer stores, or one multimem.st);
+//   3. done barrier   : the last block to finish posts "done" to all peers and waits for theirs, so
+//                       kernel completion on this stream means the whole bucket is final locally.
+// All waits are bounded; a wait that runs out records ST_TIMEOUT_PEER and the kernel returns.
+// No TMA is involved: cross-GPU traffic is ordinary ld/st (or multimem) from inside the kernel.
+#include "../common/ptx.cuh"
+#include "../ops_api.h"
+
+namespace b200 {
+
+constexpr int AR_THREADS = 512;
+
+struct ArPeers {
+  float* buf[B200_MAX_RANKS];   // flat gradient buffers (same layout on every rank)
+  int* flags[B200_MAX_RANKS];   // int[2 * B200_MAX_RANKS] per rank: arrive[src], done[src]
+  float* norm[B200_MAX_RANKS];  // float[B200_MAX_RANKS] per rank: squared-norm partial of each source rank
+};
+
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_peer_f4(float* p, float4 v) {
+  asm volatile("st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
+}
+
+// state: local scratch, int[2] + float[2]: {blocks finished, unused} / {this bucket's sum, running sum of the step}
+template <bool MULTIMEM>
+__global__ void __launch_bounds__(AR_THREADS)
+allreduce_kernel(ArPeers peers, float* mc_buf, int rank, int world, long long off, long long n, float scale,
+                 const int* epoch_base, int epoch_off, int final_bucket, int* state_i, float* state_f, int* status,
+                 unsigned long long limit_ns) {
+  __shared__ float sh[AR_THREADS / 32];
+  __shared__ int sh_ok;
+  int* my_flags = peers.flags[rank];
+  // epochs grow monotonically; the base lives in device memory so that a captured graph can be replayed
+  const int epoch = *epoch_base + epoch_off;
+  // ---- 1. arrive
+  if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + rank, epoch);
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < world && ok; ++r) ok = wait_flag_ge(my_flags + r, epoch, limit_ns) ? 1 : 0;
+    sh_ok = ok;
+  }
+  __syncthreads();
+  float ss = 0.f;
+  if (sh_ok) {
+    // ---- 2. reduce my slice, publish it everywhere
+    const long long n4 = n >> 2;  // bucket sizes are multiples of 4 floats
+    const long long per = (n4 + world - 1) / world;
+    const long long lo = per * rank, hi = (lo + per < n4) ? lo + per : n4;
+    for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < hi;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long e = off + (i << 2);
+      float4 acc;
+      if constexpr (MULTIMEM) {
+        acc = multimem_ld_reduce_f4(mc_buf + e);
+      } else {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < world; ++r) {
+          const float4 v = ld_peer_f4(peers.buf[(rank + r) % world] + e);  // stagger the peers
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+      }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+      if constexpr (MULTIMEM) {
+        multimem_st_f4(mc_buf + e, acc);
+      } else {
+        for (int r = 0; r < world; ++r) st_peer_f4(peers.buf[(rank + r) % world] + e, acc);
+      }
+    }
+  } else if (threadIdx.x == 0) {
+    report(status, ST_TIMEOUT_PEER);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  // ---- 3. done: last block of this rank posts and waits
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < AR_THREADS / 32; ++i) s += sh[i];
+    atomicAdd(&state_f[0], s);
+    __threadfence_system();
+    const int ticket = atomicAdd(&state_i[0], 1);
+    if (ticket == static_cast<int>(gridDim.x) - 1) {
+      __threadfence();
+      const float bucket = atomicExch(&state_f[0], 0.f);
+      const float total = state_f[1] + bucket;
+      state_f[1] = final_bucket ? 0.f : total;
+      state_i[0] = 0;
+      if (final_bucket)
+        for (int r = 0; r < world; ++r) peers.norm[r][rank] = total;  // peer store of this rank's partial
+      __threadfence_system();
+      for (int r = 0; r < world; ++r) st_release_sys(peers.flags[r] + B200_MAX_RANKS + rank, epoch);
+      bool ok = true;
+      for (int r = 0; r < world && ok; ++r) ok = wait_flag_ge(my_flags + B200_MAX_RANKS + r, epoch, limit_ns);
+      if (!ok) report(status, ST_TIMEOUT_PEER);
+    }
+  }
+}
+
+// coef[0] = min(1, max_norm / (norm + 1e-6)), coef[1] = norm, norm^2 = sum of the ranks' partials
+__global__ void clip_coef_multi_kernel(const float* __restrict__ parts, int world, float max_norm,
+                                       float* __restrict__ coef) {
+  float s = 0.f;
+  for (int r = 0; r < world; ++r) s += parts[r];
+  const float norm = sqrtf(s);
+  coef[0] = max_norm > 0.f ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  coef[1] = norm;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long long n, float scale,
+                              const int* epoch_base, int epoch_off, int final_bucket, int use_multimem, int blocks, int* state_i, float* state_f,
+                              int* status, unsigned long long limit_ns, cudaStream_t stream) {
+  if (world < 1 || world > B200_MAX_RANKS || rank < 0 || rank >= world) return -1;
+  if (n <= 0) return 0;
+  if ((n & 3) != 0 || (off & 3) != 0) return -1;
+  if (use_multimem && p->mc_buf == nullptr) return -1;
+  ArPeers ap;
+  for (int r = 0; r < B200_MAX_RANKS; ++r) {
+    ap.buf[r] = reinterpret_cast<float*>(p->buf[r]);
+    ap.flags[r] = reinterpret_cast<int*>(p->flags[r]);
+    ap.norm[r] = reinterpret_cast<float*>(p->norm[r]);
+  }
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148) blocks = 148;
+  if (limit_ns == 0) limit_ns = 10000000000ull;  // ten seconds: peers may be busy with compute
+  float* mc = reinterpret_cast<float*>(p->mc_buf);
+  if (use_multimem)
+    allreduce_kernel<true><<<blocks, AR_THREADS, 0, stream>>>(ap, mc, rank, world, off, n, scale, epoch_base, epoch_off,
+                                                               final_bucket,
+                                                               state_i, state_f, status, limit_ns);
+  else
+    allreduce_kernel<false><<<blocks, AR_THREADS, 0, stream>>>(ap, mc, rank, world, off, n, scale, epoch_base, epoch_off,
+                                                               final_bucket,
+                                                                state_i, state_f, status, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_clip_coef_multi(const float* parts, int world, float max_norm, float* coef, cudaStream_t stream) {
+  clip_coef_multi_kernel<<<1, 1, 0, stream>>>(parts, world, max_norm, coef);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

@@ -204,6 +204,11 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int target, uint64_t 
   return true;
 }
 
+// first non-zero status wins
+__device__ __forceinline__ void report(int* status, int code) {
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
 // ------------------------------------------------------------ small helpers
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

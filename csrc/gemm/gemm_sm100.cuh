@@ -88,10 +88,6 @@ __device__ __forceinline__ void decode_tile(const GemmArgs& a, int t, int m_tile
   }
 }
 
-__device__ __forceinline__ void report(int* status, int code) {
-  if (status != nullptr) atomicCAS(status, 0, code);
-}
-
 __device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>

@@ -59,6 +59,22 @@ int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long lon
                float beta2, float eps, float wd, const float* grad_coef, cudaStream_t stream);
 int b200_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 
+// ---- comm/allreduce.cu
+#define B200_MAX_RANKS 8
+typedef struct B200Peers {
+  void* buf[B200_MAX_RANKS];    // every rank's flat fp32 gradient buffer (symmetric memory)
+  void* flags[B200_MAX_RANKS];  // every rank's int[2 * B200_MAX_RANKS] flag words, zero-initialised
+  void* norm[B200_MAX_RANKS];   // every rank's float[B200_MAX_RANKS] squared-norm slots
+  void* mc_buf;                 // NVSwitch multicast address of the gradient buffers, or null
+} B200Peers;
+// One bucket [off, off+n) of the gradient buffer: average over ranks in place on every rank.
+// epoch = *epoch_base + epoch_off must grow with every launch and agree across ranks.
+// state_i: int[2], state_f: float[2], both zero-initialised local scratch.
+int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long long n, float scale,
+                   const int* epoch_base, int epoch_off, int final_bucket, int use_multimem, int blocks, int* state_i,
+                   float* state_f, int* status, unsigned long long limit_ns, cudaStream_t stream);
+int b200_clip_coef_multi(const float* parts, int world, float max_norm, float* coef, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,6 +16,7 @@ On CPU the same class runs with plain torch ops (gloo for the all-reduce).
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -60,7 +61,8 @@ class _LayerBoundary(torch.autograd.Function):
 class TrainEngine:
     def __init__(self, model: nn.Module, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, process_group=None,
-                 overlap_grad_reduce: bool = True, device: torch.device | str | None = None):
+                 overlap_grad_reduce: bool = True, device: torch.device | str | None = None,
+                 comm: str | None = None):
         self.model = model
         self.lr, self.betas, self.eps = lr, betas, eps
         self.weight_decay, self.max_grad_norm = weight_decay, max_grad_norm
@@ -90,8 +92,19 @@ class TrainEngine:
         self.slots = slots
         self.by_name = {s.name: s for s in slots}
         dev = self.device
+        # gradient reduction: "p2p" = own NVLink kernel over symmetric memory (fused average + norm
+        # partials), "nccl" = library all-reduce.  Default: p2p on CUDA with up to 8 ranks.
+        comm = comm or os.environ.get("MOE_B200_COMM") or ("p2p" if self.cuda and 1 < self.world <= 8 else "nccl")
+        self.comm = comm if (self.cuda and self.world > 1) else "none"
         self.p32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
-        self.g32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self._peers = None
+        if self.comm == "p2p":
+            from .symm import PeerBuffers
+
+            self._peers = PeerBuffers(self.total, dev, process_group)
+            self.g32 = self._peers.grad
+        else:
+            self.g32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
         self.m = torch.zeros(self.total, dtype=torch.float32, device=dev)
         self.v = torch.zeros(self.total, dtype=torch.float32, device=dev)
         self.p16 = torch.zeros(self.total, dtype=torch.bfloat16, device=dev) if self.cuda else None
@@ -120,6 +133,14 @@ class TrainEngine:
             self._fuse_adjacent()
             self.refresh_compute_copy()
             self._comm_stream = torch.cuda.Stream(device=dev) if self.world > 1 else None
+            self._fused_ar = None
+            if self._peers is not None:
+                from ..ops import gemm as _G
+                from .symm import FusedAllReduce
+
+                pb = self._peers
+                self._fused_ar = FusedAllReduce(self._ext, pb.grad_ptrs, pb.flag_ptrs, pb.norm_ptrs, pb.multicast_ptr,
+                                                pb.rank, pb.world, dev, _G.status_word(dev))
         self._layer_offs = self.layer_offsets()
         inner = getattr(self.model, "model", None)
         if inner is not None and hasattr(inner, "_boundary_fn"):
@@ -190,12 +211,18 @@ class TrainEngine:
             self._launch_reduce(first_offset, hi)
             self._reduced_upto = first_offset
 
-    def _launch_reduce(self, lo: int, hi: int) -> None:
+    def _launch_reduce(self, lo: int, hi: int, final: bool = False) -> None:
         if self.world == 1 or hi <= lo:
             return
         self._zero_dead(lo, hi)
         chunk = self.g32[lo:hi]
-        if self.cuda:
+        if self.cuda and self._fused_ar is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ev)
+                self._fused_ar.reduce(lo, hi - lo, final)
+        elif self.cuda:
             ev = torch.cuda.Event()
             ev.record()
             with torch.cuda.stream(self._comm_stream):
@@ -251,14 +278,19 @@ class TrainEngine:
             return
         # the undecayed tail (norm weights) and anything below the last boundary
         hi = min(self._reduced_upto, self.decay_end)
-        self._launch_reduce(0, hi)
-        self._launch_reduce(self.decay_end, self.total)
+        tail = self.total > self.decay_end
+        self._launch_reduce(0, hi, final=not tail)
+        self._launch_reduce(self.decay_end, self.total, final=True)
+        if self._fused_ar is not None and hi <= 0 and not tail:
+            raise RuntimeError("no final gradient bucket was launched")
         self._reduced_upto = 0
         for w in self._pending:
             w.wait()
         self._pending = []
         if self.cuda and self._comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
+        if self.cuda and self._fused_ar is not None:
+            self._fused_ar.end_step()
 
     def set_hyper(self, lr: float | None = None) -> None:
         """Stage the learning rate and Adam bias corrections of the NEXT step on the device."""
@@ -285,8 +317,11 @@ class TrainEngine:
         b1, b2 = self.betas
         if self.cuda:
             e = self._ext
-            e.sumsq(self.g32, self._ss_scratch, self._norm_ss, False)
-            e.clip_coef(self._norm_ss, float(self.max_grad_norm or 0.0), self._coef)
+            if self._fused_ar is not None:  # the reduce kernels already produced every rank's sum of squares
+                e.clip_coef_multi(self._peers.norm, self.world, float(self.max_grad_norm or 0.0), self._coef)
+            else:
+                e.sumsq(self.g32, self._ss_scratch, self._norm_ss, False)
+                e.clip_coef(self._norm_ss, float(self.max_grad_norm or 0.0), self._coef)
             d = self.decay_end
             if d > 0:
                 e.adamw(self.p32[:d], self.g32[:d], self.m[:d], self.v[:d], self.p16[:d], self._hyper, b1, b2, self.eps,

@@ -1,0 +1,77 @@
+"""Symmetric (peer-mapped) buffers for the NVLink kernels, and the fused gradient all-reduce.
+
+Each rank allocates the same buffers through `torch.distributed._symmetric_memory`; after the
+rendezvous every rank holds device pointers to every peer's copy (and, on NVSwitch systems, one
+multicast address that fans a store out to all ranks and reduces a load across them).  The kernels
+in `csrc/comm` use those pointers with ordinary peer loads / stores or `multimem` instructions;
+nothing here goes through TMA.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+MAX_RANKS = 8
+
+
+class PeerBuffers:
+    """Three symmetric allocations: the flat fp32 gradient buffer, flag words, squared-norm slots."""
+
+    def __init__(self, numel: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as sm
+
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > MAX_RANKS:
+            raise ValueError(f"the peer-memory kernels support at most {MAX_RANKS} ranks (one NVLink domain)")
+        self.grad = sm.empty(numel, dtype=torch.float32, device=device)
+        self.flags = sm.empty(2 * MAX_RANKS, dtype=torch.int32, device=device)
+        self.norm = sm.empty(MAX_RANKS, dtype=torch.float32, device=device)
+        for t in (self.grad, self.flags, self.norm):
+            t.zero_()
+        torch.cuda.synchronize(device)
+        hg = sm.rendezvous(self.grad, group)
+        hf = sm.rendezvous(self.flags, group)
+        hn = sm.rendezvous(self.norm, group)
+        self._handles = (hg, hf, hn)
+        self.grad_ptrs = [int(p) for p in hg.buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in hf.buffer_ptrs]
+        self.norm_ptrs = [int(p) for p in hn.buffer_ptrs]
+        mc = 0
+        try:
+            if hg.has_multicast_support(device.type, device.index if device.index is not None else 0):
+                mc = int(hg.multicast_ptr)
+        except Exception:
+            mc = int(getattr(hg, "multicast_ptr", 0) or 0)
+        # NVLS only on request to opt out: MOE_B200_MULTIMEM=0 forces plain peer loads / stores
+        self.multicast_ptr = mc if os.environ.get("MOE_B200_MULTIMEM", "1") != "0" else 0
+        dist.barrier(group)
+
+
+class FusedAllReduce:
+    """Launches `csrc/comm/allreduce.cu` on slices of a flat gradient buffer (see that file)."""
+
+    def __init__(self, ext, grad_ptrs, flag_ptrs, norm_ptrs, multicast_ptr, rank, world, device, status,
+                 blocks: int = 32, limit_ns: int = 0):
+        self.ext, self.rank, self.world = ext, rank, world
+        self.grad_ptrs, self.flag_ptrs, self.norm_ptrs, self.mc = grad_ptrs, flag_ptrs, norm_ptrs, multicast_ptr
+        self.state_i = torch.zeros(2, dtype=torch.int32, device=device)
+        self.state_f = torch.zeros(2, dtype=torch.float32, device=device)
+        self.epoch_base = torch.ones(1, dtype=torch.int32, device=device)
+        self.status = status
+        self.blocks, self.limit_ns = blocks, limit_ns
+        self.launched = 0  # buckets since the last `end_step`
+
+    def reduce(self, off: int, n: int, final_bucket: bool) -> None:
+        self.ext.allreduce(self.grad_ptrs, self.flag_ptrs, self.norm_ptrs, self.mc, self.rank, self.world, off, n,
+                           1.0 / self.world, self.epoch_base, self.launched, final_bucket, self.mc != 0,
+                           self.blocks, self.state_i, self.state_f, self.status, self.limit_ns)
+        self.launched += 1
+
+    def end_step(self) -> None:
+        """Advance the epoch base on the device (captured by a CUDA graph, so replays keep counting)."""
+        if self.launched:
+            self.epoch_base.add_(self.launched)
+            self.launched = 0

@@ -1,0 +1,128 @@
+"""NVLink gradient all-reduce kernel.
+
+With one GPU the ranks are emulated inside one process: `world` buffers on the same device, flag
+words pre-set so that every wait is already satisfied, and the ranks' kernels run one after the
+other (rank r only rewrites slice r, so the order does not matter).  A wait that can never be
+satisfied (a flag nobody sets) must end as a status code with the context intact.  With two or
+more GPUs, real ranks are spawned and the fused path is compared with NCCL and with a single
+process run."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _emulated(world, n, flags_value):
+    from moe_b200.ops import _ext
+    from moe_b200.ops import gemm as G
+
+    e = _ext.load()
+    dev = torch.device("cuda")
+    bufs = [torch.randn(n, device=dev) for _ in range(world)]
+    flags = [torch.full((16,), flags_value, dtype=torch.int32, device=dev) for _ in range(world)]
+    norms = [torch.zeros(8, device=dev) for _ in range(world)]
+    st = G.status_word(dev)
+    return e, bufs, flags, norms, st
+
+
+@pytest.mark.parametrize("world,n", [(2, 4096), (4, 1_000_000), (8, 12_345_676)])
+def test_allreduce_emulated_ranks(world, n):
+    from moe_b200.ops import gemm as G
+
+    e, bufs, flags, norms, st = _emulated(world, n, flags_value=1 << 20)
+    ref = torch.stack(bufs).sum(0) / world
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    for r in range(world):
+        si, sf = torch.zeros(2, dtype=torch.int32, device="cuda"), torch.zeros(2, device="cuda")
+        half = (n // 2) // 4 * 4
+        for (off, cnt, final) in ((0, half, False), (half, n - half, True)):  # two buckets per step
+            e.allreduce([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], [x.data_ptr() for x in norms], 0,
+                        r, world, off, cnt, 1.0 / world, epoch, 0, final, False, 16, si, sf, st, 0)
+    torch.cuda.synchronize()
+    G.check_status()
+    for b in bufs:
+        assert torch.allclose(b, ref, atol=1e-6)
+    total = sum(float(norms[0][r]) for r in range(world))
+    assert abs(total - float(ref.double().pow(2).sum())) < 1e-3 * total
+    for x in norms[1:]:
+        assert torch.equal(x, norms[0])
+    coef = torch.zeros(2, device="cuda")
+    e.clip_coef_multi(norms[0], world, 1.0, coef)
+    assert abs(float(coef[1]) - float(ref.norm())) < 1e-3 * float(ref.norm())
+
+
+def test_wait_that_nobody_satisfies_becomes_a_status_code():
+    from moe_b200.ops import gemm as G
+
+    e, bufs, flags, norms, st = _emulated(2, 4096, flags_value=0)  # rank 1 never shows up
+    before = bufs[0].clone()
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")
+    si, sf = torch.zeros(2, dtype=torch.int32, device="cuda"), torch.zeros(2, device="cuda")
+    e.allreduce([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], [x.data_ptr() for x in norms], 0, 0, 2, 0,
+                4096, 0.5, epoch, 0, True, False, 4, si, sf, st, 50_000_000)  # 50 ms limit
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="peer wait"):
+        G.check_status()
+    assert torch.equal(bufs[0], before)  # gave up before touching the data
+    y = torch.ones(4, device="cuda") * 2  # the context is still usable
+    assert float(y.sum()) == 8.0
+    G.check_status()  # the word was cleared
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ddp_rank(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from test_gpu_model import tiny_cfg
+    from moe_b200.models import build_model
+    from moe_b200.ops import gemm as G
+    from moe_b200.parallel.engine import TrainEngine
+
+    g = torch.Generator().manual_seed(0)
+    full = [torch.randint(0, 2048, (4, 128), generator=g) for _ in range(3)]
+    res = {}
+    for comm, overlap in (("nccl", False), ("p2p", False), ("p2p", True)):
+        model, _ = build_model(tiny_cfg("dense"), seed=3, device=f"cuda:{rank}")
+        eng = TrainEngine(model, lr=1e-3, comm=comm, overlap_grad_reduce=overlap)
+        for b in full:
+            mine = b[rank * 2:(rank + 1) * 2].cuda()
+            eng.zero_grad()
+            model(input_ids=mine, labels=mine).loss.backward()
+            gn = eng.step()
+        torch.cuda.synchronize()
+        G.check_status()
+        res[(comm, overlap)] = (eng.p32.clone().cpu(), float(gn))
+        dist.barrier()
+    torch.save(res, os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_fused_allreduce_matches_nccl(tmp_path):
+    import torch.multiprocessing as mp
+
+    mp.spawn(_ddp_rank, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    a, b = torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt")
+    for key in a:
+        assert torch.equal(a[key][0], b[key][0]), key  # ranks agree bit for bit
+    ref, gn = a[("nccl", False)]
+    for key in (("p2p", False), ("p2p", True)):
+        d = (a[key][0] - ref).abs()
+        assert d.max() < 5e-3 and (d > 1e-4).float().mean() < 1e-2, key
+        assert abs(a[key][1] - gn) < 2e-2 * gn
