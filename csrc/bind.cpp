@@ -6,6 +6,9 @@
 #include "gemm/gemm_api.h"
 #include "ops_api.h"
 
+#include <cstring>
+#include <vector>
+
 namespace {
 
 using torch::Tensor;
@@ -27,13 +30,18 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
              int64_t a_inner, int64_t a_rows, const Tensor& B, int64_t ldb, int64_t b_expert_stride, int64_t b_inner,
              int64_t b_rows, int64_t b_experts, const OptT& tile_expert, const OptT& num_m_tiles,
              const OptT& seg_off, const Tensor& C, int64_t ldc, int64_t c_expert_stride, const OptT& aux0,
-             int64_t ld_aux0, const OptT& aux1, int64_t ld_aux1, const Tensor& status) {
+             int64_t ld_aux0, const OptT& aux1, int64_t ld_aux1, const Tensor& status, const OptT& ep_wait_flags,
+             int64_t ep_wait_n, const OptT& ep_epoch_base, int64_t ep_wait_epoch_off,
+             const std::vector<int64_t>& ep_scatter_dst, const OptT& ep_scatter_meta,
+             const std::vector<int64_t>& ep_post_flags, int64_t ep_post_index, int64_t ep_post_epoch_off,
+             int64_t ep_world, const OptT& ep_counter) {
   check_cuda(A, "A");
   check_cuda(B, "B");
   check_cuda(C, "C");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "A and B must be bf16");
   c10::cuda::CUDAGuard guard(A.device());
   B200GemmDesc d;
+  std::memset(&d, 0, sizeof(d));
   d.mode = (int)mode; d.epi = (int)epi; d.bn = (int)bn; d.a_mn = (int)a_mn; d.b_mn = (int)b_mn;
   d.M = (int)M; d.N = (int)N; d.K = (int)K;
   d.num_experts = (int)num_experts; d.m_fast = (int)m_fast; d.beta = (int)beta; d.n_half = (int)n_half;
@@ -47,6 +55,17 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
   d.aux0 = ptr_or_null<void>(aux0); d.ld_aux0 = ld_aux0;
   d.aux1 = ptr_or_null<void>(aux1); d.ld_aux1 = ld_aux1;
   d.status = reinterpret_cast<int*>(status.data_ptr());
+  d.ep_wait_flags = ptr_or_null<const int>(ep_wait_flags);
+  d.ep_wait_n = (int)ep_wait_n;
+  d.ep_epoch_base = ptr_or_null<const int>(ep_epoch_base);
+  d.ep_wait_epoch_off = (int)ep_wait_epoch_off;
+  for (size_t r = 0; r < ep_scatter_dst.size() && r < 8; ++r) d.ep_scatter_dst[r] = reinterpret_cast<void*>(ep_scatter_dst[r]);
+  d.ep_scatter_meta = ptr_or_null<const int>(ep_scatter_meta);
+  for (size_t r = 0; r < ep_post_flags.size() && r < 8; ++r) d.ep_post_flags[r] = reinterpret_cast<int*>(ep_post_flags[r]);
+  d.ep_post_index = (int)ep_post_index;
+  d.ep_post_epoch_off = (int)ep_post_epoch_off;
+  d.ep_world = (int)ep_world;
+  d.ep_counter = ptr_or_null<int>(ep_counter);
   const int rc = b200_gemm(&d, cur_stream());
   TORCH_CHECK(rc == 0, "b200_gemm failed with host code ", rc);
   return rc;
@@ -57,6 +76,17 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
 void bind_ops(pybind11::module_& m);  // bind_ops.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gemm", &gemm, "tcgen05 GEMM family (dense / grouped)");
+  namespace py = pybind11;
+  m.def("gemm", &gemm, "tcgen05 GEMM family (dense / grouped)", py::arg("mode"), py::arg("epi"), py::arg("bn"),
+        py::arg("a_mn"), py::arg("b_mn"), py::arg("M"), py::arg("N"), py::arg("K"), py::arg("num_experts"),
+        py::arg("m_fast"), py::arg("beta"), py::arg("n_half"), py::arg("A"), py::arg("lda"), py::arg("a_inner"),
+        py::arg("a_rows"), py::arg("B"), py::arg("ldb"), py::arg("b_expert_stride"), py::arg("b_inner"),
+        py::arg("b_rows"), py::arg("b_experts"), py::arg("tile_expert"), py::arg("num_m_tiles"), py::arg("seg_off"),
+        py::arg("C"), py::arg("ldc"), py::arg("c_expert_stride"), py::arg("aux0"), py::arg("ld_aux0"),
+        py::arg("aux1"), py::arg("ld_aux1"), py::arg("status"), py::arg("ep_wait_flags") = py::none(),
+        py::arg("ep_wait_n") = 0, py::arg("ep_epoch_base") = py::none(), py::arg("ep_wait_epoch_off") = 0,
+        py::arg("ep_scatter_dst") = std::vector<int64_t>(), py::arg("ep_scatter_meta") = py::none(),
+        py::arg("ep_post_flags") = std::vector<int64_t>(), py::arg("ep_post_index") = 0,
+        py::arg("ep_post_epoch_off") = 0, py::arg("ep_world") = 0, py::arg("ep_counter") = py::none());
   bind_ops(m);
 }

@@ -127,11 +127,53 @@ void moe_gather(const Tensor& x, const Tensor& row_slot, const Tensor& seg_off, 
   rc_ok(b200_moe_gather(x.data_ptr(), row_slot.data_ptr<int>(), seg_off.data_ptr<int>(), (int)E, (int)K,
                         (int)x.size(1), xs.data_ptr(), (int)xs.size(0), stream()), "moe_gather");
 }
-void moe_combine(const Tensor& ys, const Tensor& pos, const OptT& w, const OptT& res, Tensor& out, int64_t K) {
-  bf16c(ys, "ys"); i32c(pos, "pos"); bf16c(out, "out");
+void moe_combine(const Tensor& ys, const OptT& pos, const OptT& w, const OptT& res, Tensor& out, int64_t K,
+                 const OptT& wait_flags, int64_t wait_n, const OptT& epoch_base, int64_t epoch_off,
+                 const OptT& status) {
+  bf16c(ys, "ys"); bf16c(out, "out");
   c10::cuda::CUDAGuard g(ys.device());
-  rc_ok(b200_moe_combine(ys.data_ptr(), pos.data_ptr<int>(), optp<const float>(w), optp<const void>(res),
-                         (int)out.size(0), (int)K, (int)out.size(1), out.data_ptr(), stream()), "moe_combine");
+  rc_ok(b200_moe_combine(ys.data_ptr(), optp<const int>(pos), optp<const float>(w), optp<const void>(res),
+                         (int)out.size(0), (int)K, (int)out.size(1), out.data_ptr(), optp<const int>(wait_flags),
+                         (int)wait_n, optp<const int>(epoch_base), (int)epoch_off, optp<int>(status), stream()),
+        "moe_combine");
+}
+
+std::vector<void*> ptrs8(const std::vector<int64_t>& v) {
+  std::vector<void*> p(B200_MAX_RANKS, nullptr);
+  for (size_t i = 0; i < v.size() && i < B200_MAX_RANKS; ++i) p[i] = reinterpret_cast<void*>(v[i]);
+  return p;
+}
+
+void ep_exchange(const Tensor& counts, const std::vector<int64_t>& cmat, const std::vector<int64_t>& flags,
+                 const Tensor& epoch_base, int64_t epoch_off, int64_t rank, int64_t world, int64_t E, int64_t H,
+                 Tensor& send_base, Tensor& recv_seg_off, Tensor& recv_tile_expert, Tensor& recv_num_m_tiles,
+                 Tensor& recv_buf, Tensor& recv_meta, Tensor& status) {
+  i32c(counts, "counts"); i32c(send_base, "send_base"); i32c(recv_seg_off, "recv_seg_off");
+  i32c(recv_tile_expert, "recv_tile_expert"); i32c(recv_num_m_tiles, "recv_num_m_tiles"); bf16c(recv_buf, "recv_buf");
+  i32c(recv_meta, "recv_meta"); i32c(epoch_base, "epoch_base");
+  c10::cuda::CUDAGuard g(counts.device());
+  auto cm = ptrs8(cmat), fl = ptrs8(flags);
+  rc_ok(b200_ep_exchange(counts.data_ptr<int>(), cm.data(), fl.data(), B200_EP_CH_COUNTS, epoch_base.data_ptr<int>(),
+                         (int)epoch_off, (int)rank, (int)world, (int)E, (int)H, (int)recv_buf.size(0),
+                         send_base.data_ptr<int>(), recv_seg_off.data_ptr<int>(), recv_tile_expert.data_ptr<int>(),
+                         recv_num_m_tiles.data_ptr<int>(), recv_buf.data_ptr(), recv_meta.data_ptr<int>(),
+                         status.data_ptr<int>(), 0, stream()), "ep_exchange");
+}
+
+void ep_dispatch(const Tensor& rows, const OptT& scale, const Tensor& idx, const Tensor& pos,
+                 const Tensor& local_seg_off, const Tensor& send_base, const std::vector<int64_t>& recv_buf,
+                 const std::vector<int64_t>& recv_meta, const std::vector<int64_t>& flags, const Tensor& epoch_base,
+                 int64_t epoch_off, int64_t rank, int64_t world, int64_t E, int64_t K, int64_t capacity,
+                 Tensor& counter) {
+  bf16c(rows, "rows"); i32c(idx, "idx"); i32c(pos, "pos"); i32c(local_seg_off, "local_seg_off");
+  i32c(send_base, "send_base"); i32c(epoch_base, "epoch_base"); i32c(counter, "counter");
+  c10::cuda::CUDAGuard g(rows.device());
+  auto rb = ptrs8(recv_buf), rm = ptrs8(recv_meta), fl = ptrs8(flags);
+  rc_ok(b200_ep_dispatch(rows.data_ptr(), optp<const float>(scale), idx.data_ptr<int>(), pos.data_ptr<int>(),
+                         local_seg_off.data_ptr<int>(), send_base.data_ptr<int>(), rb.data(), rm.data(), fl.data(),
+                         B200_EP_CH_DISPATCH, epoch_base.data_ptr<int>(), (int)epoch_off, (int)rank, (int)world, (int)E,
+                         (int)idx.numel(), (int)K, (int)rows.size(1), (int)capacity, counter.data_ptr<int>(), stream()),
+        "ep_dispatch");
 }
 void moe_combine_bwd(const Tensor& dout, const Tensor& ys, const Tensor& row_slot, const Tensor& seg_off,
                      const Tensor& w, int64_t E, int64_t K, Tensor& dys, Tensor& dw) {
@@ -239,6 +281,8 @@ void clip_coef_multi(const Tensor& parts, int64_t world, double max_norm, Tensor
 
 void bind_ops(pybind11::module_& m) {
   m.def("allreduce", &allreduce);
+  m.def("ep_exchange", &ep_exchange);
+  m.def("ep_dispatch", &ep_dispatch);
   m.def("clip_coef_multi", &clip_coef_multi);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd_blocks", &rmsnorm_bwd_blocks);

@@ -19,7 +19,8 @@
 
 namespace b200 {
 
-constexpr int AR_THREADS = 512;
+constexpr int AR_THREADS = 256;  // 256 x ~120 registers: fits next to a resident GEMM CTA on the same SM
+constexpr int AR_UNROLL = 2;
 
 struct ArPeers {
   float* buf[B200_MAX_RANKS];   // flat gradient buffers (same layout on every rank)
@@ -74,25 +75,65 @@ allreduce_kernel(ArPeers peers, float* mc_buf, int rank, int world, long long of
     const long long n4 = n >> 2;  // bucket sizes are multiples of 4 floats
     const long long per = (n4 + world - 1) / world;
     const long long lo = per * rank, hi = (lo + per < n4) ? lo + per : n4;
-    for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < hi;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-      const long long e = off + (i << 2);
-      float4 acc;
+    // AR_UNROLL independent 16-byte accesses per thread and peer are in flight at once: NVLink
+    // round trips take microseconds, so bandwidth comes from memory-level parallelism
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < hi;
+         i0 += stride * AR_UNROLL) {
+      float4 acc[AR_UNROLL];
+#pragma unroll
+      for (int u = 0; u < AR_UNROLL; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       if constexpr (MULTIMEM) {
-        acc = multimem_ld_reduce_f4(mc_buf + e);
+#pragma unroll
+        for (int u = 0; u < AR_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < hi) acc[u] = multimem_ld_reduce_f4(mc_buf + off + (i << 2));
+        }
       } else {
-        acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < world; ++r) {
-          const float4 v = ld_peer_f4(peers.buf[(rank + r) % world] + e);  // stagger the peers
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        // issue the loads of every peer before the first add, so that all of them are in flight together
+        float4 v[B200_MAX_RANKS][AR_UNROLL];
+#pragma unroll
+        for (int r = 0; r < B200_MAX_RANKS; ++r) {
+          if (r < world) {
+            const float* src = peers.buf[(rank + r) % world] + off;  // stagger the peers
+#pragma unroll
+            for (int u = 0; u < AR_UNROLL; ++u) {
+              const long long i = i0 + u * stride;
+              v[r][u] = i < hi ? ld_peer_f4(src + (i << 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < B200_MAX_RANKS; ++r) {
+          if (r < world) {
+#pragma unroll
+            for (int u = 0; u < AR_UNROLL; ++u) {
+              acc[u].x += v[r][u].x; acc[u].y += v[r][u].y; acc[u].z += v[r][u].z; acc[u].w += v[r][u].w;
+            }
+          }
         }
       }
-      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-      ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+#pragma unroll
+      for (int u = 0; u < AR_UNROLL; ++u) {
+        acc[u].x *= scale; acc[u].y *= scale; acc[u].z *= scale; acc[u].w *= scale;
+        const long long i = i0 + u * stride;
+        if (i < hi) ss += acc[u].x * acc[u].x + acc[u].y * acc[u].y + acc[u].z * acc[u].z + acc[u].w * acc[u].w;
+      }
       if constexpr (MULTIMEM) {
-        multimem_st_f4(mc_buf + e, acc);
+#pragma unroll
+        for (int u = 0; u < AR_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < hi) multimem_st_f4(mc_buf + off + (i << 2), acc[u]);
+        }
       } else {
-        for (int r = 0; r < world; ++r) st_peer_f4(peers.buf[(rank + r) % world] + e, acc);
+        for (int r = 0; r < world; ++r) {
+          float* dst = peers.buf[(rank + r) % world] + off;
+#pragma unroll
+          for (int u = 0; u < AR_UNROLL; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < hi) st_peer_f4(dst + (i << 2), acc[u]);
+          }
+        }
       }
     }
   } else if (threadIdx.x == 0) {

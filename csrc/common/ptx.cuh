@@ -23,7 +23,7 @@ enum : int {
 };
 
 #ifndef B200_WAIT_LIMIT_NS
-#define B200_WAIT_LIMIT_NS 2000000000ull  // two seconds
+#define B200_WAIT_LIMIT_NS 20000000000ull  // twenty seconds: longer than any peer wait a kernel may sit behind
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

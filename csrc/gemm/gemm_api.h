@@ -9,7 +9,7 @@ extern "C" {
 // Problem modes / epilogues: numeric values match b200::GemmMode / b200::GemmEpi.
 typedef struct B200GemmDesc {
   int mode;  // 0 dense, 1 grouped by rows (padded expert segments), 2 grouped by contraction (per-expert dW)
-  int epi;   // 0 bf16, 1 fp32 (beta), 2 swiglu, 3 swiglu backward, 4 bf16 + softmax partials
+  int epi;   // 0 bf16, 1 fp32 (beta), 2 swiglu, 3 swiglu backward, 4 bf16 + softmax partials, 5 bf16 scatter to peers
   int bn;    // tile width: 256, 128 or 64
   int a_mn;  // A stored with the M index contiguous (rows = contraction index)
   int b_mn;  // B stored with the N index contiguous (rows = contraction index)
@@ -37,6 +37,19 @@ typedef struct B200GemmDesc {
   void* aux1;
   long long ld_aux1;
   int* status;  // device int, 0 = ok; a bounded wait that ran out writes its code here
+  // ---- expert-parallel hooks (see b200::GemmEp); leave zeroed when unused
+  const int* ep_wait_flags;
+  int ep_wait_n;
+  const int* ep_epoch_base;
+  int ep_wait_epoch_off;
+  void* ep_scatter_dst[8];
+  const int* ep_scatter_meta;
+  int* ep_post_flags[8];
+  int ep_post_index;
+  int ep_post_epoch_off;
+  int ep_world;
+  int* ep_counter;
+  unsigned long long ep_limit_ns;
 } B200GemmDesc;
 
 // Enqueue one GEMM on `stream`. Returns 0 on success, a negative code on a host-side error.

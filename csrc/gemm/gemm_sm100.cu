@@ -119,6 +119,22 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   a.aux0 = d->aux0; a.ld_aux0 = d->ld_aux0;
   a.aux1 = d->aux1; a.ld_aux1 = d->ld_aux1;
   a.status = d->status;
+  a.ep.wait_flags = d->ep_wait_flags;
+  a.ep.wait_n = d->ep_wait_n;
+  a.ep.epoch_base = d->ep_epoch_base;
+  a.ep.wait_epoch_off = d->ep_wait_epoch_off;
+  for (int r = 0; r < 8; ++r) {
+    a.ep.scatter_dst[r] = d->ep_scatter_dst[r];
+    a.ep.post_flags[r] = d->ep_post_flags[r];
+  }
+  a.ep.scatter_meta = d->ep_scatter_meta;
+  a.ep.post_index = d->ep_post_index;
+  a.ep.post_epoch_off = d->ep_post_epoch_off;
+  a.ep.world = d->ep_world;
+  a.ep.counter = d->ep_counter;
+  a.ep.limit_ns = d->ep_limit_ns ? d->ep_limit_ns : 10000000000ull;
+  if ((a.ep.wait_flags || a.ep.counter) && a.ep.epoch_base == nullptr) return -22;
+  if (d->epi == EPI_BF16_SCATTER && a.ep.scatter_meta == nullptr) return -22;
 
   CUtensorMap ma, mb;
   int rc;
@@ -157,6 +173,10 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   B200_CASE(256, 0, 1, EPI_SWIGLU_BWD)
   B200_CASE(128, 0, 1, EPI_SWIGLU_BWD)
   B200_CASE(256, 0, 0, EPI_LSE)
+  B200_CASE(256, 0, 0, EPI_BF16_SCATTER)
+  B200_CASE(128, 0, 0, EPI_BF16_SCATTER)
+  B200_CASE(256, 0, 1, EPI_BF16_SCATTER)
+  B200_CASE(128, 0, 1, EPI_BF16_SCATTER)
 #undef B200_CASE
   return -21;
 }

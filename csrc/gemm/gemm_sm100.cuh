@@ -24,6 +24,23 @@ enum GemmEpi : int {
   EPI_SWIGLU = 2,      // acc = [gate | up]; C = silu(gate)*up, aux0 = pre-activations
   EPI_SWIGLU_BWD = 3,  // acc = d(act); aux0 = pre-activations; aux1 = d(pre-activations)
   EPI_LSE = 4,         // C bf16 = acc, aux0 = per (row, n-tile) (max, sum exp) partials
+  EPI_BF16_SCATTER = 5,  // bf16 rows stored into peers' buffers: row r -> scatter_dst[src(r)] + slot(r) * ldc
+};
+
+// Expert-parallel hooks (all optional; null pointers switch them off).
+struct GemmEp {
+  const int* wait_flags;  // local flag words the producer waits on (>= epoch) before its first load
+  int wait_n;
+  const int* epoch_base;  // device scalar; epochs are epoch_base + offset so that graph replays keep counting
+  int wait_epoch_off;
+  void* scatter_dst[8];     // EPI_BF16_SCATTER: every rank's return buffer
+  const int* scatter_meta;  // per row: (source rank << 28) | slot, or -1 for a padding row
+  int* post_flags[8];       // completion flag words on every rank, set by the last CTA to finish
+  int post_index;
+  int post_epoch_off;
+  int world;
+  int* counter;             // local ticket counter, zero between launches
+  unsigned long long limit_ns;
 };
 
 struct GemmArgs {
@@ -44,6 +61,7 @@ struct GemmArgs {
   void* aux1;
   long long ld_aux1;
   int* status;
+  GemmEp ep;
 };
 
 struct TileInfo {
@@ -152,6 +170,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
+      if (args.ep.wait_flags != nullptr && blockIdx.x < total) {
+        // rows of the A operand are being pushed into local memory by peer GPUs: wait for their flags,
+        // then order the (generic-proxy) acquire before the async-proxy TMA reads
+        const int epoch = *args.ep.epoch_base + args.ep.wait_epoch_off;
+        for (int r = 0; r < args.ep.wait_n && ok; ++r) ok = wait_flag_ge(args.ep.wait_flags + r, epoch, args.ep.limit_ns);
+        if (!ok) report(args.status, ST_TIMEOUT_PEER);
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
         TileInfo ti;
         decode_tile(args, t, m_tiles, n_tiles, ti);
@@ -280,7 +306,39 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
       const bool row_ok = row_g < args.M;
       const int n0 = ti.n_idx * BN_OUT;
 
-      if constexpr (EPI == EPI_BF16 || EPI == EPI_LSE) {
+      if constexpr (EPI == EPI_BF16_SCATTER) {
+        // result rows go straight to the rank that owns the token (plain peer stores)
+        int meta = -1;
+        if (row_ok) meta = args.ep.scatter_meta[row_g];
+        const bool live = meta >= 0;
+        __nv_bfloat16* crow = nullptr;
+        if (live)
+          crow = reinterpret_cast<__nv_bfloat16*>(args.ep.scatter_dst[(meta >> 28) & 7]) +
+                 static_cast<long long>(meta & 0x0fffffff) * args.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= args.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          if (live) {
+            if (col0 + 32 <= args.N) {
+              uint4* dst = reinterpret_cast<uint4*>(crow + col0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                dst[j] = make_uint4(pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                                    pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                                    pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                                    pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < args.N) crow[col0 + j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_BF16 || EPI == EPI_LSE) {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(args.C) + row_g * args.ldc;
         float run_max = -INFINITY, run_sum = 0.f;
 #pragma unroll 1
@@ -451,6 +509,21 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
       if (lane == 0) mbar_arrive(&bar_tempty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if (args.ep.counter != nullptr) {
+      // everything this CTA stored (possibly into peers' memory) is ordered before its ticket; the
+      // last CTA of the grid tells every rank that this rank's rows have been delivered
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int ticket = atomicAdd(args.ep.counter, 1);
+        if (ticket == static_cast<int>(gridDim.x) - 1) {
+          *args.ep.counter = 0;
+          __threadfence_system();
+          const int epoch = *args.ep.epoch_base + args.ep.post_epoch_off;
+          for (int r = 0; r < args.ep.world; ++r) st_release_sys(args.ep.post_flags[r] + args.ep.post_index, epoch);
+        }
+      }
     }
   }
 

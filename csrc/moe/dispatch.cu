@@ -124,11 +124,26 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int
 }
 
 // out[t] = sum_k w[t,k] * ys[pos[t,k]] (+ res[t]);  w == null -> plain sum.  Fixed k order.
+// pos == null: slot (t, k) reads row t*K + k.  wait_flags != null: rows of `ys` are being stored by
+// peer GPUs; every block first waits (bounded) until all `wait_n` flag words reach the epoch.
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const int* __restrict__ pos,
                                    const float* __restrict__ w, const __nv_bfloat16* __restrict__ res, int T, int K,
-                                   int H, __nv_bfloat16* __restrict__ out) {
+                                   int H, __nv_bfloat16* __restrict__ out, const int* wait_flags, int wait_n,
+                                   const int* epoch_base, int epoch_off, int* status) {
   const int nch = H >> 3;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  if (wait_flags != nullptr) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) {
+      const int epoch = *epoch_base + epoch_off;
+      int ok = 1;
+      for (int r = 0; r < wait_n && ok; ++r) ok = wait_flag_ge(wait_flags + r, epoch, 10000000000ull) ? 1 : 0;
+      if (!ok) report(status, ST_TIMEOUT_PEER);
+      ok_s = ok;
+    }
+    __syncthreads();
+    if (!ok_s) return;
+  }
   for (int t = blockIdx.x * wpb + warp; t < T; t += gridDim.x * wpb) {
     for (int c = lane; c < nch; c += 32) {
       float acc[8];
@@ -145,10 +160,11 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ ys, const i
         }
       }
       for (int k = 0; k < K; ++k) {
-        const int p = pos[static_cast<size_t>(t) * K + k];
+        const int p = pos ? pos[static_cast<size_t>(t) * K + k] : t * K + k;
         if (p < 0) continue;
         const float wk = w ? w[static_cast<size_t>(t) * K + k] : 1.f;
-        const uint4 q = *reinterpret_cast<const uint4*>(ys + static_cast<size_t>(p) * H + c * 8);
+        // rows may have been written by a peer a moment ago: read them past L1
+        const uint4 q = __ldcg(reinterpret_cast<const uint4*>(ys + static_cast<size_t>(p) * H + c * 8));
         const uint32_t u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -232,14 +248,16 @@ extern "C" int b200_moe_gather(const void* x, const int* row_slot, const int* se
 }
 
 extern "C" int b200_moe_combine(const void* ys, const int* pos, const float* w, const void* res, int T, int K, int H,
-                                void* out, cudaStream_t stream) {
+                                void* out, const int* wait_flags, int wait_n, const int* epoch_base, int epoch_off,
+                                int* status, cudaStream_t stream) {
   if (H % 8 != 0) return -1;
   if (T <= 0) return 0;
   int grid = (T + 7) / 8;
   if (grid > 1184) grid = 1184;
   moe_combine_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(ys), pos, w,
                                                reinterpret_cast<const __nv_bfloat16*>(res), T, K, H,
-                                               reinterpret_cast<__nv_bfloat16*>(out));
+                                               reinterpret_cast<__nv_bfloat16*>(out), wait_flags, wait_n, epoch_base,
+                                               epoch_off, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -38,6 +38,7 @@ int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* 
 int b200_moe_gather(const void* x, const int* row_slot, const int* seg_off, int E, int K, int H, void* xs,
                     int capacity, cudaStream_t stream);
 int b200_moe_combine(const void* ys, const int* pos, const float* w, const void* res, int T, int K, int H, void* out,
+                     const int* wait_flags, int wait_n, const int* epoch_base, int epoch_off, int* status,
                      cudaStream_t stream);
 int b200_moe_combine_bwd(const void* dout, const void* ys, const int* row_slot, const int* seg_off, const float* w,
                          int E, int K, int H, void* dys, float* dw, int capacity, cudaStream_t stream);
@@ -74,6 +75,19 @@ int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long 
                    const int* epoch_base, int epoch_off, int final_bucket, int use_multimem, int blocks, int* state_i,
                    float* state_f, int* status, unsigned long long limit_ns, cudaStream_t stream);
 int b200_clip_coef_multi(const float* parts, int world, float max_norm, float* coef, cudaStream_t stream);
+
+// ---- moe/ep.cu (expert parallelism over peer memory; pointer arrays have B200_MAX_RANKS entries)
+#define B200_EP_CH_COUNTS 0
+#define B200_EP_CH_DISPATCH 1
+#define B200_EP_CH_RETURN 2
+int b200_ep_exchange(const int* counts, void* const* cmat, void* const* flags, int chan, const int* epoch_base,
+                     int epoch_off, int rank, int world, int E, int H, int capacity, int* send_base, int* recv_seg_off,
+                     int* recv_tile_expert, int* recv_num_m_tiles, void* recv_buf, int* recv_meta, int* status,
+                     unsigned long long limit_ns, cudaStream_t stream);
+int b200_ep_dispatch(const void* rows, const float* scale, const int* idx, const int* pos, const int* local_seg_off,
+                     const int* send_base, void* const* recv_buf, void* const* recv_meta, void* const* flags, int chan,
+                     const int* epoch_base, int epoch_off, int rank, int world, int E, int n, int K, int H,
+                     int capacity, int* counter, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

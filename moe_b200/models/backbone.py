@@ -92,8 +92,13 @@ class Experts(nn.Module):
         self.num_experts = config.num_experts
         self.hidden_dim = config.hidden_size
         self.intermediate_dim = config.moe_intermediate_size
-        self.gate_up_proj = nn.Parameter(torch.empty(self.num_experts, 2 * self.intermediate_dim, self.hidden_dim))
-        self.down_proj = nn.Parameter(torch.empty(self.num_experts, self.hidden_dim, self.intermediate_dim))
+        ep_size = getattr(config, "ep_size", 1)
+        self.num_local_experts = self.num_experts // ep_size
+        self.gate_up_proj = nn.Parameter(torch.empty(self.num_local_experts, 2 * self.intermediate_dim, self.hidden_dim))
+        self.down_proj = nn.Parameter(torch.empty(self.num_local_experts, self.hidden_dim, self.intermediate_dim))
+        if ep_size > 1:  # this rank's slice of the bank along the expert dimension
+            for p in (self.gate_up_proj, self.down_proj):
+                p._ep_shard = (getattr(config, "ep_rank", 0), ep_size)
 
     def forward(self, hidden_states, top_k_index, top_k_weights):
         return ops.moe_experts(hidden_states, top_k_index, top_k_weights, self.gate_up_proj, self.down_proj)
@@ -230,6 +235,14 @@ def init_weights_(module: nn.Module, std: float = 0.02, generator: torch.Generat
         if name.endswith("norm.weight") or "layernorm" in name:
             with torch.no_grad():
                 p.fill_(1.0)
+        elif getattr(p, "_ep_shard", None) is not None:
+            # draw the whole bank so that the values do not depend on the expert-parallel size, keep our slice
+            r, n = p._ep_shard
+            with torch.no_grad():
+                full = torch.empty((p.shape[0] * n, *p.shape[1:]), dtype=p.dtype, device=p.device)
+                full.normal_(mean=0.0, std=std, generator=generator)
+                p.copy_(full[r * p.shape[0]:(r + 1) * p.shape[0]])
+                del full
         else:
             with torch.no_grad():
                 p.normal_(mean=0.0, std=std, generator=generator)

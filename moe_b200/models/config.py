@@ -77,6 +77,9 @@ class Qwen3MoeConfig(Qwen3Config):
     # "softmax" | "sigmoid"; None = decided by the model class
     score_fn: str | None = None
     expert_bias: bool | None = None
+    # expert parallelism: this process holds experts [ep_rank * E/ep_size, (ep_rank + 1) * E/ep_size)
+    ep_size: int = 1
+    ep_rank: int = 0
     model_type: str = "qwen3_moe"
 
     def __post_init__(self) -> None:
@@ -85,6 +88,8 @@ class Qwen3MoeConfig(Qwen3Config):
             raise ValueError("num_experts_per_tok cannot exceed num_experts")
         if (self.num_groups is None) != (self.group_topk is None):
             raise ValueError("num_groups and group_topk must be set together")
+        if self.ep_size > 1 and self.num_experts % self.ep_size != 0:
+            raise ValueError("num_experts must be divisible by ep_size")
         if self.num_groups is not None:
             if self.num_experts % self.num_groups != 0:
                 raise ValueError("num_experts must be divisible by num_groups")

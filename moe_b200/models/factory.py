@@ -31,7 +31,7 @@ def load_config(path: str) -> dict:
         return yaml.safe_load(f)
 
 
-def model_config_from_dict(mcfg: dict):
+def model_config_from_dict(mcfg: dict, ep: tuple[int, int] | None = None):
     mtype = mcfg["type"]
     if mtype not in MODEL_TYPES:
         raise ValueError(f"Unknown model type: {mtype}")
@@ -66,14 +66,18 @@ def model_config_from_dict(mcfg: dict):
     if mtype.startswith("deepseek") or mcfg.get("expert_bias") or mcfg.get("score_fn") == "sigmoid":
         moe.update(topk_scaling_factor=mcfg.get("topk_scaling_factor"), num_groups=mcfg.get("num_groups"),
                    group_topk=mcfg.get("group_topk"))
+    if ep is not None and ep[1] > 1:
+        moe.update(ep_rank=ep[0], ep_size=ep[1])
     cls = GlobalMoEConfig if "global" in mtype else Qwen3MoeConfig
     return cls(**base, **moe)
 
 
-def build_model(cfg: dict, seed: int | None = None, device: str | torch.device | None = None):
-    """Returns (model, model_config).  `cfg` is the whole YAML dict (uses `cfg['model']`)."""
+def build_model(cfg: dict, seed: int | None = None, device: str | torch.device | None = None,
+                ep: tuple[int, int] | None = None):
+    """Returns (model, model_config).  `cfg` is the whole YAML dict (uses `cfg['model']`).
+    `ep=(rank, size)` shards every expert bank over `size` ranks (expert parallelism)."""
     mcfg = cfg["model"]
-    config = model_config_from_dict(mcfg)
+    config = model_config_from_dict(mcfg, ep)
     mtype = mcfg["type"]
     cls = {"dense": Qwen3ForCausalLM, "standard_moe": StandardMoEModel,
            "deepseek_standard_moe": DeepSeekStandardMoEModel, "global_moe": GlobalMoEForCausalLM,

@@ -105,6 +105,13 @@ def router(x, weight, bias, *, top_k, score_fn, norm_topk_prob, scaling_factor, 
 
 
 def moe_experts(x, idx, w, gate_up, down):
+    ep = getattr(gate_up, "_ep", None)
+    if ep is not None:  # experts sharded over ranks: dispatch / combine over NVLink peer memory
+        from ..parallel.ep import moe_experts_ep
+
+        return moe_experts_ep(x, idx, w, gate_up, down, ep)
+    if getattr(gate_up, "_ep_shard", None) is not None:
+        raise RuntimeError("expert-parallel parameters need an EPContext (create the model through Trainer)")
     if _k(x):
         return _f().moe_experts(x, idx, w, gate_up, down)
     return oracle.moe_experts(x, idx.long(), w, gate_up, down)

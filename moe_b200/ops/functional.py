@@ -383,7 +383,7 @@ class MoEExpertsFn(torch.autograd.Function):
         ys = torch.empty(cap, H, dtype=BF16, device=dev)
         G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys)
         out = torch.empty(T, H, dtype=BF16, device=dev)
-        e.moe_combine(ys, plan.pos, tw, None, out, K)
+        e.moe_combine(ys, plan.pos, tw, None, out, K, None, 0, None, 0, None)
         ctx.save_for_backward(xs, gu, act, ys, tw)
         ctx.plan = plan
         ctx.params = (gate_up, down)
@@ -420,7 +420,7 @@ class MoEExpertsFn(torch.autograd.Function):
         t1, b1 = s1.target()
         G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1)
         dx = torch.empty(T, H, dtype=BF16, device=dev)
-        e.moe_combine(dxs, plan.pos, None, None, dx, K)
+        e.moe_combine(dxs, plan.pos, None, None, dx, K, None, 0, None, 0, None)
         return dx.view(ctx.in_shape), dw.view(T, K), None, s1.done(t1), s2.done(t2)
 
 

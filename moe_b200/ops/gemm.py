@@ -12,7 +12,7 @@ import torch
 from . import _ext
 
 MODE_DENSE, MODE_GROUPED_M, MODE_GROUPED_K = 0, 1, 2
-EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD, EPI_LSE = 0, 1, 2, 3, 4
+EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD, EPI_LSE, EPI_BF16_SCATTER = 0, 1, 2, 3, 4, 5
 
 _status_words: dict[int, torch.Tensor] = {}
 
@@ -53,11 +53,11 @@ def _pick_bn(n: int) -> int:
 
 def _launch(*, mode, epi, bn, a_mn, b_mn, M, N, K, A, lda, a_inner, a_rows, B, ldb, b_expert_stride, b_inner,
             b_rows, b_experts, C, ldc, num_experts=1, m_fast=1, beta=0, n_half=0, tile_expert=None,
-            num_m_tiles=None, seg_off=None, c_expert_stride=0, aux0=None, ld_aux0=0, aux1=None, ld_aux1=0):
+            num_m_tiles=None, seg_off=None, c_expert_stride=0, aux0=None, ld_aux0=0, aux1=None, ld_aux1=0, ep=None):
     ext = _ext.load()
     ext.gemm(mode, epi, bn, a_mn, b_mn, M, N, K, num_experts, m_fast, beta, n_half, A, lda, a_inner, a_rows, B, ldb,
              b_expert_stride, b_inner, b_rows, b_experts, tile_expert, num_m_tiles, seg_off, C, ldc,
-             c_expert_stride, aux0, ld_aux0, aux1, ld_aux1, status_word(A.device))
+             c_expert_stride, aux0, ld_aux0, aux1, ld_aux1, status_word(A.device), **(ep or {}))
 
 
 def _check2d(t: torch.Tensor, name: str) -> None:
@@ -131,7 +131,7 @@ def gemm_nt_lse(a: torch.Tensor, b: torch.Tensor, logits: torch.Tensor | None = 
 
 # ------------------------------------------------------------------ grouped (MoE)
 def grouped_up_swiglu(xs: torch.Tensor, w_gate_up: torch.Tensor, tile_expert: torch.Tensor,
-                      num_m_tiles: torch.Tensor, act: torch.Tensor, gu: torch.Tensor, bn: int = 256) -> None:
+                      num_m_tiles: torch.Tensor, act: torch.Tensor, gu: torch.Tensor, bn: int = 256, ep=None) -> None:
     """`xs[R,H]` (expert-sorted, 128-row padded) x `w_gate_up[E,2I,H]` -> `act[R,I]`, pre-activations `gu[R,2I]`."""
     R, H = xs.shape
     E, I2, _ = w_gate_up.shape
@@ -139,34 +139,35 @@ def grouped_up_swiglu(xs: torch.Tensor, w_gate_up: torch.Tensor, tile_expert: to
     _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU, bn=bn, a_mn=0, b_mn=0, M=R, N=I, K=H, A=xs, lda=xs.stride(0),
             a_inner=H, a_rows=R, B=w_gate_up, ldb=w_gate_up.stride(1), b_expert_stride=w_gate_up.stride(0),
             b_inner=H, b_rows=I2, b_experts=E, C=act, ldc=act.stride(0), n_half=I, tile_expert=tile_expert,
-            num_m_tiles=num_m_tiles, aux0=gu, ld_aux0=gu.stride(0), m_fast=0)
+            num_m_tiles=num_m_tiles, aux0=gu, ld_aux0=gu.stride(0), m_fast=0, ep=ep)
 
 
 def grouped_nt(xs: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, num_m_tiles: torch.Tensor,
-               out: torch.Tensor, bn: int | None = None) -> None:
-    """`out[R,N] = xs[R,K] @ w[e(row)][N,K]^T` (down projection)."""
+               out: torch.Tensor, bn: int | None = None, ep=None, scatter: bool = False) -> None:
+    """`out[R,N] = xs[R,K] @ w[e(row)][N,K]^T` (down projection).  `scatter=True`: rows go to the peers'
+    return buffers named in `ep` instead of `out` (only `out.stride(0)` is used)."""
     R, K = xs.shape
     E, N, _ = w.shape
-    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=0, M=R, N=N, K=K,
+    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16_SCATTER if scatter else EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=0, M=R, N=N, K=K,
             A=xs, lda=xs.stride(0), a_inner=K, a_rows=R, B=w, ldb=w.stride(1), b_expert_stride=w.stride(0),
             b_inner=K, b_rows=N, b_experts=E, C=out, ldc=out.stride(0), tile_expert=tile_expert,
-            num_m_tiles=num_m_tiles, m_fast=0)
+            num_m_tiles=num_m_tiles, m_fast=0, ep=ep)
 
 
 def grouped_nn(xs: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, num_m_tiles: torch.Tensor,
-               out: torch.Tensor, bn: int | None = None) -> None:
+               out: torch.Tensor, bn: int | None = None, ep=None, scatter: bool = False) -> None:
     """`out[R,N] = xs[R,K] @ w[e(row)][K,N]` (input gradients; weights read in place)."""
     R, K = xs.shape
     E, _, N = w.shape
-    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=1, M=R, N=N, K=K,
+    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16_SCATTER if scatter else EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=1, M=R, N=N, K=K,
             A=xs, lda=xs.stride(0), a_inner=K, a_rows=R, B=w, ldb=w.stride(1), b_expert_stride=w.stride(0),
             b_inner=N, b_rows=K, b_experts=E, C=out, ldc=out.stride(0), tile_expert=tile_expert,
-            num_m_tiles=num_m_tiles, m_fast=0)
+            num_m_tiles=num_m_tiles, m_fast=0, ep=ep)
 
 
 def grouped_nn_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, tile_expert: torch.Tensor,
                           num_m_tiles: torch.Tensor, gu: torch.Tensor, dgu: torch.Tensor,
-                          bn: int | None = None) -> None:
+                          bn: int | None = None, ep=None) -> None:
     """`d(act) = dy[R,H] @ w_down[e][H,I]`, fused with the SwiGLU backward: writes `dgu[R,2I]`."""
     R, H = dy.shape
     E, _, I = w_down.shape
@@ -174,7 +175,7 @@ def grouped_nn_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, tile_expert: t
             K=H, A=dy, lda=dy.stride(0), a_inner=H, a_rows=R, B=w_down, ldb=w_down.stride(1),
             b_expert_stride=w_down.stride(0), b_inner=I, b_rows=H, b_experts=E, C=dgu, ldc=dgu.stride(0),
             n_half=I, tile_expert=tile_expert, num_m_tiles=num_m_tiles, aux0=gu, ld_aux0=gu.stride(0), aux1=dgu,
-            ld_aux1=dgu.stride(0), m_fast=0)
+            ld_aux1=dgu.stride(0), m_fast=0, ep=ep)
 
 
 def grouped_tn(a: torch.Tensor, b: torch.Tensor, seg_off: torch.Tensor, out: torch.Tensor, beta: int = 0,

@@ -40,7 +40,8 @@ class Slot:
     param: nn.Parameter
     offset: int
     numel: int
-    decay: bool
+    decay: bool  # replicated and weight-decayed: the part that takes part in the overlapped reduce
+    ep: bool = False  # expert-parallel shard: local to this rank, never all-reduced
 
 
 class _LayerBoundary(torch.autograd.Function):
@@ -78,17 +79,26 @@ class TrainEngine:
         self.cuda = self.device.type == "cuda"
         self.overlap = overlap_grad_reduce and self.cuda and self.world > 1
         # ---- layout: decayed parameters first, then the rest; module order inside each part
+        # regions: [replicated, decayed | expert-parallel shards (decayed) | not decayed]
         slots: list[Slot] = []
         off = 0
-        for want_decay in (True, False):
+        for region in ("dense", "ep", "nodecay"):
             for n, p in params:
-                if (not is_no_decay(n, p)) != want_decay:
+                is_ep = getattr(p, "_ep_shard", None) is not None
+                nd = is_no_decay(n, p)
+                kind = "nodecay" if nd else ("ep" if is_ep else "dense")
+                if kind != region:
                     continue
-                slots.append(Slot(n, p, off, p.numel(), want_decay))
+                slots.append(Slot(n, p, off, p.numel(), kind == "dense", kind == "ep"))
                 off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
-            if want_decay:
+            if region == "dense":
                 self.decay_end = off
+            elif region == "ep":
+                self.ep_end = off
         self.total = off
+        self.has_ep = self.ep_end > self.decay_end
+        if self.has_ep and not self.cuda:
+            raise ValueError("expert-parallel parameters need CUDA (peer-memory kernels)")
         self.slots = slots
         self.by_name = {s.name: s for s in slots}
         dev = self.device
@@ -126,6 +136,7 @@ class TrainEngine:
             # an async copy from pinned memory before each step (so a captured graph can be replayed)
             self._hyper = torch.zeros(3, dtype=torch.float32, device=dev)
             self._hyper_host = torch.zeros(3, dtype=torch.float32).pin_memory()
+            self._coef_ep = torch.ones(1, dtype=torch.float32, device=dev)
             from ..ops import _ext
 
             self._ext = _ext.load()
@@ -145,6 +156,7 @@ class TrainEngine:
         inner = getattr(self.model, "model", None)
         if inner is not None and hasattr(inner, "_boundary_fn"):
             inner._boundary_fn = self.boundary if self.overlap else None
+        self.end_step_hooks: list = []
         self._grad_norm = None
         self._reduced_upto = self.total  # everything at or above this offset has been handed to the reducer
         self._pending = []
@@ -278,9 +290,11 @@ class TrainEngine:
             return
         # the undecayed tail (norm weights) and anything below the last boundary
         hi = min(self._reduced_upto, self.decay_end)
-        tail = self.total > self.decay_end
+        tail = self.total > self.ep_end
+        if self.has_ep:
+            self._account_ep_norm()
         self._launch_reduce(0, hi, final=not tail)
-        self._launch_reduce(self.decay_end, self.total, final=True)
+        self._launch_reduce(self.ep_end, self.total, final=True)
         if self._fused_ar is not None and hi <= 0 and not tail:
             raise RuntimeError("no final gradient bucket was launched")
         self._reduced_upto = 0
@@ -291,6 +305,8 @@ class TrainEngine:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
         if self.cuda and self._fused_ar is not None:
             self._fused_ar.end_step()
+        for hook in self.end_step_hooks:
+            hook()
 
     def set_hyper(self, lr: float | None = None) -> None:
         """Stage the learning rate and Adam bias corrections of the NEXT step on the device."""
@@ -302,6 +318,21 @@ class TrainEngine:
             self._hyper_host[1] = 1.0 - self.betas[0] ** t
             self._hyper_host[2] = 1.0 - self.betas[1] ** t
             self._hyper.copy_(self._hyper_host, non_blocking=True)
+
+    def _account_ep_norm(self) -> None:
+        """Expert shards are not reduced: every token of every rank already contributed to the owner's
+        gradient.  What remains is the 1/world of the data-parallel mean (applied inside AdamW) and this
+        rank's share of the global gradient norm, added to the running sum the fused all-reduce keeps."""
+        self._zero_dead(self.decay_end, self.ep_end)
+        e = self._ext
+        e.sumsq(self.g32[self.decay_end:self.ep_end], self._ss_scratch, self._norm_ss, False)
+        if self._fused_ar is None:
+            raise RuntimeError("expert parallelism requires the peer-memory gradient path (comm='p2p')")
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self._comm_stream):
+            self._comm_stream.wait_event(ev)
+            self._fused_ar.state_f[1:2].add_(self._norm_ss / float(self.world * self.world))
 
     def step(self, lr: float | None = None, *, update_hyper: bool = True, count: bool = True) -> torch.Tensor:
         """Reduce, clip by global norm, AdamW.  Returns the (pre-clip) gradient norm as a tensor.
@@ -322,12 +353,16 @@ class TrainEngine:
             else:
                 e.sumsq(self.g32, self._ss_scratch, self._norm_ss, False)
                 e.clip_coef(self._norm_ss, float(self.max_grad_norm or 0.0), self._coef)
-            d = self.decay_end
+            d, pe = self.decay_end, self.ep_end
             if d > 0:
                 e.adamw(self.p32[:d], self.g32[:d], self.m[:d], self.v[:d], self.p16[:d], self._hyper, b1, b2, self.eps,
                         self.weight_decay, self._coef)
-            if self.total > d:
-                e.adamw(self.p32[d:], self.g32[d:], self.m[d:], self.v[d:], self.p16[d:], self._hyper, b1, b2,
+            if pe > d:  # expert shards: same clip coefficient, times the 1/world of the data-parallel mean
+                torch.div(self._coef[:1], float(self.world), out=self._coef_ep)
+                e.adamw(self.p32[d:pe], self.g32[d:pe], self.m[d:pe], self.v[d:pe], self.p16[d:pe], self._hyper, b1, b2,
+                        self.eps, self.weight_decay, self._coef_ep)
+            if self.total > pe:
+                e.adamw(self.p32[pe:], self.g32[pe:], self.m[pe:], self.v[pe:], self.p16[pe:], self._hyper, b1, b2,
                         self.eps, 0.0, self._coef)
             self._grad_norm = self._coef[1]
         else:
@@ -336,7 +371,7 @@ class TrainEngine:
             if self.max_grad_norm and self.max_grad_norm > 0:
                 coef = float(min(1.0, self.max_grad_norm / (norm.item() + 1e-6)))
             d = self.decay_end
-            for lo, hi, wd in ((0, d, self.weight_decay), (d, self.total, 0.0)):
+            for lo, hi, wd in ((0, d, self.weight_decay), (self.ep_end, self.total, 0.0)):
                 if hi > lo:
                     oracle.adamw_step_(self.p32[lo:hi], self.g32[lo:hi], self.m[lo:hi], self.v[lo:hi], lr=self.lr,
                                        beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd, step=self.step_count,

@@ -54,7 +54,7 @@ class FusedAllReduce:
     """Launches `csrc/comm/allreduce.cu` on slices of a flat gradient buffer (see that file)."""
 
     def __init__(self, ext, grad_ptrs, flag_ptrs, norm_ptrs, multicast_ptr, rank, world, device, status,
-                 blocks: int = 32, limit_ns: int = 0):
+                 blocks: int = 128, limit_ns: int = 0):
         self.ext, self.rank, self.world = ext, rank, world
         self.grad_ptrs, self.flag_ptrs, self.norm_ptrs, self.mc = grad_ptrs, flag_ptrs, norm_ptrs, multicast_ptr
         self.state_i = torch.zeros(2, dtype=torch.int32, device=device)

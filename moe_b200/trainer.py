@@ -34,15 +34,26 @@ class StepResult:
 
 class Trainer:
     def __init__(self, model, cfg: TrainingConfig, *, device=None, process_group=None, is_moe: bool = True,
-                 overlap_grad_reduce: bool = True, cuda_graph: bool = False, graph_warmup_steps: int = 2):
+                 overlap_grad_reduce: bool = True, cuda_graph: bool = False, graph_warmup_steps: int = 2,
+                 ep_capacity_factor: float = 2.0, comm: str | None = None):
         self.model = model
         self.cfg = cfg
         self.is_moe = is_moe
         self.engine = TrainEngine(model, lr=cfg.learning_rate, betas=(cfg.beta1, cfg.beta2), eps=cfg.eps,
                                   weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
                                   process_group=process_group, device=device,
-                                  overlap_grad_reduce=overlap_grad_reduce)
+                                  overlap_grad_reduce=overlap_grad_reduce, comm=comm)
         self.device = self.engine.device
+        # expert parallelism: parameters that are shards of an expert bank get the peer-memory context
+        self.ep = None
+        if self.engine.has_ep:
+            from .parallel.ep import EPContext
+
+            self.ep = EPContext(model.config.num_experts, process_group, self.device, ep_capacity_factor)
+            for s in self.engine.slots:
+                if s.ep:
+                    s.param._ep = self.ep
+            self.engine.end_step_hooks.append(self.ep.end_step)
         self.global_step = 0
         self.world = self.engine.world
         # whole-step CUDA graph: the step is captured once (after a few eager steps have run every
@@ -83,6 +94,8 @@ class Trainer:
     def _forward_backward(self, dev_batches):
         n = len(dev_batches)
         self.engine.zero_grad()
+        if self.ep is not None:
+            self.ep.begin_step()
         scale = 1.0 / n
         out, tokens = None, 0
         for mb in dev_batches:

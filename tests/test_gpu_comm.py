@@ -126,3 +126,73 @@ def test_two_gpu_fused_allreduce_matches_nccl(tmp_path):
         d = (a[key][0] - ref).abs()
         assert d.max() < 5e-3 and (d > 1e-4).float().mean() < 1e-2, key
         assert abs(a[key][1] - gn) < 2e-2 * gn
+
+
+def _ep_rank(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from test_gpu_model import tiny_cfg
+    from moe_b200.models import build_model
+    from moe_b200.ops import gemm as G
+    from moe_b200.trainer import Trainer
+    from moe_b200.utils.training import TrainingConfig
+
+    tcfg = TrainingConfig(learning_rate=1e-3, warmup_steps=0, max_steps=10, batch_size=2, gradient_accumulation=1,
+                          lr_scheduler="constant")
+    g = torch.Generator().manual_seed(0)
+    full = [torch.randint(0, 2048, (4, 128), generator=g) for _ in range(2)]
+    out = {}
+    for mtype in ("global_moe", "standard_moe"):
+        for ep in (None, (rank, world)):
+            model, _ = build_model(tiny_cfg(mtype), seed=5, device=f"cuda:{rank}", ep=ep)
+            tr = Trainer(model, tcfg, comm="p2p", overlap_grad_reduce=False)
+            losses, grads = [], None
+            for b in full:
+                mine = b[rank * 2:(rank + 1) * 2].cuda()
+                tr.engine.zero_grad()
+                if tr.ep is not None:
+                    tr.ep.begin_step()
+                o = model(input_ids=mine, labels=mine, output_router_logits=True)
+                o.loss.backward()
+                losses.append(float(o.loss.detach()))
+                tr.engine.step()  # reduces, clips, updates; the reduced gradients stay in the flat buffer
+                if grads is None:  # first step: identical weights in both set-ups
+                    grads = {s.name: (s.param.main_grad.clone().cpu() / (world if s.ep else 1))
+                             for s in tr.engine.slots}
+                    norm0 = float(tr.engine.grad_norm())
+            torch.cuda.synchronize()
+            G.check_status()
+            out[(mtype, ep is not None)] = (losses, grads, norm0)
+            dist.barrier()
+    torch.save(out, os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_expert_parallel_matches_replicated_experts(tmp_path):
+    import torch.multiprocessing as mp
+
+    mp.spawn(_ep_rank, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    res = [torch.load(tmp_path / f"rank{r}.pt") for r in range(2)]
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+    for mtype in ("global_moe", "standard_moe"):
+        for r in range(2):
+            la, lb = res[r][(mtype, True)][0], res[r][(mtype, False)][0]
+            assert all(abs(x - y) < 5e-3 * abs(y) for x, y in zip(la, lb)), (mtype, la, lb)
+            ga, gb = res[r][(mtype, True)][1], res[r][(mtype, False)][1]
+            for name, ref in gb.items():
+                got = ga[name]
+                if got.shape != ref.shape:  # expert shard: compare with this rank's slice of the full bank
+                    n = got.shape[0]
+                    ref = ref[r * n:(r + 1) * n]
+                assert rel(got, ref) < 3e-2, (mtype, name, rel(got, ref))
+            assert abs(res[r][(mtype, True)][2] - res[r][(mtype, False)][2]) < 2e-2 * res[r][(mtype, False)][2]
