@@ -39,6 +39,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=None, help="override per-GPU micro-batch")
     ap.add_argument("--seq", type=int, default=None, help="override sequence length")
     ap.add_argument("--no-overlap", action="store_true", help="reduce gradients after backward, not during")
+    ap.add_argument("--ep", action="store_true", help="shard the experts over all ranks (expert parallelism)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no whole-step CUDA graph)")
     return ap.parse_args()
 
@@ -176,10 +177,16 @@ def run_ours(args) -> dict:
     tcfg = TrainingConfig.from_dict(cfg["training"])
     B, S = tcfg.batch_size, cfg["data"]["seq_len"]
     V = cfg["model"]["vocab_size"]
-    model, mcfg = build_model(cfg, seed=42, device=f"cuda:{local}")
+    ep_size = int(cfg.get("parallel", {}).get("ep_size", 1) or 1)
+    if ep_size < 0 or args.ep:
+        ep_size = world
+    ep = (rank % ep_size, ep_size) if ep_size > 1 else None
+    if ep is not None and ep_size != world:
+        raise SystemExit("bench.py runs expert parallelism over all ranks (ep_size == number of GPUs)")
+    model, mcfg = build_model(cfg, seed=42, device=f"cuda:{local}", ep=ep)
     trainer = Trainer(model, tcfg, is_moe=cfg["model"]["type"] != "dense", overlap_grad_reduce=not args.no_overlap,
                       cuda_graph=not args.no_graph)
-    n_params = sum(p.numel() for p in model.parameters())
+    n_params = sum(p.numel() * (ep_size if getattr(p, "_ep_shard", None) else 1) for p in model.parameters())
     K, W = args.steps, args.warmup
     host = make_batches(W + 2 * K, B, S, V, rank, cfg["data"].get("seed", 0))
     # ---- warm-up (untimed); with the CUDA graph on, the first two steps run eagerly, the third captures
@@ -211,7 +218,7 @@ def run_ours(args) -> dict:
     tokens = B * S * world * K
     value = tokens / (ms / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
-    par = f"dp{world}"
+    par = f"dp{world}" + (f"+ep{ep_size}" if ep else "")
     return {
         "metric": "train_tokens_per_sec", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",

@@ -108,6 +108,8 @@ class TrainEngine:
         self.comm = comm if (self.cuda and self.world > 1) else "none"
         self.p32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
         self._peers = None
+        self._fused_ar = None
+        self._comm_stream = None
         if self.comm == "p2p":
             from .symm import PeerBuffers
 
@@ -144,7 +146,6 @@ class TrainEngine:
             self._fuse_adjacent()
             self.refresh_compute_copy()
             self._comm_stream = torch.cuda.Stream(device=dev) if self.world > 1 else None
-            self._fused_ar = None
             if self._peers is not None:
                 from ..ops import gemm as _G
                 from .symm import FusedAllReduce

@@ -155,7 +155,13 @@ def main(argv=None) -> None:
     is_global = mtype in ("global_moe", "deepseek_global_moe")
     # every rank builds identical weights from --seed (the reference reaches the same state through
     # DDP's initial broadcast of rank 0's weights); the data / dropout RNG is seeded per rank
-    model, mcfg = build_model(cfg, seed=args.seed, device=dev)
+    pcfg0 = cfg.get("parallel", {})
+    ep_size = int(pcfg0.get("ep_size", 1) or 1)
+    if ep_size < 0:
+        ep_size = world
+    if ep_size > 1 and (device != "cuda" or ep_size != world):
+        raise ValueError("parallel.ep_size must be 1, -1 or the number of ranks, and needs CUDA")
+    model, mcfg = build_model(cfg, seed=args.seed, device=dev, ep=(rank, ep_size) if ep_size > 1 else None)
     torch.manual_seed(args.seed + rank)
     params = count_parameters(model)
     expert_params = sum(p.numel() for n, p in model.named_parameters() if "gate_up_proj" in n or "down_proj" in n)

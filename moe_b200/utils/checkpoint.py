@@ -91,18 +91,27 @@ def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | N
             shutil.rmtree(tmp)
         os.makedirs(tmp, exist_ok=True)
     _barrier()
+    # expert-parallel shards are gathered into whole banks (all ranks take part), so the files do
+    # not depend on the expert-parallel size of the run that wrote them
+    shards = {n: getattr(p, "_ep_shard", None) for n, p in trainer.model.named_parameters()}
+    sd = {}
+    seen = {}
+    for k, v in trainer.model.state_dict().items():
+        t = _gather_full(v.detach(), shards.get(k))
+        key = (v.data_ptr(), tuple(v.shape))
+        if key in seen:  # tied weights: safetensors refuses shared storage
+            t = t.clone()
+        seen[key] = k
+        sd[k] = t
+    opt = trainer.engine.optimizer_state_dict()
+    for name, st in opt["state"].items():
+        if shards.get(name) is not None:
+            dev = trainer.engine.device
+            st["exp_avg"] = _gather_full(st["exp_avg"].to(dev), shards[name])
+            st["exp_avg_sq"] = _gather_full(st["exp_avg_sq"].to(dev), shards[name])
     if rank == 0:
-        sd = {}
-        seen = {}
-        for k, v in trainer.model.state_dict().items():
-            t = v.detach().cpu().contiguous()
-            key = (v.data_ptr(), tuple(v.shape))
-            if key in seen:  # tied weights: safetensors refuses shared storage
-                t = t.clone()
-            seen[key] = k
-            sd[k] = t
         save_file(sd, os.path.join(tmp, "model.safetensors"), metadata={"format": "pt"})
-        torch.save(trainer.engine.optimizer_state_dict(), os.path.join(tmp, "optimizer.bin"))
+        torch.save(opt, os.path.join(tmp, "optimizer.bin"))
         torch.save(scheduler_state or {"last_epoch": trainer.global_step}, os.path.join(tmp, "scheduler.bin"))
     with open(os.path.join(tmp, f"random_states_{rank}.pkl"), "wb") as f:
         pickle.dump(_rng_state(), f)
@@ -125,6 +134,22 @@ def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | N
     return final
 
 
+def _gather_full(t: torch.Tensor, shard) -> torch.Tensor:
+    if shard is None or not (dist.is_available() and dist.is_initialized()):
+        return t.cpu().contiguous()
+    parts = [torch.empty_like(t) for _ in range(shard[1])]
+    dist.all_gather(parts, t.contiguous())
+    return torch.cat(parts, dim=0).cpu()
+
+
+def _slice_for(p: torch.Tensor, full: torch.Tensor) -> torch.Tensor:
+    shard = getattr(p, "_ep_shard", None)
+    if shard is None or full.shape == p.shape:
+        return full
+    n = p.shape[0]
+    return full[shard[0] * n:(shard[0] + 1) * n]
+
+
 def read_meta(ckpt_dir: str) -> dict:
     p = os.path.join(ckpt_dir, "meta.json")
     if os.path.exists(p):
@@ -143,10 +168,18 @@ def load_checkpoint(trainer, resume_from: str, strict: bool = True) -> tuple[int
         sd = load_file(mpath)
         if getattr(trainer.model.config, "tie_word_embeddings", False) and "lm_head.weight" not in sd:
             sd["lm_head.weight"] = sd["model.embed_tokens.weight"]
+        params = dict(trainer.model.named_parameters())
+        sd = {k: (_slice_for(params[k], v) if k in params else v) for k, v in sd.items()}
         trainer.engine.load_model_state_dict(sd, strict=strict)
     opath = os.path.join(resume_from, "optimizer.bin")
     if os.path.exists(opath):
-        trainer.engine.load_optimizer_state_dict(torch.load(opath, map_location="cpu", weights_only=False))
+        opt = torch.load(opath, map_location="cpu", weights_only=False)
+        params = dict(trainer.model.named_parameters())
+        for name, st in opt["state"].items():
+            if name in params:
+                st["exp_avg"] = _slice_for(params[name], st["exp_avg"])
+                st["exp_avg_sq"] = _slice_for(params[name], st["exp_avg_sq"])
+        trainer.engine.load_optimizer_state_dict(opt)
     meta = read_meta(resume_from)
     step = int(meta.get("step", 0))
     spath = os.path.join(resume_from, "scheduler.bin")
