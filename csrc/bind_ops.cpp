@@ -78,7 +78,7 @@ void qknorm_rope_bwd(const Tensor& dq, const Tensor& dk, const Tensor& dv, const
   c10::cuda::CUDAGuard g(qkv.device());
   const int ld = (int)qkv.size(-1);
   const int T = (int)(qkv.numel() / ld);
-  need(dw_part.numel() >= b200_qknorm_rope_blocks((int64_t)T * (nh + 2 * nkv)) * 2 * hd, "qk dw scratch too small");
+  need(dw_part.numel() >= b200_qknorm_rope_blocks((int64_t)T) * 2 * hd, "qk dw scratch too small");
   rc_ok(b200_qknorm_rope_bwd(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), qkv.data_ptr(), ld, rstd.data_ptr<float>(),
                              qw.data_ptr<float>(), kw.data_ptr<float>(), cs.data_ptr<float>(), dqkv.data_ptr(),
                              dw_part.data_ptr<float>(), dqw.data_ptr<float>(), dkw.data_ptr<float>(),

@@ -29,6 +29,24 @@ __device__ __forceinline__ void store_lane(__nv_bfloat16* p, int lane, const flo
   }
 }
 
+// round-trip through bf16 (what the unfused module sequence would have stored), two lanes of work at a time
+template <int EPL>
+__device__ __forceinline__ void round_bf16(float (&v)[EPL]) {
+  if constexpr (EPL >= 2) {
+#pragma unroll
+    for (int i = 0; i < EPL; i += 2) {
+      const float2 f = unpack_bf16x2(pack_bf16x2(v[i], v[i + 1]));
+      v[i] = f.x;
+      v[i + 1] = f.y;
+    }
+  } else {
+    v[0] = __bfloat162float(__float2bfloat16(v[0]));
+  }
+}
+
+// One warp per token, looping over that token's heads: the position, the cos/sin values and the norm
+// weights of a lane's elements are loaded once per token instead of once per (token, head), and no
+// index division is left in the inner loop.
 template <int EPL>
 __global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, const float* __restrict__ qw,
                                        const float* __restrict__ kw, const float* __restrict__ cs,  // [S, hd/2, 2]
@@ -38,40 +56,56 @@ __global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, in
   constexpr int HD = EPL * 32, HALF = HD / 2;
   const int lane = threadIdx.x & 31;
   const int nqk = nh + nkv, nall = nh + 2 * nkv;
-  const long long total = static_cast<long long>(T) * nall;
-  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long it = wid; it < total; it += nw) {
-    const int t = static_cast<int>(it / nall), h = static_cast<int>(it - static_cast<long long>(t) * nall);
-    const bool is_q = h < nh;
-    const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * HD;
-    float x[EPL];
-    load_lane<EPL>(src, lane, x);
-    if (h >= nqk) {  // v head: plain copy into the attention layout
-      store_lane<EPL>(v_out + (static_cast<size_t>(t) * nkv + (h - nqk)) * HD, lane, x);
-      continue;
-    }
-    float ss = 0.f;
+  const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nw = (gridDim.x * blockDim.x) >> 5;
+  float wq[EPL], wk[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) ss += x[i] * x[i];
-    ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / HD + eps);
-    if (lane == 0) rstd_out[static_cast<long long>(t) * nqk + h] = rstd;
-    const float* w = is_q ? qw : kw;
+  for (int i = 0; i < EPL; ++i) {
+    wq[i] = qw[lane * EPL + i];
+    wk[i] = kw[lane * EPL + i];
+  }
+  const bool lower = lane < 16;  // elements of this lane lie in the first half of the head
+  for (int t = wid; t < T; t += nw) {
     const float* csr = cs + static_cast<size_t>(t % S) * HALF * 2;
-    float y[EPL];
+    float c[EPL], sn[EPL];
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
-      const int e = lane * EPL + i;
-      const float xn = w[e] * __bfloat162float(__float2bfloat16(x[i] * rstd));
-      const float other = __shfl_xor_sync(0xffffffffu, xn, 16);
-      const int j = e % HALF;
-      const float c = csr[2 * j], s = csr[2 * j + 1];
-      y[i] = xn * c + (e < HALF ? -other : other) * s;
+      const int j = (lane * EPL + i) % HALF;
+      const float2 v = *reinterpret_cast<const float2*>(csr + 2 * j);
+      c[i] = v.x;
+      sn[i] = lower ? -v.y : v.y;
     }
-    __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(t) * nh + h) * HD
-                              : k_out + (static_cast<size_t>(t) * nkv + (h - nh)) * HD;
-    store_lane<EPL>(dst, lane, y);
+    const __nv_bfloat16* row = qkv + static_cast<size_t>(t) * ld;
+#pragma unroll 2
+    for (int h = 0; h < nall; ++h) {
+      float x[EPL];
+      load_lane<EPL>(row + h * HD, lane, x);
+      if (h >= nqk) {  // v head: plain copy into the attention layout
+        store_lane<EPL>(v_out + (static_cast<size_t>(t) * nkv + (h - nqk)) * HD, lane, x);
+        continue;
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) ss += x[i] * x[i];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss * (1.0f / HD) + eps);
+      if (lane == 0) rstd_out[t * nqk + h] = rstd;
+      const bool is_q = h < nh;
+      float xn[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) xn[i] = x[i] * rstd;
+      round_bf16<EPL>(xn);
+      float y[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        xn[i] *= is_q ? wq[i] : wk[i];
+        const float other = __shfl_xor_sync(0xffffffffu, xn[i], 16);
+        y[i] = xn[i] * c[i] + other * sn[i];
+      }
+      __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(t) * nh + h) * HD
+                                : k_out + (static_cast<size_t>(t) * nkv + (h - nh)) * HD;
+      store_lane<EPL>(dst, lane, y);
+    }
   }
 }
 
@@ -87,51 +121,63 @@ __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, con
   __shared__ float sm[8][2][HD];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nqk = nh + nkv, nall = nh + 2 * nkv;
-  const long long total = static_cast<long long>(T) * nall;
-  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  float dwq[EPL], dwk[EPL];
+  const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nw = (gridDim.x * blockDim.x) >> 5;
+  float dwq[EPL], dwk[EPL], wq[EPL], wk[EPL];
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) dwq[i] = dwk[i] = 0.f;
-  for (long long it = wid; it < total; it += nw) {
-    const int t = static_cast<int>(it / nall), h = static_cast<int>(it - static_cast<long long>(t) * nall);
-    __nv_bfloat16* dst = dqkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * HD;
-    if (h >= nqk) {  // v head: plain copy
-      float g[EPL];
-      load_lane<EPL>(dv + (static_cast<size_t>(t) * nkv + (h - nqk)) * HD, lane, g);
-      store_lane<EPL>(dst, lane, g);
-      continue;
-    }
-    const bool is_q = h < nh;
-    const __nv_bfloat16* gsrc = is_q ? dq + (static_cast<size_t>(t) * nh + h) * HD
-                                     : dk + (static_cast<size_t>(t) * nkv + (h - nh)) * HD;
-    float g[EPL], x[EPL];
-    load_lane<EPL>(gsrc, lane, g);
-    load_lane<EPL>(qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * HD, lane, x);
-    const float rstd = rstd_in[static_cast<long long>(t) * nqk + h];
-    const float* w = is_q ? qw : kw;
+  for (int i = 0; i < EPL; ++i) {
+    dwq[i] = dwk[i] = 0.f;
+    wq[i] = qw[lane * EPL + i];
+    wk[i] = kw[lane * EPL + i];
+  }
+  const bool lower = lane < 16;
+  for (int t = wid; t < T; t += nw) {
     const float* csr = cs + static_cast<size_t>(t % S) * HALF * 2;
-    float dxn[EPL], xh[EPL], wd[EPL];
-    float dot = 0.f;
+    float c[EPL], sn[EPL];
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
-      const int e = lane * EPL + i;
-      const int j = e % HALF;
-      const float c = csr[2 * j], s = csr[2 * j + 1];
-      const float gs = g[i] * s;
-      const float other = __shfl_xor_sync(0xffffffffu, gs, 16);
-      // transpose of the rotation: lower half receives +z[i+HALF], upper half -z[i-HALF]
-      dxn[i] = g[i] * c + (e < HALF ? other : -other);
-      xh[i] = x[i] * rstd;
-      wd[i] = dxn[i] * w[e];
-      dot += wd[i] * xh[i];
-      if (is_q) dwq[i] += dxn[i] * xh[i]; else dwk[i] += dxn[i] * xh[i];
+      const int j = (lane * EPL + i) % HALF;
+      const float2 v = *reinterpret_cast<const float2*>(csr + 2 * j);
+      c[i] = v.x;
+      sn[i] = v.y;
     }
-    dot = warp_sum(dot) / HD;
-    float o[EPL];
+    const __nv_bfloat16* row = qkv + static_cast<size_t>(t) * ld;
+    __nv_bfloat16* drow = dqkv + static_cast<size_t>(t) * ld;
+#pragma unroll 2
+    for (int h = 0; h < nall; ++h) {
+      __nv_bfloat16* dst = drow + h * HD;
+      if (h >= nqk) {  // v head: plain copy
+        float g[EPL];
+        load_lane<EPL>(dv + (static_cast<size_t>(t) * nkv + (h - nqk)) * HD, lane, g);
+        store_lane<EPL>(dst, lane, g);
+        continue;
+      }
+      const bool is_q = h < nh;
+      const __nv_bfloat16* gsrc = is_q ? dq + (static_cast<size_t>(t) * nh + h) * HD
+                                       : dk + (static_cast<size_t>(t) * nkv + (h - nh)) * HD;
+      float g[EPL], x[EPL];
+      load_lane<EPL>(gsrc, lane, g);
+      load_lane<EPL>(row + h * HD, lane, x);
+      const float rstd = rstd_in[t * nqk + h];
+      float xh[EPL], wd[EPL];
+      float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) o[i] = rstd * (wd[i] - xh[i] * dot);
-    store_lane<EPL>(dst, lane, o);
+      for (int i = 0; i < EPL; ++i) {
+        const float gs = g[i] * sn[i];
+        const float other = __shfl_xor_sync(0xffffffffu, gs, 16);
+        // transpose of the rotation: lower half receives +z[i+HALF], upper half -z[i-HALF]
+        const float dxn = g[i] * c[i] + (lower ? other : -other);
+        xh[i] = x[i] * rstd;
+        wd[i] = dxn * (is_q ? wq[i] : wk[i]);
+        dot += wd[i] * xh[i];
+        if (is_q) dwq[i] += dxn * xh[i]; else dwk[i] += dxn * xh[i];
+      }
+      dot = warp_sum(dot) * (1.0f / HD);
+      float o[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) o[i] = rstd * (wd[i] - xh[i] * dot);
+      store_lane<EPL>(dst, lane, o);
+    }
   }
 #pragma unroll
   for (int i = 0; i < EPL; ++i) {
@@ -140,10 +186,10 @@ __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, con
   }
   __syncthreads();
   const int nwarps = blockDim.x >> 5;
-  for (int c = threadIdx.x; c < 2 * HD; c += blockDim.x) {
+  for (int cc = threadIdx.x; cc < 2 * HD; cc += blockDim.x) {
     float s = 0.f;
-    for (int wv = 0; wv < nwarps; ++wv) s += sm[wv][c / HD][c % HD];
-    dw_part[static_cast<size_t>(blockIdx.x) * 2 * HD + c] = s;
+    for (int wv = 0; wv < nwarps; ++wv) s += sm[wv][cc / HD][cc % HD];
+    dw_part[static_cast<size_t>(blockIdx.x) * 2 * HD + cc] = s;
   }
 }
 
@@ -171,6 +217,7 @@ __global__ void qk_dw_reduce_kernel(const float* __restrict__ part, int nblocks,
 
 using namespace b200;
 
+// `items` = number of tokens; one warp per token, eight warps per block
 extern "C" int b200_qknorm_rope_blocks(long long items) {
   long long g = (items + 7) / 8;
   return static_cast<int>(g < 1 ? 1 : (g > 1184 ? 1184 : g));
@@ -180,7 +227,7 @@ extern "C" int b200_qknorm_rope_fwd(const void* qkv, int ld, const float* qw, co
                                     void* q_out, void* k_out, void* v_out, float* rstd, int T, int S, int nh, int nkv,
                                     int hd, float eps, cudaStream_t stream) {
   if (T <= 0) return 0;
-  const int grid = b200_qknorm_rope_blocks(static_cast<long long>(T) * (nh + 2 * nkv));
+  const int grid = b200_qknorm_rope_blocks(T);
 #define ARGS reinterpret_cast<const __nv_bfloat16*>(qkv), ld, qw, kw, cs, reinterpret_cast<__nv_bfloat16*>(q_out), \
              reinterpret_cast<__nv_bfloat16*>(k_out), reinterpret_cast<__nv_bfloat16*>(v_out), rstd, T, S, nh, nkv, eps
   if (hd == 128) qknorm_rope_fwd_kernel<4><<<grid, 256, 0, stream>>>(ARGS);
@@ -196,7 +243,7 @@ extern "C" int b200_qknorm_rope_bwd(const void* dq, const void* dk, const void* 
                                     float* dw_part, float* dqw, float* dkw, int dw_accumulate, int T, int S, int nh,
                                     int nkv, int hd, cudaStream_t stream) {
   if (T <= 0) return 0;
-  const int grid = b200_qknorm_rope_blocks(static_cast<long long>(T) * (nh + 2 * nkv));
+  const int grid = b200_qknorm_rope_blocks(T);
 #define ARGS reinterpret_cast<const __nv_bfloat16*>(dq), reinterpret_cast<const __nv_bfloat16*>(dk),             \
              reinterpret_cast<const __nv_bfloat16*>(dv), reinterpret_cast<const __nv_bfloat16*>(qkv), ld, rstd, \
              qw, kw, cs, reinterpret_cast<__nv_bfloat16*>(dqkv), dw_part, T, S, nh, nkv

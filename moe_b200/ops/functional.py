@@ -267,7 +267,7 @@ class QKNormRopeFn(torch.autograd.Function):
         if bq != bk:  # keep one accumulate flag for the fused kernel
             (tq if bq == 0 else tk).zero_()
             bq = bk = 1
-        part = _scratch("qk_dw", e.qknorm_rope_blocks(T * (nh + 2 * nkv)) * 2 * hd, torch.float32, dev)
+        part = _scratch("qk_dw", e.qknorm_rope_blocks(T) * 2 * hd, torch.float32, dev)
         dqkv = torch.empty_like(qkv2)
         e.qknorm_rope_bwd(dq.contiguous(), dk.contiguous(), dv.contiguous(), qkv2, rstd, w32(ctx.q_w), w32(ctx.k_w), cs,
                           dqkv, part, tq, tk, bool(bq), S, nh, nkv, hd)
