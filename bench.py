@@ -40,6 +40,7 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=None, help="override sequence length")
     ap.add_argument("--no-overlap", action="store_true", help="reduce gradients after backward, not during")
     ap.add_argument("--ep", action="store_true", help="shard the experts over all ranks (expert parallelism)")
+    ap.add_argument("--zero", action="store_true", help="shard Adam moments and the update over the ranks (ZeRO-1)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no whole-step CUDA graph)")
     return ap.parse_args()
 
@@ -185,7 +186,7 @@ def run_ours(args) -> dict:
         raise SystemExit("bench.py runs expert parallelism over all ranks (ep_size == number of GPUs)")
     model, mcfg = build_model(cfg, seed=42, device=f"cuda:{local}", ep=ep)
     trainer = Trainer(model, tcfg, is_moe=cfg["model"]["type"] != "dense", overlap_grad_reduce=not args.no_overlap,
-                      cuda_graph=not args.no_graph)
+                      cuda_graph=not args.no_graph, shard_optimizer=args.zero and world > 1)
     n_params = sum(p.numel() * (ep_size if getattr(p, "_ep_shard", None) else 1) for p in model.parameters())
     K, W = args.steps, args.warmup
     host = make_batches(W + 2 * K, B, S, V, rank, cfg["data"].get("seed", 0))

@@ -151,7 +151,7 @@ def case_allreduce_emulated(small):
     ep = torch.ones(1, dtype=torch.int32, device="cuda")
     st = G.status_word(torch.device("cuda"))
     args = ([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], [x.data_ptr() for x in norms], 0)
-    ms = timeit(lambda: e.allreduce(*args, 0, world, 0, n, 1.0 / world, ep, 0, True, False, 128, si, sf, st, 0))
+    ms = timeit(lambda: e.allreduce(*args, 0, world, 0, n, 1.0 / world, ep, 0, True, True, False, 128, si, sf, st, 0))
     return dict(shape=[world, n], ms=ms, bytes=2.0 * n * 4)  # one slice read from 8 buffers + written to 8
 
 

@@ -6,6 +6,7 @@
 
 #include "ops_api.h"
 
+#include <cstring>
 #include <vector>
 
 namespace {
@@ -234,14 +235,17 @@ void clip_coef(const Tensor& ss, double max_norm, Tensor& coef) {
   rc_ok(b200_clip_coef(ss.data_ptr<float>(), (float)max_norm, coef.data_ptr<float>(), stream()), "clip_coef");
 }
 void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptT& p16, const Tensor& hyper, double beta1,
-           double beta2, double eps, double wd, const OptT& grad_coef) {
+           double beta2, double eps, double wd, const OptT& grad_coef, const std::vector<int64_t>& p16_peers) {
   f32c(p, "p"); f32c(g, "g"); f32c(m, "m"); f32c(v, "v"); f32c(hyper, "hyper");
   need(hyper.numel() >= 3, "hyper must hold {lr, bc1, bc2}");
+  std::vector<void*> peers;
+  for (auto a : p16_peers) peers.push_back(reinterpret_cast<void*>(a));
   c10::cuda::CUDAGuard gd(p.device());
   need(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw sizes");
   rc_ok(b200_adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
                    optp<void>(p16), p.numel(), hyper.data_ptr<float>(), (float)beta1, (float)beta2, (float)eps,
-                   (float)wd, optp<const float>(grad_coef), stream()), "adamw");
+                   (float)wd, optp<const float>(grad_coef), p16_peers.empty() ? nullptr : peers.data(),
+                   (int)p16_peers.size(), stream()), "adamw");
 }
 void cast_bf16(const Tensor& src, Tensor& dst) {
   f32c(src, "src"); bf16c(dst, "dst");
@@ -252,8 +256,8 @@ void cast_bf16(const Tensor& src, Tensor& dst) {
 // --------------------------------------------------------------------- comm
 void allreduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>& flags, const std::vector<int64_t>& norms,
                int64_t mc_buf, int64_t rank, int64_t world, int64_t off, int64_t n, double scale,
-               const Tensor& epoch_base, int64_t epoch_off, bool final_bucket, bool use_multimem, int64_t blocks,
-               Tensor& state_i, Tensor& state_f, Tensor& status, int64_t limit_ns) {
+               const Tensor& epoch_base, int64_t epoch_off, bool final_bucket, bool publish, bool use_multimem,
+               int64_t blocks, Tensor& state_i, Tensor& state_f, Tensor& status, int64_t limit_ns) {
   i32c(epoch_base, "epoch_base"); i32c(state_i, "state_i"); f32c(state_f, "state_f"); i32c(status, "status");
   need((int64_t)bufs.size() >= world && (int64_t)flags.size() >= world && (int64_t)norms.size() >= world,
        "peer pointer lists shorter than world");
@@ -266,9 +270,19 @@ void allreduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>& fla
   }
   p.mc_buf = reinterpret_cast<void*>(mc_buf);
   rc_ok(b200_allreduce(&p, (int)rank, (int)world, off, n, (float)scale, epoch_base.data_ptr<int>(), (int)epoch_off,
-                       final_bucket ? 1 : 0, use_multimem ? 1 : 0, (int)blocks, state_i.data_ptr<int>(),
+                       final_bucket ? 1 : 0, publish ? 1 : 0, use_multimem ? 1 : 0, (int)blocks, state_i.data_ptr<int>(),
                        state_f.data_ptr<float>(), status.data_ptr<int>(), (unsigned long long)limit_ns, stream()),
         "allreduce");
+}
+void peer_barrier(const std::vector<int64_t>& flags, int64_t rank, int64_t world, int64_t chan,
+                  const Tensor& epoch_base, int64_t epoch_off, Tensor& status) {
+  i32c(epoch_base, "epoch_base"); i32c(status, "status");
+  c10::cuda::CUDAGuard g(status.device());
+  B200Peers p;
+  std::memset(&p, 0, sizeof(p));
+  for (int r = 0; r < B200_MAX_RANKS && r < (int)flags.size(); ++r) p.flags[r] = reinterpret_cast<void*>(flags[r]);
+  rc_ok(b200_peer_barrier(&p, (int)rank, (int)world, (int)chan, epoch_base.data_ptr<int>(), (int)epoch_off,
+                          status.data_ptr<int>(), 0, stream()), "peer_barrier");
 }
 void clip_coef_multi(const Tensor& parts, int64_t world, double max_norm, Tensor& coef) {
   f32c(parts, "parts"); f32c(coef, "coef");
@@ -281,6 +295,7 @@ void clip_coef_multi(const Tensor& parts, int64_t world, double max_norm, Tensor
 
 void bind_ops(pybind11::module_& m) {
   m.def("allreduce", &allreduce);
+  m.def("peer_barrier", &peer_barrier);
   m.def("ep_exchange", &ep_exchange);
   m.def("ep_dispatch", &ep_dispatch);
   m.def("clip_coef_multi", &clip_coef_multi);
@@ -304,6 +319,8 @@ void bind_ops(pybind11::module_& m) {
   m.def("sumsq_blocks", &sumsq_blocks);
   m.def("sumsq", &sumsq);
   m.def("clip_coef", &clip_coef);
-  m.def("adamw", &adamw);
+  m.def("adamw", &adamw, pybind11::arg("p"), pybind11::arg("g"), pybind11::arg("m"), pybind11::arg("v"),
+        pybind11::arg("p16"), pybind11::arg("hyper"), pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("eps"),
+        pybind11::arg("wd"), pybind11::arg("grad_coef"), pybind11::arg("p16_peers") = std::vector<int64_t>());
   m.def("cast_bf16", &cast_bf16);
 }

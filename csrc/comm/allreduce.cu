@@ -54,8 +54,8 @@ __device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(AR_THREADS)
 allreduce_kernel(ArPeers peers, float* mc_buf, int rank, int world, long long off, long long n, float scale,
-                 const int* epoch_base, int epoch_off, int final_bucket, int* state_i, float* state_f, int* status,
-                 unsigned long long limit_ns) {
+                 const int* epoch_base, int epoch_off, int final_bucket, int publish, int* state_i, float* state_f,
+                 int* status, unsigned long long limit_ns) {
   __shared__ float sh[AR_THREADS / 32];
   __shared__ int sh_ok;
   int* my_flags = peers.flags[rank];
@@ -119,7 +119,15 @@ allreduce_kernel(ArPeers peers, float* mc_buf, int rank, int world, long long of
         const long long i = i0 + u * stride;
         if (i < hi) ss += acc[u].x * acc[u].x + acc[u].y * acc[u].y + acc[u].z * acc[u].z + acc[u].w * acc[u].w;
       }
-      if constexpr (MULTIMEM) {
+      if (!publish) {
+        // reduce-scatter: only the owner keeps its slice (sharded optimizer state)
+        float* dst = peers.buf[rank] + off;
+#pragma unroll
+        for (int u = 0; u < AR_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < hi) st_peer_f4(dst + (i << 2), acc[u]);
+        }
+      } else if constexpr (MULTIMEM) {
 #pragma unroll
         for (int u = 0; u < AR_UNROLL; ++u) {
           const long long i = i0 + u * stride;
@@ -176,13 +184,27 @@ __global__ void clip_coef_multi_kernel(const float* __restrict__ parts, int worl
   coef[1] = norm;
 }
 
+// Post flag word `index` (= channel * B200_MAX_RANKS + rank) on every rank and wait for all ranks' words of
+// that channel.  One thread; used after kernels that stored into peers' memory (parameter publish).
+__global__ void peer_barrier_kernel(ArPeers peers, int rank, int world, int chan, const int* epoch_base, int epoch_off,
+                                    int* status, unsigned long long limit_ns) {
+  const int epoch = *epoch_base + epoch_off;
+  __threadfence_system();
+  for (int r = 0; r < world; ++r) st_release_sys(peers.flags[r] + chan * B200_MAX_RANKS + rank, epoch);
+  bool ok = true;
+  for (int r = 0; r < world && ok; ++r)
+    ok = wait_flag_ge(peers.flags[rank] + chan * B200_MAX_RANKS + r, epoch, limit_ns);
+  if (!ok) report(status, ST_TIMEOUT_PEER);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long long n, float scale,
-                              const int* epoch_base, int epoch_off, int final_bucket, int use_multimem, int blocks, int* state_i, float* state_f,
-                              int* status, unsigned long long limit_ns, cudaStream_t stream) {
+                              const int* epoch_base, int epoch_off, int final_bucket, int publish, int use_multimem,
+                              int blocks, int* state_i, float* state_f, int* status, unsigned long long limit_ns,
+                              cudaStream_t stream) {
   if (world < 1 || world > B200_MAX_RANKS || rank < 0 || rank >= world) return -1;
   if (n <= 0) return 0;
   if ((n & 3) != 0 || (off & 3) != 0) return -1;
@@ -199,16 +221,30 @@ extern "C" int b200_allreduce(const B200Peers* p, int rank, int world, long long
   float* mc = reinterpret_cast<float*>(p->mc_buf);
   if (use_multimem)
     allreduce_kernel<true><<<blocks, AR_THREADS, 0, stream>>>(ap, mc, rank, world, off, n, scale, epoch_base, epoch_off,
-                                                               final_bucket,
-                                                               state_i, state_f, status, limit_ns);
+                                                               final_bucket, publish, state_i, state_f, status,
+                                                               limit_ns);
   else
     allreduce_kernel<false><<<blocks, AR_THREADS, 0, stream>>>(ap, mc, rank, world, off, n, scale, epoch_base, epoch_off,
-                                                               final_bucket,
-                                                                state_i, state_f, status, limit_ns);
+                                                                final_bucket, publish, state_i, state_f, status,
+                                                                limit_ns);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int b200_clip_coef_multi(const float* parts, int world, float max_norm, float* coef, cudaStream_t stream) {
   clip_coef_multi_kernel<<<1, 1, 0, stream>>>(parts, world, max_norm, coef);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_peer_barrier(const B200Peers* p, int rank, int world, int chan, const int* epoch_base, int epoch_off,
+                                 int* status, unsigned long long limit_ns, cudaStream_t stream) {
+  if (world < 1 || world > B200_MAX_RANKS || rank < 0 || rank >= world || chan < 0 || chan > 3) return -1;
+  ArPeers ap;
+  for (int r = 0; r < B200_MAX_RANKS; ++r) {
+    ap.buf[r] = nullptr;
+    ap.norm[r] = nullptr;
+    ap.flags[r] = reinterpret_cast<int*>(p->flags[r]);
+  }
+  if (limit_ns == 0) limit_ns = 10000000000ull;
+  peer_barrier_kernel<<<1, 1, 0, stream>>>(ap, rank, world, chan, epoch_base, epoch_off, status, limit_ns);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

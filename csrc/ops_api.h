@@ -56,8 +56,11 @@ int b200_sumsq_blocks(long long n);  // scratch: float[blocks]
 int b200_sumsq(const float* g, long long n, float* scratch, float* out, int accumulate, cudaStream_t stream);
 int b200_clip_coef(const float* sumsq, float max_norm, float* coef, cudaStream_t stream);
 // hyper: device float[3] = {lr, 1 - beta1^t, 1 - beta2^t}
+// p16_peers (optional, `world` entries): the same slice of every rank's bf16 compute copy; when given the
+// new weights are also stored there (sharded optimizer: update + parameter all-gather in one pass)
 int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, const float* hyper, float beta1,
-               float beta2, float eps, float wd, const float* grad_coef, cudaStream_t stream);
+               float beta2, float eps, float wd, const float* grad_coef, void* const* p16_peers, int world,
+               cudaStream_t stream);
 int b200_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 
 // ---- comm/allreduce.cu
@@ -72,8 +75,11 @@ typedef struct B200Peers {
 // epoch = *epoch_base + epoch_off must grow with every launch and agree across ranks.
 // state_i: int[2], state_f: float[2], both zero-initialised local scratch.
 int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long long n, float scale,
-                   const int* epoch_base, int epoch_off, int final_bucket, int use_multimem, int blocks, int* state_i,
-                   float* state_f, int* status, unsigned long long limit_ns, cudaStream_t stream);
+                   const int* epoch_base, int epoch_off, int final_bucket, int publish, int use_multimem, int blocks,
+                   int* state_i, float* state_f, int* status, unsigned long long limit_ns, cudaStream_t stream);
+// flags must then hold 4 * B200_MAX_RANKS words; channels 0/1 belong to b200_allreduce
+int b200_peer_barrier(const B200Peers* p, int rank, int world, int chan, const int* epoch_base, int epoch_off,
+                      int* status, unsigned long long limit_ns, cudaStream_t stream);
 int b200_clip_coef_multi(const float* parts, int world, float max_norm, float* coef, cudaStream_t stream);
 
 // ---- moe/ep.cu (expert parallelism over peer memory; pointer arrays have B200_MAX_RANKS entries)

@@ -63,7 +63,7 @@ class TrainEngine:
     def __init__(self, model: nn.Module, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, process_group=None,
                  overlap_grad_reduce: bool = True, device: torch.device | str | None = None,
-                 comm: str | None = None):
+                 comm: str | None = None, shard_optimizer: bool = False):
         self.model = model
         self.lr, self.betas, self.eps = lr, betas, eps
         self.weight_decay, self.max_grad_norm = weight_decay, max_grad_norm
@@ -117,9 +117,21 @@ class TrainEngine:
             self.g32 = self._peers.grad
         else:
             self.g32 = torch.zeros(self.total, dtype=torch.float32, device=dev)
-        self.m = torch.zeros(self.total, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(self.total, dtype=torch.float32, device=dev)
-        self.p16 = torch.zeros(self.total, dtype=torch.bfloat16, device=dev) if self.cuda else None
+        # sharded optimizer (ZeRO stage 1 over the NVLink domain): each rank keeps Adam moments only for
+        # the slice of every gradient bucket it reduces, updates that slice and stores the new bf16
+        # weights into every rank's compute copy
+        self.sharded = bool(shard_optimizer) and self.world > 1
+        if self.sharded and self.comm != "p2p":
+            raise ValueError("shard_optimizer needs the peer-memory gradient path (CUDA, comm='p2p', <= 8 ranks)")
+        self._layer_offs = self.layer_offsets()
+        self._plan_segments()
+        self.m = torch.zeros(self._moment_numel, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self._moment_numel, dtype=torch.float32, device=dev)
+        if self.sharded:
+            self._peers.add_param_copy(self.total)
+            self.p16 = self._peers.p16
+        else:
+            self.p16 = torch.zeros(self.total, dtype=torch.bfloat16, device=dev) if self.cuda else None
         for s in slots:
             view = self.p32[s.offset:s.offset + s.numel].view(s.param.shape)
             view.copy_(s.param.data)
@@ -153,7 +165,6 @@ class TrainEngine:
                 pb = self._peers
                 self._fused_ar = FusedAllReduce(self._ext, pb.grad_ptrs, pb.flag_ptrs, pb.norm_ptrs, pb.multicast_ptr,
                                                 pb.rank, pb.world, dev, _G.status_word(dev))
-        self._layer_offs = self.layer_offsets()
         inner = getattr(self.model, "model", None)
         if inner is not None and hasattr(inner, "_boundary_fn"):
             inner._boundary_fn = self.boundary if self.overlap else None
@@ -185,6 +196,67 @@ class TrainEngine:
                 mod._fused_qkv = adjacent([mod.q_proj.weight, mod.k_proj.weight, mod.v_proj.weight])
             elif isinstance(mod, DenseMLP):
                 mod._fused_gate_up = adjacent([mod.gate_proj.weight, mod.up_proj.weight])
+
+    def bucket_ranges(self) -> list[tuple[int, int]]:
+        """The (lo, hi) slices of the replicated, decayed region in the order backward hands them to the
+        reducer: one per decoder layer from the last to the first, then whatever lies below layer 0."""
+        d = self.decay_end
+        if d == 0:
+            return []
+        if not self.overlap:
+            return [(0, d)]
+        out, upto = [], d
+        for off in reversed([o for o in self._layer_offs if o is not None]):
+            if off < upto:
+                out.append((off, upto))
+                upto = off
+        if upto > 0:
+            out.append((0, upto))
+        return out
+
+    def owned_slice(self, lo: int, hi: int, rank: int | None = None) -> tuple[int, int]:
+        """The part of bucket [lo, hi) that `rank` reduces and updates; same arithmetic as the reduce kernel
+        (whole float4 groups, ceil-divided over the ranks)."""
+        rank = self.rank if rank is None else rank
+        n4 = (hi - lo) // 4
+        per = (n4 + self.world - 1) // self.world
+        a = min(per * rank, n4)
+        b = min(a + per, n4)
+        return lo + 4 * a, lo + 4 * b
+
+    def _plan_segments(self) -> None:
+        """Update segments (p_lo, p_hi, m_lo, weight_decay, kind); kind: 0 replicated, 1 expert shard,
+        2 owned slice of a sharded bucket.  `m_lo` indexes the moment buffers."""
+        self.rank = dist.get_rank(self.group) if self.world > 1 else 0
+        d, pe, wd = self.decay_end, self.ep_end, self.weight_decay
+        segs = []
+        if not self.sharded:
+            if d > 0:
+                segs.append((0, d, 0, wd, 0))
+            if pe > d:
+                segs.append((d, pe, d, wd, 1))
+            if self.total > pe:
+                segs.append((pe, self.total, pe, 0.0, 0))
+            self._moment_numel = self.total
+        else:
+            moff = 0
+            for lo, hi in self.bucket_ranges():
+                a, b = self.owned_slice(lo, hi)
+                if b > a:
+                    segs.append((a, b, moff, wd, 2))
+                    moff += b - a
+            if pe > d:
+                segs.append((d, pe, moff, wd, 1))
+                moff += pe - d
+            if self.total > pe:
+                segs.append((pe, self.total, moff, 0.0, 0))
+                moff += self.total - pe
+            self._moment_numel = moff
+        self._segments = segs
+        self._bucket_set = set(self.bucket_ranges())
+
+    def _moment_index(self, kind_filter=None):
+        return [(p_lo, p_hi, m_lo) for p_lo, p_hi, m_lo, _, k in self._segments if kind_filter is None or k in kind_filter]
 
     def _slot_of(self, p) -> Slot | None:
         for s in self.slots:
@@ -228,13 +300,15 @@ class TrainEngine:
         if self.world == 1 or hi <= lo:
             return
         self._zero_dead(lo, hi)
+        if self.sharded and hi <= self.decay_end and (lo, hi) not in self._bucket_set:
+            raise RuntimeError(f"gradient bucket [{lo}, {hi}) is not one of the planned optimizer shards")
         chunk = self.g32[lo:hi]
         if self.cuda and self._fused_ar is not None:
             ev = torch.cuda.Event()
             ev.record()
             with torch.cuda.stream(self._comm_stream):
                 self._comm_stream.wait_event(ev)
-                self._fused_ar.reduce(lo, hi - lo, final)
+                self._fused_ar.reduce(lo, hi - lo, final, publish=not (self.sharded and hi <= self.decay_end))
         elif self.cuda:
             ev = torch.cuda.Event()
             ev.record()
@@ -354,17 +428,16 @@ class TrainEngine:
             else:
                 e.sumsq(self.g32, self._ss_scratch, self._norm_ss, False)
                 e.clip_coef(self._norm_ss, float(self.max_grad_norm or 0.0), self._coef)
-            d, pe = self.decay_end, self.ep_end
-            if d > 0:
-                e.adamw(self.p32[:d], self.g32[:d], self.m[:d], self.v[:d], self.p16[:d], self._hyper, b1, b2, self.eps,
-                        self.weight_decay, self._coef)
-            if pe > d:  # expert shards: same clip coefficient, times the 1/world of the data-parallel mean
+            if self.ep_end > self.decay_end:  # expert shards: clip coefficient times the 1/world of the mean
                 torch.div(self._coef[:1], float(self.world), out=self._coef_ep)
-                e.adamw(self.p32[d:pe], self.g32[d:pe], self.m[d:pe], self.v[d:pe], self.p16[d:pe], self._hyper, b1, b2,
-                        self.eps, self.weight_decay, self._coef_ep)
-            if self.total > pe:
-                e.adamw(self.p32[pe:], self.g32[pe:], self.m[pe:], self.v[pe:], self.p16[pe:], self._hyper, b1, b2,
-                        self.eps, 0.0, self._coef)
+            for p_lo, p_hi, m_lo, wd, kind in self._segments:
+                n = p_hi - p_lo
+                e.adamw(self.p32[p_lo:p_hi], self.g32[p_lo:p_hi], self.m[m_lo:m_lo + n], self.v[m_lo:m_lo + n],
+                        None if kind == 2 else self.p16[p_lo:p_hi], self._hyper, b1, b2, self.eps, wd,
+                        self._coef_ep if kind == 1 else self._coef,
+                        [q + 2 * p_lo for q in self._peers.p16_ptrs] if kind == 2 else [])
+            if self.sharded:  # every rank's stores into this rank's bf16 copy have landed after this
+                self._fused_ar.param_barrier()
             self._grad_norm = self._coef[1]
         else:
             norm = self.g32.norm()
@@ -384,24 +457,69 @@ class TrainEngine:
     def grad_norm(self) -> torch.Tensor | None:
         return self._grad_norm
 
+    def full_moments(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """Adam moments in parameter layout.  Collective when the optimizer is sharded: every rank fills in
+        what it owns and a sum over ranks assembles the rest."""
+        if not self.sharded:
+            return self.m, self.v
+        outs = []
+        for src in (self.m, self.v):
+            full = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+            for p_lo, p_hi, m_lo, _, kind in self._segments:
+                if kind == 2 or self.rank == 0 or kind == 1:  # replicated tails: taken from rank 0 only
+                    full[p_lo:p_hi].copy_(src[m_lo:m_lo + p_hi - p_lo])
+            d, pe = self.decay_end, self.ep_end
+            if d > 0:
+                dist.all_reduce(full[:d], group=self.group)
+            if self.total > pe:
+                dist.all_reduce(full[pe:], group=self.group)
+            outs.append(full)
+        return outs[0], outs[1]
+
+    def sync_master(self) -> None:
+        """Sharded optimizer: bring the fp32 master weights of every rank up to date (each rank only
+        advances the slices it owns).  Collective; call before reading `state_dict()`."""
+        if not self.sharded or self.decay_end == 0:
+            return
+        own = torch.zeros(self.decay_end, dtype=torch.float32, device=self.device)
+        for p_lo, p_hi, _, _, kind in self._segments:
+            if kind == 2:
+                own[p_lo:p_hi].copy_(self.p32[p_lo:p_hi])
+        dist.all_reduce(own, group=self.group)
+        # float4 remainders of a bucket belong to nobody and never change
+        mask = torch.zeros(self.decay_end, dtype=torch.bool, device=self.device)
+        for lo, hi in self.bucket_ranges():
+            mask[lo:lo + (hi - lo) // 4 * 4] = True
+        self.p32[:self.decay_end] = torch.where(mask, own, self.p32[:self.decay_end])
+
     def optimizer_state_dict(self) -> dict:
         st = {"step": self.step_count, "lr": self.lr, "state": {}}
+        m, v = self.full_moments()
         for s in self.slots:
             sl = slice(s.offset, s.offset + s.numel)
-            st["state"][s.name] = {"exp_avg": self.m[sl].view(s.param.shape).detach().cpu().clone(),
-                                   "exp_avg_sq": self.v[sl].view(s.param.shape).detach().cpu().clone()}
+            st["state"][s.name] = {"exp_avg": m[sl].view(s.param.shape).detach().cpu().clone(),
+                                   "exp_avg_sq": v[sl].view(s.param.shape).detach().cpu().clone()}
         return st
 
     def load_optimizer_state_dict(self, st: dict) -> None:
         self.step_count = int(st["step"])
         self.lr = float(st.get("lr", self.lr))
+        if self.sharded:
+            m = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+            v = torch.zeros_like(m)
+        else:
+            m, v = self.m, self.v
         for name, d in st["state"].items():
             s = self.by_name.get(name)
             if s is None:
                 continue
             sl = slice(s.offset, s.offset + s.numel)
-            self.m[sl].copy_(d["exp_avg"].reshape(-1))
-            self.v[sl].copy_(d["exp_avg_sq"].reshape(-1))
+            m[sl].copy_(d["exp_avg"].reshape(-1))
+            v[sl].copy_(d["exp_avg_sq"].reshape(-1))
+        if self.sharded:
+            for p_lo, p_hi, m_lo, _, _ in self._segments:
+                self.m[m_lo:m_lo + p_hi - p_lo].copy_(m[p_lo:p_hi])
+                self.v[m_lo:m_lo + p_hi - p_lo].copy_(v[p_lo:p_hi])
 
     def load_model_state_dict(self, sd: dict, strict: bool = True) -> None:
         self.model.load_state_dict(sd, strict=strict)

@@ -27,7 +27,7 @@ class PeerBuffers:
         if self.world > MAX_RANKS:
             raise ValueError(f"the peer-memory kernels support at most {MAX_RANKS} ranks (one NVLink domain)")
         self.grad = sm.empty(numel, dtype=torch.float32, device=device)
-        self.flags = sm.empty(2 * MAX_RANKS, dtype=torch.int32, device=device)
+        self.flags = sm.empty(4 * MAX_RANKS, dtype=torch.int32, device=device)
         self.norm = sm.empty(MAX_RANKS, dtype=torch.float32, device=device)
         for t in (self.grad, self.flags, self.norm):
             t.zero_()
@@ -47,7 +47,23 @@ class PeerBuffers:
             mc = int(getattr(hg, "multicast_ptr", 0) or 0)
         # NVLS only on request to opt out: MOE_B200_MULTIMEM=0 forces plain peer loads / stores
         self.multicast_ptr = mc if os.environ.get("MOE_B200_MULTIMEM", "1") != "0" else 0
+        self.group = group
+        self.p16 = None
+        self.p16_ptrs: list[int] = []
         dist.barrier(group)
+
+    def add_param_copy(self, numel: int) -> None:
+        """A symmetric bf16 parameter copy: with a sharded optimizer the owner of a slice stores the updated
+        weights into every rank's copy."""
+        import torch.distributed._symmetric_memory as sm
+
+        self.p16 = sm.empty(numel, dtype=torch.bfloat16, device=self.grad.device)
+        self.p16.zero_()
+        torch.cuda.synchronize(self.grad.device)
+        h = sm.rendezvous(self.p16, self.group)
+        self._handles = self._handles + (h,)
+        self.p16_ptrs = [int(p) for p in h.buffer_ptrs]
+        dist.barrier(self.group)
 
 
 class FusedAllReduce:
@@ -64,10 +80,15 @@ class FusedAllReduce:
         self.blocks, self.limit_ns = blocks, limit_ns
         self.launched = 0  # buckets since the last `end_step`
 
-    def reduce(self, off: int, n: int, final_bucket: bool) -> None:
+    def reduce(self, off: int, n: int, final_bucket: bool, publish: bool = True) -> None:
         self.ext.allreduce(self.grad_ptrs, self.flag_ptrs, self.norm_ptrs, self.mc, self.rank, self.world, off, n,
-                           1.0 / self.world, self.epoch_base, self.launched, final_bucket, self.mc != 0,
+                           1.0 / self.world, self.epoch_base, self.launched, final_bucket, publish, self.mc != 0,
                            self.blocks, self.state_i, self.state_f, self.status, self.limit_ns)
+        self.launched += 1
+
+    def param_barrier(self) -> None:
+        """All ranks' parameter stores into this rank's memory are complete once this kernel has run."""
+        self.ext.peer_barrier(self.flag_ptrs, self.rank, self.world, 2, self.epoch_base, self.launched, self.status)
         self.launched += 1
 
     def end_step(self) -> None:

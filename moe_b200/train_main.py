@@ -169,15 +169,20 @@ def main(argv=None) -> None:
     bias_interp = cfg["model"].get("bias_interpolation", False)
     seq_coef = cfg["model"].get("seq_aux_loss_coef", 0.0) or 0.0
     pcfg = cfg.get("parallel", {})
-    if pcfg.get("mode", "ddp") not in ("ddp",):
-        raise ValueError(f"parallel.mode={pcfg.get('mode')!r} is not available in this build (ddp only)")
+    # "ddp": replicated optimizer state; "zero" (alias "fsdp"): Adam moments and the update sharded over the
+    # ranks, new bf16 weights stored to every rank by the update kernel
+    pmode = str(pcfg.get("mode", "ddp")).lower()
+    if pmode not in ("ddp", "zero", "fsdp"):
+        raise ValueError(f"parallel.mode={pcfg.get('mode')!r}: expected ddp, zero or fsdp")
+    shard_opt = pmode in ("zero", "fsdp") and world > 1 and device == "cuda"
     if main_proc:
         print(f"\n{'=' * 60}\n  Model     : {mtype}\n  Params    : {params['total'] / 1e9:.3f}B total  |  "
-              f"{expert_params / 1e9:.3f}B expert\n  Dist type : {'DDP' if world > 1 else 'single'} ({device})\n"
+              f"{expert_params / 1e9:.3f}B expert\n  Dist type : {('ZeRO-1' if shard_opt else 'DDP') if world > 1 else 'single'} ({device})\n"
               f"  Precision : {'bf16 compute, fp32 master' if device == 'cuda' else 'fp32'}\n  GPUs      : {world}\n"
               f"{'=' * 60}\n", flush=True)
 
-    trainer = Trainer(model, tcfg, is_moe=not is_dense, overlap_grad_reduce=pcfg.get("overlap", True))
+    trainer = Trainer(model, tcfg, is_moe=not is_dense, overlap_grad_reduce=pcfg.get("overlap", True),
+                      shard_optimizer=shard_opt)
     trainer.engine.broadcast_parameters(0)
     dataset = build_dataset(ddict, cfg["model"]["vocab_size"], rank, world)
     if resume_from:

@@ -94,6 +94,7 @@ def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | N
     # expert-parallel shards are gathered into whole banks (all ranks take part), so the files do
     # not depend on the expert-parallel size of the run that wrote them
     shards = {n: getattr(p, "_ep_shard", None) for n, p in trainer.model.named_parameters()}
+    trainer.engine.sync_master()  # sharded optimizer: every rank's fp32 weights brought up to date first
     sd = {}
     seen = {}
     for k, v in trainer.model.state_dict().items():

@@ -42,7 +42,7 @@ def test_allreduce_emulated_ranks(world, n):
         half = (n // 2) // 4 * 4
         for (off, cnt, final) in ((0, half, False), (half, n - half, True)):  # two buckets per step
             e.allreduce([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], [x.data_ptr() for x in norms], 0,
-                        r, world, off, cnt, 1.0 / world, epoch, 0, final, False, 16, si, sf, st, 0)
+                        r, world, off, cnt, 1.0 / world, epoch, 0, final, True, False, 16, si, sf, st, 0)
     torch.cuda.synchronize()
     G.check_status()
     for b in bufs:
@@ -64,7 +64,7 @@ def test_wait_that_nobody_satisfies_becomes_a_status_code():
     epoch = torch.ones(1, dtype=torch.int32, device="cuda")
     si, sf = torch.zeros(2, dtype=torch.int32, device="cuda"), torch.zeros(2, device="cuda")
     e.allreduce([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], [x.data_ptr() for x in norms], 0, 0, 2, 0,
-                4096, 0.5, epoch, 0, True, False, 4, si, sf, st, 50_000_000)  # 50 ms limit
+                4096, 0.5, epoch, 0, True, True, False, 4, si, sf, st, 50_000_000)  # 50 ms limit
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="peer wait"):
         G.check_status()
@@ -72,6 +72,39 @@ def test_wait_that_nobody_satisfies_becomes_a_status_code():
     y = torch.ones(4, device="cuda") * 2  # the context is still usable
     assert float(y.sum()) == 8.0
     G.check_status()  # the word was cleared
+
+
+def test_adamw_publishes_bf16_weights_to_every_rank():
+    from moe_b200.ops import _ext, oracle
+
+    e = _ext.load()
+    n = 4096 * 3
+    p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    copies = [torch.zeros(n + 64, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    hyper = torch.tensor([1e-2, 0.1, 0.05], device="cuda")
+    coef = torch.ones(2, device="cuda")
+    p_ref, m_ref, v_ref = p.clone(), m.clone(), v.clone()
+    oracle.adamw_step_(p_ref, g, m_ref, v_ref, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1)
+    e.adamw(p, g, m, v, None, hyper, 0.9, 0.95, 1e-8, 0.1, coef, [c.data_ptr() + 2 * 64 for c in copies])
+    torch.cuda.synchronize()
+    assert torch.allclose(p, p_ref, atol=1e-6)
+    for c in copies:
+        assert torch.equal(c[64:], p.to(torch.bfloat16)) and float(c[:64].abs().sum()) == 0.0
+
+
+def test_peer_barrier_emulated_and_bounded():
+    from moe_b200.ops import _ext
+    from moe_b200.ops import gemm as G
+
+    e = _ext.load()
+    st = G.status_word(torch.device("cuda"))
+    epoch = torch.full((1,), 7, dtype=torch.int32, device="cuda")
+    flags = [torch.full((32,), 100, dtype=torch.int32, device="cuda") for _ in range(2)]  # peers already there
+    e.peer_barrier([f.data_ptr() for f in flags], 0, 2, 2, epoch, 1, st)
+    torch.cuda.synchronize()
+    G.check_status()
+    assert int(flags[1][16]) == 8 and int(flags[0][16]) == 8  # rank 0 posted epoch 7 + 1 on channel 2 everywhere
 
 
 def _free_port():
@@ -97,9 +130,10 @@ def _ddp_rank(rank, world, port, out_dir):
     g = torch.Generator().manual_seed(0)
     full = [torch.randint(0, 2048, (4, 128), generator=g) for _ in range(3)]
     res = {}
-    for comm, overlap in (("nccl", False), ("p2p", False), ("p2p", True)):
+    for comm, overlap in (("nccl", False), ("p2p", False), ("p2p", True), ("zero", False), ("zero", True)):
         model, _ = build_model(tiny_cfg("dense"), seed=3, device=f"cuda:{rank}")
-        eng = TrainEngine(model, lr=1e-3, comm=comm, overlap_grad_reduce=overlap)
+        eng = TrainEngine(model, lr=1e-3, comm="p2p" if comm == "zero" else comm, overlap_grad_reduce=overlap,
+                          shard_optimizer=comm == "zero")
         for b in full:
             mine = b[rank * 2:(rank + 1) * 2].cuda()
             eng.zero_grad()
@@ -107,6 +141,16 @@ def _ddp_rank(rank, world, port, out_dir):
             gn = eng.step()
         torch.cuda.synchronize()
         G.check_status()
+        if comm == "zero":
+            assert eng.m.numel() < 0.6 * eng.total  # moments really are sharded
+            eng.sync_master()
+            st = eng.optimizer_state_dict()
+            res[(comm, overlap, "p16")] = (eng.p16.clone().cpu(), 0.0)
+            res[(comm, overlap, "m")] = (torch.cat([v["exp_avg"].reshape(-1) for v in st["state"].values()]), 0.0)
+        elif comm == "p2p":
+            st = eng.optimizer_state_dict()
+            res[(comm, overlap, "p16")] = (eng.p16.clone().cpu(), 0.0)
+            res[(comm, overlap, "m")] = (torch.cat([v["exp_avg"].reshape(-1) for v in st["state"].values()]), 0.0)
         res[(comm, overlap)] = (eng.p32.clone().cpu(), float(gn))
         dist.barrier()
     torch.save(res, os.path.join(out_dir, f"rank{rank}.pt"))
@@ -126,6 +170,15 @@ def test_two_gpu_fused_allreduce_matches_nccl(tmp_path):
         d = (a[key][0] - ref).abs()
         assert d.max() < 5e-3 and (d > 1e-4).float().mean() < 1e-2, key
         assert abs(a[key][1] - gn) < 2e-2 * gn
+    # sharded optimizer: same arithmetic per element as the replicated one; the only difference is the
+    # order in which blocks add their partial sums of squares (atomics), i.e. the last bits of the clip factor
+    for overlap in (False, True):
+        for what in ((), ("m",)):
+            z, r = a[("zero", overlap, *what)], a[("p2p", overlap, *what)]
+            assert (z[0] - r[0]).abs().max() < 1e-5, (overlap, what)
+        z, r = a[("zero", overlap, "p16")][0].float(), a[("p2p", overlap, "p16")][0].float()
+        assert (z - r).abs().max() < 1e-2 and (z != r).float().mean() < 1e-3
+        assert abs(a[("zero", overlap)][1] - a[("p2p", overlap)][1]) < 1e-4 * gn
 
 
 def _ep_rank(rank, world, port, out_dir):
