@@ -137,6 +137,23 @@ def case_qknorm_rope(small):
     return dict(shape=[B, S, nh, nkv, hd], ms=ms, bytes=2.0 * qkv.numel() * 2)
 
 
+def case_flash_attn_fwd(small):
+    import math
+
+    from moe_b200.ops import _ext
+    from moe_b200.ops import gemm as G
+
+    e = _ext.load()
+    B, S, nh, nkv = (2, 2048, 16, 8) if small else (8, 2048, 16, 8)
+    q, k, v = bf(B, S, nh, 128), bf(B, S, nkv, 128), bf(B, S, nkv, 128)
+    o, lse = torch.empty_like(q), torch.empty(B, nh, S, device="cuda")
+    st = G.status_word(q.device)
+    ms = timeit(lambda: e.flash_fwd(q, k, v, o, lse, 1 / math.sqrt(128), st))
+    ref = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True))
+    return dict(shape=[B, S, nh, nkv, 128], ms=ms, flops=2.0 * B * nh * S * S * 128, sdpa_ms=ref)
+
+
 def case_allreduce_emulated(small):
     """Eight ranks emulated on one GPU (flags pre-set): measures the kernel's local memory path only."""
     from moe_b200.ops import _ext

@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include "ops_api.h"
+#include "attn/attn_api.h"
 
 #include <cstring>
 #include <vector>
@@ -84,6 +85,19 @@ void qknorm_rope_bwd(const Tensor& dq, const Tensor& dk, const Tensor& dv, const
                              qw.data_ptr<float>(), kw.data_ptr<float>(), cs.data_ptr<float>(), dqkv.data_ptr(),
                              dw_part.data_ptr<float>(), dqw.data_ptr<float>(), dkw.data_ptr<float>(),
                              accumulate ? 1 : 0, T, (int)S, (int)nh, (int)nkv, (int)hd, stream()), "qknorm_rope_bwd");
+}
+
+// ---------------------------------------------------------------- attention
+void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse, double scale, Tensor& status) {
+  bf16c(q, "q"); bf16c(k, "k"); bf16c(v, "v"); bf16c(o, "o"); f32c(lse, "lse"); i32c(status, "status");
+  need(q.dim() == 4 && k.dim() == 4 && q.size(3) == 128 && k.size(3) == 128, "flash attention: [B,S,h,128] expected");
+  need(k.sizes() == v.sizes() && o.sizes() == q.sizes(), "flash attention: shape mismatch");
+  const int B = (int)q.size(0), S = (int)q.size(1), nh = (int)q.size(2), nkv = (int)k.size(2);
+  need(k.size(0) == B && k.size(1) == S, "flash attention: k/v batch or length");
+  need(lse.numel() == (int64_t)B * nh * S, "flash attention: lse size");
+  c10::cuda::CUDAGuard g(q.device());
+  rc_ok(b200_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, S, nh, nkv,
+                       (float)scale, status.data_ptr<int>(), stream()), "flash_fwd");
 }
 
 // ------------------------------------------------------------------- router
@@ -305,6 +319,7 @@ void bind_ops(pybind11::module_& m) {
   m.def("qknorm_rope_blocks", &qknorm_rope_blocks);
   m.def("qknorm_rope_fwd", &qknorm_rope_fwd);
   m.def("qknorm_rope_bwd", &qknorm_rope_bwd);
+  m.def("flash_fwd", &flash_fwd);
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);
   m.def("moe_plan_blocks", &moe_plan_blocks);

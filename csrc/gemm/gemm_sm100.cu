@@ -1,6 +1,7 @@
 // Host side of the tcgen05 GEMM family: tensor-map construction and kernel dispatch.
 #include "gemm_api.h"
 #include "gemm_sm100.cuh"
+#include "../common/tma_host.h"
 
 #include <cudaTypedefs.h>
 #include <cstdio>
@@ -39,7 +40,7 @@ struct MapKeyHash {
 };
 
 // bf16 tensor, up to 3 dims (inner first), 128B swizzle, zero fill out of bounds.
-static int make_map(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes,
+int make_map(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes,
                     uint64_t s2_bytes, uint32_t b0, uint32_t b1) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;

@@ -10,6 +10,9 @@ engine the same functions cast on the fly and return ordinary gradients.
 """
 from __future__ import annotations
 
+import math
+import os
+
 import torch
 
 from . import _ext
@@ -279,11 +282,79 @@ def qk_norm_rope(qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps):
 
 
 # ------------------------------------------------------------------- attention
-def attention(q, k, v):
-    """Causal GQA attention, `[B,S,h,hd]` layout.  Library kernel (cuDNN / flash via SDPA) for now."""
+def _sdpa(q, k, v):
     o = torch.nn.functional.scaled_dot_product_attention(
         q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True)
     return o.transpose(1, 2).contiguous()
+
+
+def flash_supported(q, k) -> bool:
+    """Shapes the tcgen05 forward kernel covers: head_dim 128, length a multiple of 128, an even number of
+    query heads per key/value head (a CTA works on two query heads that share their key/value tiles)."""
+    B, S, nh, hd = q.shape
+    nkv = k.shape[2]
+    return (q.is_cuda and q.dtype == BF16 and hd == 128 and S % 128 == 0 and nh % nkv == 0
+            and (nh // nkv) % 2 == 0)
+
+
+_ATTN_STATE = {"library_backward_ok": None, "dummy": {}}
+
+
+class FlashAttnFn(torch.autograd.Function):
+    """Causal GQA attention.  Forward: `csrc/attn/flash_fwd.cu` (returns the base-2 log-sum-exp per row).
+    Backward: the cuDNN flash-attention backward kernel (a library call), which takes the forward's
+    output and natural-log log-sum-exp as inputs; if that entry point is not usable in the running
+    torch build, the gradients are obtained by differentiating a recomputed library forward."""
+
+    @staticmethod
+    def forward(ctx, q, k, v):
+        B, S, nh, hd = q.shape
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o = torch.empty_like(q)
+        lse2 = torch.empty(B, nh, S, dtype=torch.float32, device=q.device)
+        scale = 1.0 / math.sqrt(hd)
+        ext().flash_fwd(q, k, v, o, lse2, scale, G.status_word(q.device))
+        ctx.save_for_backward(q, k, v, o, lse2)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse2 = ctx.saved_tensors
+        B, S, nh, hd = q.shape
+        do = do.contiguous()
+        st = _ATTN_STATE
+        if st["library_backward_ok"] is not False:
+            try:
+                key = q.device
+                if key not in st["dummy"]:
+                    st["dummy"][key] = torch.zeros((), dtype=torch.int64, device=q.device)
+                z = st["dummy"][key]
+                lse = (lse2 * math.log(2.0)).unsqueeze(-1)
+                g = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
+                    do.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), o.transpose(1, 2),
+                    lse, z, z, None, None, None, S, S, 0.0, True, scale=ctx.scale)
+                st["library_backward_ok"] = True
+                return g[0].transpose(1, 2), g[1].transpose(1, 2), g[2].transpose(1, 2)
+            except (RuntimeError, TypeError, AttributeError) as ex:
+                if st["library_backward_ok"]:
+                    raise
+                import warnings
+
+                warnings.warn(f"cuDNN attention backward entry point unavailable ({ex}); recomputing through SDPA")
+                st["library_backward_ok"] = False
+        with torch.enable_grad():
+            qq, kk, vv = (t.detach().requires_grad_() for t in (q, k, v))
+            return torch.autograd.grad(_sdpa(qq, kk, vv), (qq, kk, vv), do)
+
+
+def attention(q, k, v):
+    """Causal GQA attention, `[B,S,h,hd]` layout.  Own forward kernel where it applies (see
+    `flash_supported`), the library's scaled-dot-product attention otherwise or when
+    MOE_B200_ATTN=sdpa."""
+    if flash_supported(q, k) and os.environ.get("MOE_B200_ATTN", "own") != "sdpa":
+        return FlashAttnFn.apply(q, k, v)
+    return _sdpa(q, k, v)
 
 
 # ---------------------------------------------------------------------- router

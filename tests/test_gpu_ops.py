@@ -255,3 +255,37 @@ def test_adamw_and_norm(dev):
     assert abs(coef[1].item() - g.norm().item()) < 1e-3 * g.norm().item()
     assert relerr(p, p2) < 1e-6 and relerr(m, m2) < 1e-5 and relerr(v, v2) < 1e-5
     assert relerr(p16, p2) < 5e-3
+
+
+@pytest.mark.parametrize("B,S,nh,nkv,spread", [(1, 128, 2, 1, 1.0), (2, 384, 4, 2, 1.0), (1, 1024, 8, 1, 1.0),
+                                               (2, 512, 4, 2, 6.0)])
+def test_flash_attention_forward_and_grads(dev, B, S, nh, nkv, spread):
+    """Own tcgen05 forward (output and log-sum-exp) and the gradients of `ops.attention` against the fp32
+    statement; `spread` widens the score range so that the lazy accumulator rescale in TMEM is exercised."""
+    from moe_b200.ops import _ext, oracle
+    from moe_b200.ops import functional as F
+    from moe_b200.ops import gemm as G
+
+    q, k, v = _bf(B, S, nh, 128, scale=spread), _bf(B, S, nkv, 128, scale=spread), _bf(B, S, nkv, 128)
+    assert F.flash_supported(q, k)
+    o = torch.empty_like(q)
+    lse2 = torch.empty(B, nh, S, device=dev)
+    _ext.load().flash_fwd(q, k, v, o, lse2, 1 / math.sqrt(128), G.status_word(dev))
+    _sync_status()
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    ref = oracle.causal_gqa_attention(qf, kf, vf)
+    assert relerr(o, ref) < 1.5e-2
+    kk = kf.detach().repeat_interleave(nh // nkv, 2)
+    sc = torch.einsum("bqhd,bkhd->bhqk", qf.detach(), kk) / math.sqrt(128)
+    sc = sc.masked_fill(torch.ones(S, S, dtype=torch.bool, device=dev).triu(1), float("-inf"))
+    assert (lse2 * math.log(2) - torch.logsumexp(sc, -1)).abs().max() < 2e-3
+    # through autograd (own forward, library backward)
+    do = _bf(B, S, nh, 128)
+    q2, k2, v2 = (t.clone().requires_grad_() for t in (q, k, v))
+    out = F.attention(q2, k2, v2)
+    assert torch.equal(out, o)
+    out.backward(do)
+    ref.backward(do.float())
+    _sync_status()
+    for a, b in ((q2.grad, qf.grad), (k2.grad, kf.grad), (v2.grad, vf.grad)):
+        assert relerr(a, b) < 2e-2
