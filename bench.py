@@ -42,6 +42,7 @@ def parse_args():
     ap.add_argument("--ep", action="store_true", help="shard the experts over all ranks (expert parallelism)")
     ap.add_argument("--no-zero", action="store_true",
                     help="replicate Adam moments and the update on every rank (default for N > 1: sharded, ZeRO-1)")
+    ap.add_argument("--checkpoint", action="store_true", help="recompute each decoder layer in backward")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no whole-step CUDA graph)")
     return ap.parse_args()
 
@@ -176,6 +177,8 @@ def run_ours(args) -> dict:
 
     rank, local, world = dist_setup(args.gpus)
     cfg = load_bench_config(args.config, args.batch, args.seq)
+    if args.checkpoint:
+        cfg["training"]["gradient_checkpointing"] = True
     tcfg = TrainingConfig.from_dict(cfg["training"])
     B, S = tcfg.batch_size, cfg["data"]["seq_len"]
     V = cfg["model"]["vocab_size"]
@@ -187,7 +190,7 @@ def run_ours(args) -> dict:
         raise SystemExit("bench.py runs expert parallelism over all ranks (ep_size == number of GPUs)")
     model, mcfg = build_model(cfg, seed=42, device=f"cuda:{local}", ep=ep)
     trainer = Trainer(model, tcfg, is_moe=cfg["model"]["type"] != "dense", overlap_grad_reduce=not args.no_overlap,
-                      cuda_graph=not args.no_graph, shard_optimizer=(not args.no_zero) and world > 1 and ep is None)
+                      cuda_graph=not args.no_graph, shard_optimizer=(not args.no_zero) and world > 1)
     n_params = sum(p.numel() * (ep_size if getattr(p, "_ep_shard", None) else 1) for p in model.parameters())
     K, W = args.steps, args.warmup
     host = make_batches(W + 2 * K, B, S, V, rank, cfg["data"].get("seed", 0))
@@ -232,6 +235,7 @@ def run_ours(args) -> dict:
                             f"E{getattr(mcfg, 'num_experts', 0)} top{getattr(mcfg, 'num_experts_per_tok', 0)})",
                    "params": n_params, "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": S,
                    "parallelism": par, "optimizer": "AdamW, clip 1.0, warmup+cosine",
+                   "activation_checkpointing": bool(tcfg.gradient_checkpointing),
                    "l2": "per-step working set (GBs of weights, activations, 5 GB of logits) is far larger than "
                          "the 126 MB L2; no explicit flush"},
         "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / K, "h2d_bytes_per_step": B * S * 8,

@@ -159,6 +159,7 @@ class DecoderLayer(nn.Module):
         """`h`: residual stream, `y = input_layernorm(h)`.  Returns (h', next_norm(h'), router scores)."""
         a = self.self_attn(y)
         h, y = ops.add_rmsnorm(a, h, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon)
+        ops.set_moe_site(self.mlp, global_experts, self.layer_idx)
         m, scores = self.mlp(y, global_experts)
         h, y = ops.add_rmsnorm(m, h, next_norm.weight, next_norm.variance_epsilon)
         return h, y, scores

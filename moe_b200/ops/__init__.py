@@ -104,6 +104,14 @@ def router(x, weight, bias, *, top_k, score_fn, norm_topk_prob, scaling_factor, 
     return oracle.router_sigmoid(x, weight, bias, top_k, norm_topk_prob, scaling_factor, num_groups, group_topk)
 
 
+def set_moe_site(mlp, global_experts, layer_idx: int) -> None:
+    """Tell the expert-parallel context (if any) which decoder layer is about to call `moe_experts`."""
+    bank = global_experts if global_experts is not None else getattr(mlp, "experts", None)
+    ep = getattr(getattr(bank, "gate_up_proj", None), "_ep", None)
+    if ep is not None:
+        ep.site = layer_idx
+
+
 def moe_experts(x, idx, w, gate_up, down):
     ep = getattr(gate_up, "_ep", None)
     if ep is not None:  # experts sharded over ranks: dispatch / combine over NVLink peer memory

@@ -61,6 +61,12 @@ class EPContext:
         self.status = G.status_word(self.device)
         self._bufs: dict = {}
         self.call_index = 0
+        # call-site identity: the decoder layer sets `site` before it runs (also when a checkpointed layer is
+        # recomputed), so forward and recomputation of one layer find the same buffers
+        self.site: int | None = None
+        # with activation checkpointing a layer's buffers are rewritten by its recomputation right before
+        # its backward, so two alternating sets serve every layer
+        self.share_buffers = False
 
     # ------------------------------------------------------------------ bookkeeping
     def begin_step(self) -> None:
@@ -133,8 +139,10 @@ class EPMoEFn(torch.autograd.Function):
         idx32 = topk_idx.reshape(T, K).to(torch.int32).contiguous()
         tw = topk_w.reshape(T, K).float().contiguous()
         plan = MoEPlan(idx32, ep.E)  # by global expert id: counts + stable rank inside each expert
-        key = ep.call_index
+        key = ep.site if ep.site is not None else ep.call_index
         ep.call_index += 1
+        if ep.share_buffers:
+            key &= 1
         b = ep.buffers(key, T, K, H)
         cap = b["cap"]
         send_base = torch.empty(ep.E, dtype=torch.int32, device=dev)

@@ -68,6 +68,8 @@ class Trainer:
         self._eager_steps = 0
         if cfg.gradient_checkpointing and hasattr(model, "gradient_checkpointing_enable"):
             model.gradient_checkpointing_enable()
+            if self.ep is not None:
+                self.ep.share_buffers = True
         model.train()
 
     # LR for the optimizer step about to be taken (scheduler semantics of LambdaLR: step k uses factor(k))
