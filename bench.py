@@ -42,6 +42,7 @@ def parse_args():
     ap.add_argument("--ep", action="store_true", help="shard the experts over all ranks (expert parallelism)")
     ap.add_argument("--no-zero", action="store_true",
                     help="replicate Adam moments and the update on every rank (default for N > 1: sharded, ZeRO-1)")
+    ap.add_argument("--layers", type=int, default=None, help="override num_hidden_layers (shape debugging only)")
     ap.add_argument("--checkpoint", action="store_true", help="recompute each decoder layer in backward")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no whole-step CUDA graph)")
     return ap.parse_args()
@@ -179,6 +180,8 @@ def run_ours(args) -> dict:
     cfg = load_bench_config(args.config, args.batch, args.seq)
     if args.checkpoint:
         cfg["training"]["gradient_checkpointing"] = True
+    if args.layers:
+        cfg["model"]["num_hidden_layers"] = args.layers
     tcfg = TrainingConfig.from_dict(cfg["training"])
     B, S = tcfg.batch_size, cfg["data"]["seq_len"]
     V = cfg["model"]["vocab_size"]

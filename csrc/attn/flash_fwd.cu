@@ -312,13 +312,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           }
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
-            mx0 = fmaxf(mx0, fmaxf(__uint_as_float(r0[c]), __uint_as_float(r1[c])));
-            mx1 = fmaxf(mx1, fmaxf(__uint_as_float(r0[c + 1]), __uint_as_float(r1[c + 1])));
-            mx2 = fmaxf(mx2, fmaxf(__uint_as_float(r0[c + 2]), __uint_as_float(r1[c + 2])));
-            mx3 = fmaxf(mx3, fmaxf(__uint_as_float(r0[c + 3]), __uint_as_float(r1[c + 3])));
+            mx0 = fmax3(mx0, __uint_as_float(r0[c]), __uint_as_float(r1[c]));
+            mx1 = fmax3(mx1, __uint_as_float(r0[c + 1]), __uint_as_float(r1[c + 1]));
+            mx2 = fmax3(mx2, __uint_as_float(r0[c + 2]), __uint_as_float(r1[c + 2]));
+            mx3 = fmax3(mx3, __uint_as_float(r0[c + 3]), __uint_as_float(r1[c + 3]));
           }
         }
-        const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const float m_new = fmaxf(fmax3(mx0, mx1, mx2), mx3);
         if (j == 0) {
           m_ref = m_new;  // nothing accumulated yet
         } else {
@@ -373,7 +373,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           for (int c8 = 0; c8 < 8; ++c8) {
             float p[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) p[i] = ex2_approx(fmaf(__uint_as_float(r[c8 * 8 + i]), sl2, -mb));
+            for (int i = 0; i < 8; ++i) {
+              // every fourth exponential runs on the FMA pipe: the XU pipe (one ex2 per 8 cycles and warp)
+              // is the busiest unit of this loop
+              const float xx = fmaf(__uint_as_float(r[c8 * 8 + i]), sl2, -mb);
+              p[i] = (i & 3) == 3 ? ex2_poly(xx) : ex2_approx(xx);
+            }
             rs0 += p[0] + p[4];
             rs1 += p[1] + p[5];
             rs2 += p[2] + p[6];

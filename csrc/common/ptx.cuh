@@ -246,6 +246,23 @@ __device__ __forceinline__ void report(int* status, int code) {
 }
 
 // ------------------------------------------------------------ small helpers
+__device__ __forceinline__ float fmax3(float a, float b, float c) {  // one instruction on sm_100
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for x <= 0 on the FMA pipe (no MUFU): round-to-nearest split x = n + f with the magic-number add,
+// degree-3 minimax polynomial for 2^f on [-0.5, 0.5] (relative error 1e-4), exponent patched in by an
+// integer add.  Inputs below -126 (including -inf) give a value below 1e-37.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(0.05500893f, f, 0.24221096f);
+  p = fmaf(p, f, 0.69328293f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
