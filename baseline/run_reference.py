@@ -125,4 +125,6 @@ def run(args, root, dist_setup, timed_region, make_batches, load_bench_config) -
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tok/s", "ms_per_step": ms_e2e / K,
                 "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
         "gpu_launches": 0, "clocks": clocks, "loss_last": float(last["loss"].item()), "loss_e2e_last": losses[-1],
+        # rank 0's loss of every end-to-end step (same synthetic token stream in both arms)
+        "losses_e2e": [round(x, 4) for x in losses[:256]],
     }

@@ -244,6 +244,8 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / K, "h2d_bytes_per_step": B * S * 8,
                 "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
         "gpu_launches": launches, "clocks": clocks, "loss_last": loss_dev, "loss_e2e_last": losses[-1],
+        # rank 0's loss of every end-to-end step (same synthetic token stream in both arms)
+        "losses_e2e": [round(x, 4) for x in losses[:256]],
     }
 
 
