@@ -154,6 +154,29 @@ def case_flash_attn_fwd(small):
     return dict(shape=[B, S, nh, nkv, 128], ms=ms, flops=2.0 * B * nh * S * S * 128, sdpa_ms=ref)
 
 
+def case_flash_attn_bwd(small):
+    import math
+
+    from moe_b200.ops import _ext
+    from moe_b200.ops import gemm as G
+
+    e = _ext.load()
+    B, S, nh, nkv = (2, 2048, 16, 8) if small else (8, 2048, 16, 8)
+    q, k, v, do = bf(B, S, nh, 128), bf(B, S, nkv, 128), bf(B, S, nkv, 128), bf(B, S, nh, 128)
+    o, lse = torch.empty_like(q), torch.empty(B, nh, S, device="cuda")
+    st = G.status_word(q.device)
+    sc = 1 / math.sqrt(128)
+    e.flash_fwd(q, k, v, o, lse, sc, st)
+    dq, dk, dv, delta = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(lse)
+    ms = timeit(lambda: e.flash_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, sc, st))
+    z = torch.zeros((), dtype=torch.int64, device="cuda")
+    lse_nat = (lse * math.log(2)).unsqueeze(-1)
+    ref = timeit(lambda: torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
+        do.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), o.transpose(1, 2), lse_nat, z, z,
+        None, None, None, S, S, 0.0, True, scale=sc))
+    return dict(shape=[B, S, nh, nkv, 128], ms=ms, flops=5.0 * B * nh * S * S * 128, cudnn_ms=ref)
+
+
 def case_allreduce_emulated(small):
     """Eight ranks emulated on one GPU (flags pre-set): measures the kernel's local memory path only."""
     from moe_b200.ops import _ext

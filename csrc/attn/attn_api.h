@@ -13,12 +13,13 @@ extern "C" {
 int b200_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int nh, int nkv,
                    float softmax_scale, int* status, cudaStream_t stream);
 
-// Gradients of the same attention.  delta [B,nh,S] fp32 is scratch (row sums of dO*O); dq_acc [B,S,nh,128]
-// fp32 is scratch that must be zero on entry and holds dQ on exit (dq, bf16, is written from it);
-// dk/dv [B,S,nkv,128] bf16.
+// Gradients of the same attention (same shape rules).  delta [B,nh,S] fp32 is scratch: it receives
+// softmax_scale * rowsum(dO * O).  dq [B,S,nh,128], dk/dv [B,S,nkv,128] bf16 are overwritten.  Three
+// launches: delta, dQ (one query tile per work item, loops over key tiles) and dK/dV (one key tile per
+// work item, loops over the query heads of its group and their query tiles).
 int b200_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
-                   float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int S, int nh, int nkv,
-                   float softmax_scale, int* status, cudaStream_t stream);
+                   float* delta, void* dq, void* dk, void* dv, int B, int S, int nh, int nkv, float softmax_scale,
+                   int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

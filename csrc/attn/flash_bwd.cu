@@ -1,0 +1,627 @@
+// Causal grouped-query flash attention, backward, for sm_100a (head_dim 128).  Three kernels:
+//
+//   delta : Dsc[b,h,s] = softmax_scale * sum_d dO[b,s,h,d] * O[b,s,h,d]
+//   dQ    : work item = (batch, query head, 128 query rows); loops over key tiles j <= query tile:
+//             S = Q K_j^T, dP = dO V_j^T                       (both operands in shared memory)
+//             P = exp2(S*c - lse2), dS = P * (dP*scale - Dsc)   (one query row per pair of threads)
+//             dQ += dS K_j                                      (dS from TMEM, K_j read MN-major)
+//   dK/dV : work item = (batch, key/value head, 128 key rows); loops over the query heads of the group
+//           and their query tiles i >= key tile:
+//             S^T = K_j Q_i^T, dP^T = V_j dO_i^T                (TMEM lanes = key rows)
+//             P^T, dS^T as above with per-column statistics read from shared memory
+//             dV += P^T dO_i, dK += dS^T Q_i                    (P^T, dS^T from TMEM; dO_i, Q_i MN-major)
+//           so the sum over the query heads of a group happens in the TMEM accumulators.
+//
+// Roles as in the forward kernel: warp 0 TMA producer, warp 1 MMA issuer (owns the 512 TMEM columns),
+// warps 2..9 element-wise (TMEM lane quarter = warp % 4; warps 2..5 take columns 0..63 of a tile, warps
+// 6..9 columns 64..127).  The bf16 operands produced by the threads (dS, P^T, dS^T) are written with
+// tcgen05.st over the first 32 columns of the half of the score tile the same thread has just read, and
+// the following MMA takes them as its A operand from TMEM; MMAs of one thread execute in issue order,
+// so the next score MMA may overwrite those columns.  The same shared-memory tile is read K-major by the
+// score MMAs and MN-major (LBO = 16 KB between 64-wide chunks) by the gradient MMAs.
+#include "../common/ptx.cuh"
+#include "../common/tma_host.h"
+#include "attn_api.h"
+
+namespace b200 {
+
+constexpr int FB_THREADS = 320;
+constexpr int FB_TILE = 32768;  // 128 x 128 bf16
+constexpr int FB_SMEM = 232448;
+constexpr unsigned long long FB_LIMIT_NS = 2000000000ull;
+
+struct FbArgs {
+  const float* lse2;  // [B, nh, S]
+  const float* dsc;   // [B, nh, S]
+  __nv_bfloat16* dq;  // [B, S, nh, 128]
+  __nv_bfloat16* dk;  // [B, S, nkv, 128]
+  __nv_bfloat16* dv;
+  int B, S, nh, nkv;
+  int items;
+  float scale, scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ int fb_sched(int round, int cta, int ctas) {
+  return round * ctas + ((round & 1) ? ctas - 1 - cta : cta);
+}
+
+// ----------------------------------------------------------------------------------------- delta
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ dsc, int B, int S, int nh, float scale) {
+  // one warp per (b, s, h): 128 elements, 4 per lane
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * nh;
+  if (w >= total) return;
+  const uint2 a = reinterpret_cast<const uint2*>(o + w * 128)[lane];
+  const uint2 b = reinterpret_cast<const uint2*>(d_o + w * 128)[lane];
+  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  s = warp_sum(s);
+  if (lane == 0) {
+    const long long bs = w / nh;
+    const int h = static_cast<int>(w - bs * nh);
+    const long long b_ = bs / S;
+    const int s_ = static_cast<int>(bs - b_ * S);
+    dsc[(b_ * nh + h) * S + s_] = s * scale;
+  }
+}
+
+// -------------------------------------------------------------------------------------------- dQ
+constexpr int DQ_RING = 5;
+
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+                    const FbArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sDO = base + FB_TILE;
+  uint8_t* sR = base + 2 * FB_TILE;  // K_j at even ring entries, V_j at odd ones
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + 7 * FB_TILE);
+  uint64_t& bar_q_full = bars[0];
+  uint64_t& bar_q_empty = bars[1];
+  uint64_t* bar_r_full = bars + 2;    // [DQ_RING]
+  uint64_t* bar_r_empty = bars + 7;   // [DQ_RING]
+  uint64_t* bar_s_full = bars + 12;   // [2]
+  uint64_t& bar_dp_full = bars[14];
+  uint64_t& bar_ds_full = bars[15];
+  uint64_t& bar_dq_full = bars[16];
+  uint64_t& bar_drain = bars[17];
+  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 18);
+  int& go = *reinterpret_cast<int*>(bars + 19);
+
+  if (threadIdx.x == 0) {
+    go = 1;
+    if (base + 7 * FB_TILE + 256 > smem_raw + FB_SMEM) {
+      report(args.status, ST_BAD_ARGUMENT);
+      go = 0;
+    }
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapDO);
+    mbar_init(&bar_q_full, 1);
+    mbar_init(&bar_q_empty, 1);
+    for (int s = 0; s < DQ_RING; ++s) {
+      mbar_init(&bar_r_full[s], 1);
+      mbar_init(&bar_r_empty[s], 1);
+    }
+    mbar_init(&bar_s_full[0], 1);
+    mbar_init(&bar_s_full[1], 1);
+    mbar_init(&bar_dp_full, 1);
+    mbar_init(&bar_ds_full, 8);
+    mbar_init(&bar_dq_full, 1);
+    mbar_init(&bar_drain, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (!go) return;
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+  // TMEM columns: S[0] 0, S[1] 128, dP 256, dQ 384
+  const int group = args.nh / args.nkv;
+  const int per_qt = args.B * args.nh;
+  const int n_qt = args.S >> 7;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t load = 0;
+      int it_count = 0;
+      for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
+        if (*reinterpret_cast<volatile int*>(args.status) != 0) break;
+        const int qt = n_qt - 1 - t / per_qt, r = t % per_qt, b = r / args.nh, h = r % args.nh, hk = h / group;
+        if (!mbar_wait_ns(&bar_q_empty, (it_count & 1) ^ 1u, FB_LIMIT_NS)) {
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(&bar_q_full, 2 * FB_TILE);
+        tma_load_3d(sQ, &mapQ, &bar_q_full, h * 128, qt * 128, b);
+        tma_load_3d(sQ + 16384, &mapQ, &bar_q_full, h * 128 + 64, qt * 128, b);
+        tma_load_3d(sDO, &mapDO, &bar_q_full, h * 128, qt * 128, b);
+        tma_load_3d(sDO + 16384, &mapDO, &bar_q_full, h * 128 + 64, qt * 128, b);
+        for (int j = 0; j <= qt && ok; ++j) {
+          for (int kv = 0; kv < 2; ++kv) {
+            const int slot = load % DQ_RING;
+            if (!mbar_wait_ns(&bar_r_empty[slot], ((load / DQ_RING) & 1) ^ 1u, FB_LIMIT_NS)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&bar_r_full[slot], FB_TILE);
+            uint8_t* dst = sR + slot * FB_TILE;
+            const CUtensorMap* m = kv ? &mapV : &mapK;
+            tma_load_3d(dst, m, &bar_r_full[slot], hk * 128, j * 128, b);
+            tma_load_3d(dst + 16384, m, &bar_r_full[slot], hk * 128 + 64, j * 128, b);
+            ++load;
+          }
+        }
+      }
+      if (!ok) report(args.status, ST_TIMEOUT_PRODUCER);
+      for (uint32_t i = load > DQ_RING ? load - DQ_RING : 0; i < load; ++i)
+        (void)mbar_wait_ns(&bar_r_full[i % DQ_RING], (i / DQ_RING) & 1, FB_LIMIT_NS);
+      if (it_count > 0) (void)mbar_wait_ns(&bar_q_full, (it_count - 1) & 1, FB_LIMIT_NS);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
+      constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);  // B MN-major
+      bool ok = true;
+      uint32_t load = 0, g = 0;
+      int it_count = 0;
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+      auto ring_wait = [&](uint32_t idx) -> bool {
+        const bool r = mbar_wait_ns(&bar_r_full[idx % DQ_RING], (idx / DQ_RING) & 1, FB_LIMIT_NS);
+        tc_fence_after();
+        return r;
+      };
+      auto issue_kk = [&](uint32_t d_col, uint32_t a_addr, uint32_t b_addr) {
+#pragma unroll
+        for (int kc = 0; kc < 2; ++kc)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem + d_col, make_smem_desc(a_addr + kc * 16384 + k * 32, 16, 1024),
+                      make_smem_desc(b_addr + kc * 16384 + k * 32, 16, 1024), idesc_kk, (kc | k) != 0 ? 1u : 0u);
+      };
+      for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
+        const int qt = n_qt - 1 - t / per_qt;
+        const int n = qt + 1;
+        auto k_slot = [&](int j) { return smem_u32(sR + ((load + 2 * j) % DQ_RING) * FB_TILE); };
+        auto v_slot = [&](int j) { return smem_u32(sR + ((load + 2 * j + 1) % DQ_RING) * FB_TILE); };
+        ok = mbar_wait_ns(&bar_q_full, it_count & 1, FB_LIMIT_NS);
+        if (!ok) break;
+        tc_fence_after();
+        // S(0), dP(0), S(1)
+        if (!ring_wait(load)) { ok = false; break; }
+        issue_kk(((g + 0) & 1) * 128, q_addr, k_slot(0));
+        umma_commit(&bar_s_full[(g + 0) & 1]);
+        if (!ring_wait(load + 1)) { ok = false; break; }
+        issue_kk(256, do_addr, v_slot(0));
+        umma_commit(&bar_r_empty[(load + 1) % DQ_RING]);
+        umma_commit(&bar_dp_full);
+        if (n == 1) umma_commit(&bar_q_empty);
+        if (n > 1) {
+          if (!ring_wait(load + 2)) { ok = false; break; }
+          issue_kk(((g + 1) & 1) * 128, q_addr, k_slot(1));
+          umma_commit(&bar_s_full[(g + 1) & 1]);
+        }
+        for (int j = 0; j < n; ++j) {
+          if (!mbar_wait_ns(&bar_ds_full, (g + j) & 1, FB_LIMIT_NS)) { ok = false; break; }
+          tc_fence_after();
+          // dQ += dS K_j : A = dS in TMEM (k-steps 0..3 at dP columns 0..31, 4..7 at columns 64..95)
+          const uint32_t kj = k_slot(j);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_bf16_ts(tmem + 384, tmem + 256 + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
+                         make_smem_desc(kj + ks * 2048, 16384, 1024), idesc_mn, (j | ks) != 0 ? 1u : 0u);
+          umma_commit(&bar_r_empty[(load + 2 * j) % DQ_RING]);
+          umma_commit(&bar_dq_full);
+          if (j + 1 < n) {
+            if (!ring_wait(load + 2 * (j + 1) + 1)) { ok = false; break; }
+            issue_kk(256, do_addr, v_slot(j + 1));
+            umma_commit(&bar_r_empty[(load + 2 * (j + 1) + 1) % DQ_RING]);
+            umma_commit(&bar_dp_full);
+            if (j + 1 == n - 1) umma_commit(&bar_q_empty);
+          }
+          if (j + 2 < n) {
+            if (!ring_wait(load + 2 * (j + 2))) { ok = false; break; }
+            issue_kk(((g + j + 2) & 1) * 128, q_addr, k_slot(j + 2));
+            umma_commit(&bar_s_full[(g + j + 2) & 1]);
+          }
+        }
+        load += 2 * n;
+        g += n;
+      }
+      if (!ok) report(args.status, ST_TIMEOUT_MMA);
+      umma_commit(&bar_drain);
+      (void)mbar_wait_ns(&bar_drain, 0, FB_LIMIT_NS);
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row_l = q4 * 32 + lane;
+    const uint32_t t_row = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+    const float sl2 = args.scale_log2, scale = args.scale;
+    bool ok = true;
+    uint32_t g = 0;
+    int it_count = 0;
+    for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
+      const int qt = n_qt - 1 - t / per_qt, r = t % per_qt, b = r / args.nh, h = r % args.nh;
+      const int n = qt + 1;
+      const long long stat = (static_cast<long long>(b) * args.nh + h) * args.S + qt * 128 + row_l;
+      const float lse2 = args.lse2[stat], dsc = args.dsc[stat];
+      for (int j = 0; j < n; ++j, ++g) {
+        if (!mbar_wait_ns(&bar_s_full[g & 1], (g >> 1) & 1, FB_LIMIT_NS) ||
+            !mbar_wait_ns(&bar_dp_full, g & 1, FB_LIMIT_NS)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const bool diag = j == n - 1;
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t s[32], dp[32];
+          tmem_ld_32x32(t_row + (g & 1) * 128 + half * 64 + c * 32, s);
+          tmem_ld_32x32(t_row + 256 + half * 64 + c * 32, dp);
+          tmem_ld_wait();
+          float ds[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = fmaf(__uint_as_float(s[i]), sl2, -lse2);
+            const float p = (i & 3) == 3 ? ex2_poly(x) : ex2_approx(x);
+            ds[i] = p * fmaf(__uint_as_float(dp[i]), scale, -dsc);
+            if (diag && half * 64 + c * 32 + i > row_l) ds[i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16x2(ds[2 * i], ds[2 * i + 1]);
+        }
+        tmem_st_32x32(t_row + 256 + half * 64, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_ds_full);
+      }
+      if (!ok) break;
+      if (!mbar_wait_ns(&bar_dq_full, (g - 1) & 1, FB_LIMIT_NS)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const long long row_g = static_cast<long long>(b) * args.S + qt * 128 + row_l;
+      uint4* dst = reinterpret_cast<uint4*>(args.dq + (row_g * args.nh + h) * 128 + half * 64);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_row + 384 + half * 64 + hh * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8)
+          dst[hh * 4 + c8] = make_uint4(
+              pack_bf16x2(__uint_as_float(rr[c8 * 8]), __uint_as_float(rr[c8 * 8 + 1])),
+              pack_bf16x2(__uint_as_float(rr[c8 * 8 + 2]), __uint_as_float(rr[c8 * 8 + 3])),
+              pack_bf16x2(__uint_as_float(rr[c8 * 8 + 4]), __uint_as_float(rr[c8 * 8 + 5])),
+              pack_bf16x2(__uint_as_float(rr[c8 * 8 + 6]), __uint_as_float(rr[c8 * 8 + 7])));
+      }
+      tc_fence_before();
+    }
+    if (!ok) report(args.status, ST_TIMEOUT_EPILOGUE);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------- dK, dV
+constexpr int KV_STAGES = 2;
+
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+                     const FbArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = base;
+  uint8_t* sV = base + FB_TILE;
+  uint8_t* sSt = base + 2 * FB_TILE;  // stages: {Q_i, dO_i}
+  float* sStat = reinterpret_cast<float*>(base + 6 * FB_TILE);  // [stage][lse2 | dsc][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * FB_TILE + KV_STAGES * 1024);
+  uint64_t& bar_kv_full = bars[0];
+  uint64_t& bar_kv_empty = bars[1];
+  uint64_t* bar_st_full = bars + 2;   // [KV_STAGES]
+  uint64_t* bar_st_empty = bars + 4;  // [KV_STAGES]
+  uint64_t& bar_s_full = bars[6];
+  uint64_t& bar_ds_full = bars[7];
+  uint64_t& bar_acc_full = bars[8];
+  uint64_t& bar_drain = bars[9];
+  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 10);
+  int& go = *reinterpret_cast<int*>(bars + 11);
+
+  if (threadIdx.x == 0) {
+    go = 1;
+    if (base + 6 * FB_TILE + KV_STAGES * 1024 + 256 > smem_raw + FB_SMEM) {
+      report(args.status, ST_BAD_ARGUMENT);
+      go = 0;
+    }
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapDO);
+    mbar_init(&bar_kv_full, 1);
+    mbar_init(&bar_kv_empty, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&bar_st_full[s], 1);
+      mbar_init(&bar_st_empty[s], 1);
+    }
+    mbar_init(&bar_s_full, 1);
+    mbar_init(&bar_ds_full, 8);
+    mbar_init(&bar_acc_full, 1);
+    mbar_init(&bar_drain, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (!go) return;
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+  // TMEM columns: S^T 0, dP^T 128, dV 256, dK 384
+  const int group = args.nh / args.nkv;
+  const int per_j = args.B * args.nkv;
+  const int n_qt = args.S >> 7;
+  // item t: key tile j = t / per_j (small j = many query tiles = heavy, first), then (batch, key/value head)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      uint32_t pc = 0;  // (head, query tile) pairs issued so far
+      int it_count = 0;
+      for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
+        if (*reinterpret_cast<volatile int*>(args.status) != 0) break;
+        const int j = t / per_j, r = t % per_j, b = r / args.nkv, hk = r % args.nkv;
+        if (!mbar_wait_ns(&bar_kv_empty, (it_count & 1) ^ 1u, FB_LIMIT_NS)) {
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(&bar_kv_full, 2 * FB_TILE);
+        tma_load_3d(sK, &mapK, &bar_kv_full, hk * 128, j * 128, b);
+        tma_load_3d(sK + 16384, &mapK, &bar_kv_full, hk * 128 + 64, j * 128, b);
+        tma_load_3d(sV, &mapV, &bar_kv_full, hk * 128, j * 128, b);
+        tma_load_3d(sV + 16384, &mapV, &bar_kv_full, hk * 128 + 64, j * 128, b);
+        for (int gi = 0; gi < group && ok; ++gi) {
+          const int h = hk * group + gi;
+          for (int i = j; i < n_qt; ++i, ++pc) {
+            const int st = pc % KV_STAGES;
+            if (!mbar_wait_ns(&bar_st_empty[st], ((pc / KV_STAGES) & 1) ^ 1u, FB_LIMIT_NS)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&bar_st_full[st], 2 * FB_TILE + 1024);
+            uint8_t* dq_ = sSt + st * 2 * FB_TILE;
+            tma_load_3d(dq_, &mapQ, &bar_st_full[st], h * 128, i * 128, b);
+            tma_load_3d(dq_ + 16384, &mapQ, &bar_st_full[st], h * 128 + 64, i * 128, b);
+            tma_load_3d(dq_ + FB_TILE, &mapDO, &bar_st_full[st], h * 128, i * 128, b);
+            tma_load_3d(dq_ + FB_TILE + 16384, &mapDO, &bar_st_full[st], h * 128 + 64, i * 128, b);
+            const long long so = (static_cast<long long>(b) * args.nh + h) * args.S + i * 128;
+            bulk_load_1d(sStat + st * 256, args.lse2 + so, 512, &bar_st_full[st]);
+            bulk_load_1d(sStat + st * 256 + 128, args.dsc + so, 512, &bar_st_full[st]);
+          }
+        }
+      }
+      if (!ok) report(args.status, ST_TIMEOUT_PRODUCER);
+      for (uint32_t i = pc > KV_STAGES ? pc - KV_STAGES : 0; i < pc; ++i)
+        (void)mbar_wait_ns(&bar_st_full[i % KV_STAGES], (i / KV_STAGES) & 1, FB_LIMIT_NS);
+      if (it_count > 0) (void)mbar_wait_ns(&bar_kv_full, (it_count - 1) & 1, FB_LIMIT_NS);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);
+      bool ok = true;
+      uint32_t pc = 0;
+      int it_count = 0;
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
+        const int j = t / per_j;
+        const int pairs = group * (n_qt - j);
+        ok = mbar_wait_ns(&bar_kv_full, it_count & 1, FB_LIMIT_NS);
+        if (!ok) break;
+        tc_fence_after();
+        for (int p = 0; p < pairs; ++p, ++pc) {
+          const int st = pc % KV_STAGES;
+          if (!mbar_wait_ns(&bar_st_full[st], (pc / KV_STAGES) & 1, FB_LIMIT_NS)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t q_addr = smem_u32(sSt + st * 2 * FB_TILE), do_addr = q_addr + FB_TILE;
+          // S^T = K_j Q_i^T and dP^T = V_j dO_i^T
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(tmem, make_smem_desc(k_addr + kc * 16384 + k * 32, 16, 1024),
+                        make_smem_desc(q_addr + kc * 16384 + k * 32, 16, 1024), idesc_kk, (kc | k) != 0 ? 1u : 0u);
+#pragma unroll
+          for (int kc = 0; kc < 2; ++kc)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(tmem + 128, make_smem_desc(v_addr + kc * 16384 + k * 32, 16, 1024),
+                        make_smem_desc(do_addr + kc * 16384 + k * 32, 16, 1024), idesc_kk, (kc | k) != 0 ? 1u : 0u);
+          umma_commit(&bar_s_full);
+          if (!mbar_wait_ns(&bar_ds_full, pc & 1, FB_LIMIT_NS)) { ok = false; break; }
+          tc_fence_after();
+          // dV += P^T dO_i (A: columns 0.. of S^T), dK += dS^T Q_i (A: columns 0.. of dP^T); B read MN-major
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_bf16_ts(tmem + 256, tmem + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
+                         make_smem_desc(do_addr + ks * 2048, 16384, 1024), idesc_mn, (p | ks) != 0 ? 1u : 0u);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_bf16_ts(tmem + 384, tmem + 128 + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
+                         make_smem_desc(q_addr + ks * 2048, 16384, 1024), idesc_mn, (p | ks) != 0 ? 1u : 0u);
+          umma_commit(&bar_st_empty[st]);
+          umma_commit(&bar_acc_full);
+          if (p == pairs - 1) umma_commit(&bar_kv_empty);
+        }
+      }
+      if (!ok) report(args.status, ST_TIMEOUT_MMA);
+      umma_commit(&bar_drain);
+      (void)mbar_wait_ns(&bar_drain, 0, FB_LIMIT_NS);
+    }
+  } else {
+    const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row_l = q4 * 32 + lane;  // key row inside the tile
+    const uint32_t t_row = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
+    const float sl2 = args.scale_log2, scale = args.scale;
+    bool ok = true;
+    uint32_t pc = 0;
+    int it_count = 0;
+    for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
+      const int j = t / per_j, r = t % per_j, b = r / args.nkv, hk = r % args.nkv;
+      const int per_head = n_qt - j, pairs = group * per_head;
+      for (int p = 0; p < pairs; ++p, ++pc) {
+        if (!mbar_wait_ns(&bar_s_full, pc & 1, FB_LIMIT_NS)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float* stat = sStat + (pc % KV_STAGES) * 256 + half * 64;
+        const bool diag = (p % per_head) == 0;  // query tile == key tile: query index must be >= key index
+        uint32_t pp[32], pd[32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t s[32], dp[32];
+          tmem_ld_32x32(t_row + half * 64 + c * 32, s);
+          tmem_ld_32x32(t_row + 128 + half * 64 + c * 32, dp);
+          tmem_ld_wait();
+          float pv[32], ds[32];
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(stat + c * 32 + i4 * 4);
+            const float4 d4 = *reinterpret_cast<const float4*>(stat + 128 + c * 32 + i4 * 4);
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv_[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = i4 * 4 + u;
+              const float x = fmaf(__uint_as_float(s[i]), sl2, -lv[u]);
+              float pe = u == 3 ? ex2_poly(x) : ex2_approx(x);
+              if (diag && half * 64 + c * 32 + i < row_l) pe = 0.f;
+              pv[i] = pe;
+              ds[i] = pe * fmaf(__uint_as_float(dp[i]), scale, -dv_[u]);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            pp[c * 16 + i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
+            pd[c * 16 + i] = pack_bf16x2(ds[2 * i], ds[2 * i + 1]);
+          }
+        }
+        tmem_st_32x32(t_row + half * 64, pp);
+        tmem_st_32x32(t_row + 128 + half * 64, pd);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_ds_full);
+      }
+      if (!ok) break;
+      if (!mbar_wait_ns(&bar_acc_full, (pc - 1) & 1, FB_LIMIT_NS)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const long long row_g = static_cast<long long>(b) * args.S + j * 128 + row_l;
+      const long long off = (row_g * args.nkv + hk) * 128 + half * 64;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        uint4* dst = reinterpret_cast<uint4*>((which ? args.dk : args.dv) + off);
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t rr[32];
+          tmem_ld_32x32(t_row + 256 + which * 128 + half * 64 + hh * 32, rr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8)
+            dst[hh * 4 + c8] = make_uint4(
+                pack_bf16x2(__uint_as_float(rr[c8 * 8]), __uint_as_float(rr[c8 * 8 + 1])),
+                pack_bf16x2(__uint_as_float(rr[c8 * 8 + 2]), __uint_as_float(rr[c8 * 8 + 3])),
+                pack_bf16x2(__uint_as_float(rr[c8 * 8 + 4]), __uint_as_float(rr[c8 * 8 + 5])),
+                pack_bf16x2(__uint_as_float(rr[c8 * 8 + 6]), __uint_as_float(rr[c8 * 8 + 7])));
+        }
+      }
+      tc_fence_before();
+    }
+    if (!ok) report(args.status, ST_TIMEOUT_EPILOGUE);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int nh,
+                              int nkv, float softmax_scale, int* status, cudaStream_t stream) {
+  if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
+  CUtensorMap mq, mk, mv, mdo;
+  const uint64_t qrow = static_cast<uint64_t>(nh) * 128, krow = static_cast<uint64_t>(nkv) * 128;
+  int rc = make_map(&mq, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
+  if (rc == 0) rc = make_map(&mdo, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
+  if (rc == 0) rc = make_map(&mk, k, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
+  if (rc == 0) rc = make_map(&mv, v, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
+  if (rc != 0) return rc - 100;
+  static bool configured = false;
+  static int sms = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) != cudaSuccess)
+      return -10;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  const long long rows = static_cast<long long>(B) * S * nh;
+  attn_delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, nh,
+      softmax_scale);
+  FbArgs a;
+  a.lse2 = lse;
+  a.dsc = delta;
+  a.dq = reinterpret_cast<__nv_bfloat16*>(dq);
+  a.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.B = B; a.S = S; a.nh = nh; a.nkv = nkv;
+  a.scale = softmax_scale;
+  a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  a.status = status;
+  a.items = B * nh * (S / 128);
+  flash_bwd_dq_kernel<<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq, mk, mv, mdo, a);
+  a.items = B * nkv * (S / 128);
+  flash_bwd_dkv_kernel<<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq, mk, mv, mdo, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

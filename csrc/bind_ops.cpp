@@ -100,6 +100,21 @@ void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Ten
                        (float)scale, status.data_ptr<int>(), stream()), "flash_fwd");
 }
 
+void flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
+               Tensor& delta, Tensor& dq, Tensor& dk, Tensor& dv, double scale, Tensor& status) {
+  bf16c(q, "q"); bf16c(k, "k"); bf16c(v, "v"); bf16c(o, "o"); bf16c(d_o, "d_o"); f32c(lse, "lse"); f32c(delta, "delta");
+  bf16c(dq, "dq"); bf16c(dk, "dk"); bf16c(dv, "dv"); i32c(status, "status");
+  need(q.dim() == 4 && k.dim() == 4 && q.size(3) == 128 && k.size(3) == 128, "flash attention: [B,S,h,128] expected");
+  need(k.sizes() == v.sizes() && o.sizes() == q.sizes() && d_o.sizes() == q.sizes() && dq.sizes() == q.sizes() &&
+           dk.sizes() == k.sizes() && dv.sizes() == k.sizes(), "flash attention backward: shape mismatch");
+  const int B = (int)q.size(0), S = (int)q.size(1), nh = (int)q.size(2), nkv = (int)k.size(2);
+  need(lse.numel() == (int64_t)B * nh * S && delta.numel() == lse.numel(), "flash attention backward: statistics size");
+  c10::cuda::CUDAGuard g(q.device());
+  rc_ok(b200_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
+                       delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, nh, nkv, (float)scale,
+                       status.data_ptr<int>(), stream()), "flash_bwd");
+}
+
 // ------------------------------------------------------------------- router
 void router_fwd(const Tensor& logits, const OptT& bias, Tensor& scores, Tensor& topk_w, Tensor& topk_idx, int64_t K,
                 int64_t mode, bool norm, double scale, int64_t num_groups, int64_t group_topk) {
@@ -320,6 +335,7 @@ void bind_ops(pybind11::module_& m) {
   m.def("qknorm_rope_fwd", &qknorm_rope_fwd);
   m.def("qknorm_rope_bwd", &qknorm_rope_bwd);
   m.def("flash_fwd", &flash_fwd);
+  m.def("flash_bwd", &flash_bwd);
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);
   m.def("moe_plan_blocks", &moe_plan_blocks);

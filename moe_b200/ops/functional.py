@@ -323,6 +323,11 @@ class FlashAttnFn(torch.autograd.Function):
         q, k, v, o, lse2 = ctx.saved_tensors
         B, S, nh, hd = q.shape
         do = do.contiguous()
+        if os.environ.get("MOE_B200_ATTN_BWD", "library") == "own":
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            delta = torch.empty_like(lse2)
+            ext().flash_bwd(q, k, v, o, do, lse2, delta, dq, dk, dv, ctx.scale, G.status_word(q.device))
+            return dq, dk, dv
         st = _ATTN_STATE
         if st["library_backward_ok"] is not False:
             try:

@@ -257,9 +257,10 @@ def test_adamw_and_norm(dev):
     assert relerr(p16, p2) < 5e-3
 
 
+@pytest.mark.parametrize("bwd", ["library", "own"])
 @pytest.mark.parametrize("B,S,nh,nkv,spread", [(1, 128, 2, 1, 1.0), (2, 384, 4, 2, 1.0), (1, 1024, 8, 1, 1.0),
                                                (2, 512, 4, 2, 6.0)])
-def test_flash_attention_forward_and_grads(dev, B, S, nh, nkv, spread):
+def test_flash_attention_forward_and_grads(dev, monkeypatch, B, S, nh, nkv, spread, bwd):
     """Own tcgen05 forward (output and log-sum-exp) and the gradients of `ops.attention` against the fp32
     statement; `spread` widens the score range so that the lazy accumulator rescale in TMEM is exercised."""
     from moe_b200.ops import _ext, oracle
@@ -279,7 +280,8 @@ def test_flash_attention_forward_and_grads(dev, B, S, nh, nkv, spread):
     sc = torch.einsum("bqhd,bkhd->bhqk", qf.detach(), kk) / math.sqrt(128)
     sc = sc.masked_fill(torch.ones(S, S, dtype=torch.bool, device=dev).triu(1), float("-inf"))
     assert (lse2 * math.log(2) - torch.logsumexp(sc, -1)).abs().max() < 2e-3
-    # through autograd (own forward, library backward)
+    # through autograd: own forward, then the library's or the own backward kernels
+    monkeypatch.setenv("MOE_B200_ATTN_BWD", bwd)
     do = _bf(B, S, nh, 128)
     q2, k2, v2 = (t.clone().requires_grad_() for t in (q, k, v))
     out = F.attention(q2, k2, v2)
