@@ -13,12 +13,25 @@
 //           so the sum over the query heads of a group happens in the TMEM accumulators.
 //
 // Roles as in the forward kernel: warp 0 TMA producer, warp 1 MMA issuer (owns the 512 TMEM columns),
-// warps 2..9 element-wise (TMEM lane quarter = warp % 4; warps 2..5 take columns 0..63 of a tile, warps
-// 6..9 columns 64..127).  The bf16 operands produced by the threads (dS, P^T, dS^T) are written with
-// tcgen05.st over the first 32 columns of the half of the score tile the same thread has just read, and
-// the following MMA takes them as its A operand from TMEM; MMAs of one thread execute in issue order,
-// so the next score MMA may overwrite those columns.  The same shared-memory tile is read K-major by the
-// score MMAs and MN-major (LBO = 16 KB between 64-wide chunks) by the gradient MMAs.
+// warps 2..9 element-wise (TMEM lane quarter = warp % 4).
+//
+// dQ kernel: 128 x 128 score tiles, the score buffer double-buffered in TMEM (S[2], dP, dQ = 512 columns).
+// Of a tile, warps 2..5 take columns 0..63 and warps 6..9 columns 64..127; a thread writes its 64 dS values
+// (bf16 pairs, tcgen05.st) over the first 32 of the score columns it has just read, and dQ += dS K_j takes
+// them as its A operand from TMEM.  Issue order: S(0) dP(0) S(1) | dQ(0) dP(1) S(2) | dQ(1) dP(2) S(3) | ...
+// (MMAs of one thread execute in issue order, so S(j+2) may overwrite the columns dS(j) was read from).
+// K_j is one ring slot that is read K-major by the score MMA and MN-major by the gradient MMA.
+//
+// dK/dV kernel: all 512 TMEM columns would be live with 128-wide score tiles (S^T, dP^T, dV, dK) and
+// nothing could overlap, so this loop advances in SUB-TILES of 64 query rows: score tiles are 128 x 64 and
+// double-buffered, the score MMAs of sub-tile u+1 run while the threads work on sub-tile u.  Warps 2..5
+// take columns 0..31 of a sub-tile, warps 6..9 columns 32..63; P^T and dS^T go over the first 16 of the 32
+// score columns a thread has read.  A ring slot holds the 64 rows of Q_i and dO_i of one sub-tile.
+//
+// Measured MMA issue rates that shaped this (clock64 trace of one CTA): a 128x64x16 MMA with both
+// operands in shared memory takes about 74 cycles, a 128x128x16 MMA with its A operand in TMEM about 128
+// (twice the 64 of the shared-memory form), so both kernels are bound by the tensor pipe's operand paths,
+// not by the element-wise threads (about 800 cycles per sub-tile, idle most of the time).
 #include "../common/ptx.cuh"
 #include "../common/tma_host.h"
 #include "attn_api.h"
@@ -218,14 +231,17 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         for (int j = 0; j < n; ++j) {
           if (!mbar_wait_ns(&bar_ds_full, (g + j) & 1, FB_LIMIT_NS)) { ok = false; break; }
           tc_fence_after();
-          // dQ += dS K_j : A = dS in TMEM (k-steps 0..3 at dP columns 0..31, 4..7 at columns 64..95)
+          // dQ += dS K_j : A = dS in TMEM (k-steps 0..3 at score columns 0..31, 4..7 at columns 64..95)
           const uint32_t kj = k_slot(j);
+          const uint32_t ds_col = ((g + j) & 1) * 128;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
-            umma_bf16_ts(tmem + 384, tmem + 256 + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
+            umma_bf16_ts(tmem + 384, tmem + ds_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
                          make_smem_desc(kj + ks * 2048, 16384, 1024), idesc_mn, (j | ks) != 0 ? 1u : 0u);
           umma_commit(&bar_r_empty[(load + 2 * j) % DQ_RING]);
           umma_commit(&bar_dq_full);
+          // the threads are done with dP(j): the next dP goes first so that they can start on tile j+1
+          // while dQ(j) runs (dS(j) sits in the score buffer of tile j, not in the dP columns)
           if (j + 1 < n) {
             if (!ring_wait(load + 2 * (j + 1) + 1)) { ok = false; break; }
             issue_kk(256, do_addr, v_slot(j + 1));
@@ -286,7 +302,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16x2(ds[2 * i], ds[2 * i + 1]);
         }
-        tmem_st_32x32(t_row + 256 + half * 64, pk);
+        tmem_st_32x32(t_row + (g & 1) * 128 + half * 64, pk);  // over this thread's own score columns
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -326,12 +342,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 }
 
 
-// ----------------------------------------------------------------------------------------- dK, dV
-constexpr int KV_STAGES = 2;
+constexpr int FB_RING = 5;        // dK/dV ring slots, one sub-tile each: two half tiles of 64 rows (2 x 16 KB)
+constexpr int FB_SLOT = 32768;
+constexpr int FB_HALF = 16384;    // 64 rows x 128 columns bf16: [hd chunk 0: 64 rows x 128 B][hd chunk 1]
 
+__device__ __forceinline__ uint32_t fb_a_col(int ks) { return ks < 2 ? ks * 8 : 32 + (ks - 2) * 8; }
+
+// ----------------------------------------------------------------------------------------- dK, dV
 __global__ void __launch_bounds__(FB_THREADS, 1)
-flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_constant__ CUtensorMap mapK,
+                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO64,
                      const FbArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5;
@@ -339,38 +359,40 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = base;
   uint8_t* sV = base + FB_TILE;
-  uint8_t* sSt = base + 2 * FB_TILE;  // stages: {Q_i, dO_i}
-  float* sStat = reinterpret_cast<float*>(base + 6 * FB_TILE);  // [stage][lse2 | dsc][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(base + 6 * FB_TILE + KV_STAGES * 1024);
+  uint8_t* sR = base + 2 * FB_TILE;  // slot: {64 rows of Q_i, 64 rows of dO_i}
+  float* sStat = reinterpret_cast<float*>(base + 7 * FB_TILE);  // [slot][lse2 x 64 | dsc x 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + 7 * FB_TILE + FB_RING * 512);
   uint64_t& bar_kv_full = bars[0];
   uint64_t& bar_kv_empty = bars[1];
-  uint64_t* bar_st_full = bars + 2;   // [KV_STAGES]
-  uint64_t* bar_st_empty = bars + 4;  // [KV_STAGES]
-  uint64_t& bar_s_full = bars[6];
-  uint64_t& bar_ds_full = bars[7];
-  uint64_t& bar_acc_full = bars[8];
-  uint64_t& bar_drain = bars[9];
-  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 10);
-  int& go = *reinterpret_cast<int*>(bars + 11);
+  uint64_t* bar_r_full = bars + 2;    // [FB_RING]
+  uint64_t* bar_r_empty = bars + 7;   // [FB_RING]
+  uint64_t* bar_s_full = bars + 12;   // [2]
+  uint64_t* bar_ds_full = bars + 14;  // [2]
+  uint64_t& bar_acc_full = bars[16];
+  uint64_t& bar_drain = bars[17];
+  uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 18);
+  int& go = *reinterpret_cast<int*>(bars + 19);
 
   if (threadIdx.x == 0) {
     go = 1;
-    if (base + 6 * FB_TILE + KV_STAGES * 1024 + 256 > smem_raw + FB_SMEM) {
+    if (base + 7 * FB_TILE + FB_RING * 512 + 256 > smem_raw + FB_SMEM) {
       report(args.status, ST_BAD_ARGUMENT);
       go = 0;
     }
-    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapQ64);
     tma_prefetch_desc(&mapK);
     tma_prefetch_desc(&mapV);
-    tma_prefetch_desc(&mapDO);
+    tma_prefetch_desc(&mapDO64);
     mbar_init(&bar_kv_full, 1);
     mbar_init(&bar_kv_empty, 1);
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&bar_st_full[s], 1);
-      mbar_init(&bar_st_empty[s], 1);
+    for (int s = 0; s < FB_RING; ++s) {
+      mbar_init(&bar_r_full[s], 1);
+      mbar_init(&bar_r_empty[s], 1);
     }
-    mbar_init(&bar_s_full, 1);
-    mbar_init(&bar_ds_full, 8);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_s_full[s], 1);
+      mbar_init(&bar_ds_full[s], 8);
+    }
     mbar_init(&bar_acc_full, 1);
     mbar_init(&bar_drain, 1);
     fence_mbar_init();
@@ -385,7 +407,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
-  // TMEM columns: S^T 0, dP^T 128, dV 256, dK 384
+  // TMEM columns: S^T[2] at 0 / 64, dP^T[2] at 128 / 192, dV at 256, dK at 384
   const int group = args.nh / args.nkv;
   const int per_j = args.B * args.nkv;
   const int n_qt = args.S >> 7;
@@ -394,7 +416,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
-      uint32_t pc = 0;  // (head, query tile) pairs issued so far
+      uint32_t u = 0;
       int it_count = 0;
       for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
         if (*reinterpret_cast<volatile int*>(args.status) != 0) break;
@@ -410,77 +432,90 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         tma_load_3d(sV + 16384, &mapV, &bar_kv_full, hk * 128 + 64, j * 128, b);
         for (int gi = 0; gi < group && ok; ++gi) {
           const int h = hk * group + gi;
-          for (int i = j; i < n_qt; ++i, ++pc) {
-            const int st = pc % KV_STAGES;
-            if (!mbar_wait_ns(&bar_st_empty[st], ((pc / KV_STAGES) & 1) ^ 1u, FB_LIMIT_NS)) {
+          for (int row0 = j * 128; row0 < args.S; row0 += 64, ++u) {  // query rows of this sub-tile
+            const int slot = u % FB_RING;
+            if (!mbar_wait_ns(&bar_r_empty[slot], ((u / FB_RING) & 1) ^ 1u, FB_LIMIT_NS)) {
               ok = false;
               break;
             }
-            mbar_expect_tx(&bar_st_full[st], 2 * FB_TILE + 1024);
-            uint8_t* dq_ = sSt + st * 2 * FB_TILE;
-            tma_load_3d(dq_, &mapQ, &bar_st_full[st], h * 128, i * 128, b);
-            tma_load_3d(dq_ + 16384, &mapQ, &bar_st_full[st], h * 128 + 64, i * 128, b);
-            tma_load_3d(dq_ + FB_TILE, &mapDO, &bar_st_full[st], h * 128, i * 128, b);
-            tma_load_3d(dq_ + FB_TILE + 16384, &mapDO, &bar_st_full[st], h * 128 + 64, i * 128, b);
-            const long long so = (static_cast<long long>(b) * args.nh + h) * args.S + i * 128;
-            bulk_load_1d(sStat + st * 256, args.lse2 + so, 512, &bar_st_full[st]);
-            bulk_load_1d(sStat + st * 256 + 128, args.dsc + so, 512, &bar_st_full[st]);
+            mbar_expect_tx(&bar_r_full[slot], FB_SLOT + 512);
+            uint8_t* dst = sR + slot * FB_SLOT;
+#pragma unroll
+            for (int kc = 0; kc < 2; ++kc) {
+              tma_load_3d(dst + kc * 8192, &mapQ64, &bar_r_full[slot], h * 128 + kc * 64, row0, b);
+              tma_load_3d(dst + FB_HALF + kc * 8192, &mapDO64, &bar_r_full[slot], h * 128 + kc * 64, row0, b);
+            }
+            const long long so = (static_cast<long long>(b) * args.nh + h) * args.S + row0;
+            bulk_load_1d(sStat + slot * 128, args.lse2 + so, 256, &bar_r_full[slot]);
+            bulk_load_1d(sStat + slot * 128 + 64, args.dsc + so, 256, &bar_r_full[slot]);
           }
         }
       }
       if (!ok) report(args.status, ST_TIMEOUT_PRODUCER);
-      for (uint32_t i = pc > KV_STAGES ? pc - KV_STAGES : 0; i < pc; ++i)
-        (void)mbar_wait_ns(&bar_st_full[i % KV_STAGES], (i / KV_STAGES) & 1, FB_LIMIT_NS);
+      for (uint32_t i = u > FB_RING ? u - FB_RING : 0; i < u; ++i)
+        (void)mbar_wait_ns(&bar_r_full[i % FB_RING], (i / FB_RING) & 1, FB_LIMIT_NS);
       if (it_count > 0) (void)mbar_wait_ns(&bar_kv_full, (it_count - 1) & 1, FB_LIMIT_NS);
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 1);
       bool ok = true;
-      uint32_t pc = 0;
+      uint32_t u0 = 0;
       int it_count = 0;
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      auto slot_addr = [&](uint32_t u) { return smem_u32(sR + (u % FB_RING) * FB_SLOT); };
+      auto ring_wait = [&](uint32_t u) -> bool {
+        const bool r = mbar_wait_ns(&bar_r_full[u % FB_RING], (u / FB_RING) & 1, FB_LIMIT_NS);
+        tc_fence_after();
+        return r;
+      };
+      auto mma1 = [&](uint32_t u) {  // S^T = K_j Q_sub^T, dP^T = V_j dO_sub^T
+        const uint32_t buf = u & 1, qq = slot_addr(u), dd = qq + FB_HALF;
+#pragma unroll
+        for (int kc = 0; kc < 2; ++kc)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16(tmem + buf * 64, make_smem_desc(k_addr + kc * 16384 + k * 32, 16, 1024),
+                      make_smem_desc(qq + kc * 8192 + k * 32, 16, 1024), idesc_s, (kc | k) != 0 ? 1u : 0u);
+            umma_bf16(tmem + 128 + buf * 64, make_smem_desc(v_addr + kc * 16384 + k * 32, 16, 1024),
+                      make_smem_desc(dd + kc * 8192 + k * 32, 16, 1024), idesc_s, (kc | k) != 0 ? 1u : 0u);
+          }
+        umma_commit(&bar_s_full[buf]);
+      };
       for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
         const int j = t / per_j;
-        const int pairs = group * (n_qt - j);
+        const int subs = group * 2 * (n_qt - j);
         ok = mbar_wait_ns(&bar_kv_full, it_count & 1, FB_LIMIT_NS);
         if (!ok) break;
         tc_fence_after();
-        for (int p = 0; p < pairs; ++p, ++pc) {
-          const int st = pc % KV_STAGES;
-          if (!mbar_wait_ns(&bar_st_full[st], (pc / KV_STAGES) & 1, FB_LIMIT_NS)) { ok = false; break; }
+        if (!ring_wait(u0) || !ring_wait(u0 + 1)) { ok = false; break; }
+        mma1(u0);
+        mma1(u0 + 1);
+        for (int m = 0; m < subs; ++m) {
+          const uint32_t u = u0 + m, buf = u & 1;
+          if (!mbar_wait_ns(&bar_ds_full[buf], (u >> 1) & 1, FB_LIMIT_NS)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t q_addr = smem_u32(sSt + st * 2 * FB_TILE), do_addr = q_addr + FB_TILE;
-          // S^T = K_j Q_i^T and dP^T = V_j dO_i^T
+          const uint32_t qq = slot_addr(u), dd = qq + FB_HALF;
+          // dV += P^T dO_sub, dK += dS^T Q_sub : A from TMEM, B = the 64 query rows read MN-major
 #pragma unroll
-          for (int kc = 0; kc < 2; ++kc)
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_bf16(tmem, make_smem_desc(k_addr + kc * 16384 + k * 32, 16, 1024),
-                        make_smem_desc(q_addr + kc * 16384 + k * 32, 16, 1024), idesc_kk, (kc | k) != 0 ? 1u : 0u);
-#pragma unroll
-          for (int kc = 0; kc < 2; ++kc)
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_bf16(tmem + 128, make_smem_desc(v_addr + kc * 16384 + k * 32, 16, 1024),
-                        make_smem_desc(do_addr + kc * 16384 + k * 32, 16, 1024), idesc_kk, (kc | k) != 0 ? 1u : 0u);
-          umma_commit(&bar_s_full);
-          if (!mbar_wait_ns(&bar_ds_full, pc & 1, FB_LIMIT_NS)) { ok = false; break; }
-          tc_fence_after();
-          // dV += P^T dO_i (A: columns 0.. of S^T), dK += dS^T Q_i (A: columns 0.. of dP^T); B read MN-major
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_bf16_ts(tmem + 256, tmem + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
-                         make_smem_desc(do_addr + ks * 2048, 16384, 1024), idesc_mn, (p | ks) != 0 ? 1u : 0u);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_bf16_ts(tmem + 384, tmem + 128 + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
-                         make_smem_desc(q_addr + ks * 2048, 16384, 1024), idesc_mn, (p | ks) != 0 ? 1u : 0u);
-          umma_commit(&bar_st_empty[st]);
-          umma_commit(&bar_acc_full);
-          if (p == pairs - 1) umma_commit(&bar_kv_empty);
+          for (int ks = 0; ks < 4; ++ks) {
+            umma_bf16_ts(tmem + 256, tmem + buf * 64 + fb_a_col(ks), make_smem_desc(dd + ks * 2048, 8192, 1024),
+                         idesc_g, (m | ks) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem + 384, tmem + 128 + buf * 64 + fb_a_col(ks), make_smem_desc(qq + ks * 2048, 8192, 1024),
+                         idesc_g, (m | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(&bar_r_empty[u % FB_RING]);
+          if (m == subs - 1) {
+            umma_commit(&bar_acc_full);
+            umma_commit(&bar_kv_empty);
+          }
+          if (m + 2 < subs) {
+            if (!ring_wait(u + 2)) { ok = false; break; }
+            mma1(u + 2);
+          }
         }
+        u0 += subs;
       }
       if (!ok) report(args.status, ST_TIMEOUT_MMA);
       umma_commit(&bar_drain);
@@ -493,57 +528,56 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     const uint32_t t_row = tmem + (static_cast<uint32_t>(q4 * 32) << 16);
     const float sl2 = args.scale_log2, scale = args.scale;
     bool ok = true;
-    uint32_t pc = 0;
+    uint32_t u = 0;
     int it_count = 0;
     for (int t; (t = fb_sched(it_count, blockIdx.x, gridDim.x)) < args.items && ok; ++it_count) {
       const int j = t / per_j, r = t % per_j, b = r / args.nkv, hk = r % args.nkv;
-      const int per_head = n_qt - j, pairs = group * per_head;
-      for (int p = 0; p < pairs; ++p, ++pc) {
-        if (!mbar_wait_ns(&bar_s_full, pc & 1, FB_LIMIT_NS)) {
+      const int per_head = 2 * (n_qt - j), subs = group * per_head;
+      for (int m = 0; m < subs; ++m, ++u) {
+        const uint32_t buf = u & 1;
+        if (!mbar_wait_ns(&bar_s_full[buf], (u >> 1) & 1, FB_LIMIT_NS)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const float* stat = sStat + (pc % KV_STAGES) * 256 + half * 64;
-        const bool diag = (p % per_head) == 0;  // query tile == key tile: query index must be >= key index
-        uint32_t pp[32], pd[32];
+        const float* stat = sStat + (u % FB_RING) * 128 + half * 32;
+        // query tile == key tile (the first two sub-tiles of every head): query index must be >= key index
+        const int mh = m % per_head;
+        const int col0 = mh < 2 ? mh * 64 + half * 32 : 1024;
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32(t_row + buf * 64 + half * 32, s);
+        tmem_ld_32x32(t_row + 128 + buf * 64 + half * 32, dp);
+        tmem_ld_wait();
+        uint32_t pp[16], pd[16];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t s[32], dp[32];
-          tmem_ld_32x32(t_row + half * 64 + c * 32, s);
-          tmem_ld_32x32(t_row + 128 + half * 64 + c * 32, dp);
-          tmem_ld_wait();
-          float pv[32], ds[32];
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(stat + i4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(stat + 64 + i4 * 4);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv_[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pe[4], de[4];
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(stat + c * 32 + i4 * 4);
-            const float4 d4 = *reinterpret_cast<const float4*>(stat + 128 + c * 32 + i4 * 4);
-            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv_[4] = {d4.x, d4.y, d4.z, d4.w};
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int i = i4 * 4 + u;
-              const float x = fmaf(__uint_as_float(s[i]), sl2, -lv[u]);
-              float pe = u == 3 ? ex2_poly(x) : ex2_approx(x);
-              if (diag && half * 64 + c * 32 + i < row_l) pe = 0.f;
-              pv[i] = pe;
-              ds[i] = pe * fmaf(__uint_as_float(dp[i]), scale, -dv_[u]);
-            }
+          for (int e4 = 0; e4 < 4; ++e4) {
+            const int c = i4 * 4 + e4;
+            const float x = fmaf(__uint_as_float(s[c]), sl2, -lv[e4]);
+            float p = e4 == 3 ? ex2_poly(x) : ex2_approx(x);
+            if (col0 + c < row_l) p = 0.f;
+            pe[e4] = p;
+            de[e4] = p * fmaf(__uint_as_float(dp[c]), scale, -dv_[e4]);
           }
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            pp[c * 16 + i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
-            pd[c * 16 + i] = pack_bf16x2(ds[2 * i], ds[2 * i + 1]);
-          }
+          pp[i4 * 2] = pack_bf16x2(pe[0], pe[1]);
+          pp[i4 * 2 + 1] = pack_bf16x2(pe[2], pe[3]);
+          pd[i4 * 2] = pack_bf16x2(de[0], de[1]);
+          pd[i4 * 2 + 1] = pack_bf16x2(de[2], de[3]);
         }
-        tmem_st_32x32(t_row + half * 64, pp);
-        tmem_st_32x32(t_row + 128 + half * 64, pd);
+        tmem_st_32x16(t_row + buf * 64 + half * 32, pp);
+        tmem_st_32x16(t_row + 128 + buf * 64 + half * 32, pd);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_ds_full);
+        if (lane == 0) mbar_arrive(&bar_ds_full[buf]);
       }
       if (!ok) break;
-      if (!mbar_wait_ns(&bar_acc_full, (pc - 1) & 1, FB_LIMIT_NS)) {
+      if (!mbar_wait_ns(&bar_acc_full, it_count & 1, FB_LIMIT_NS)) {
         ok = false;
         break;
       }
@@ -587,12 +621,14 @@ extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const
                               const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int nh,
                               int nkv, float softmax_scale, int* status, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mq64, mdo64;
   const uint64_t qrow = static_cast<uint64_t>(nh) * 128, krow = static_cast<uint64_t>(nkv) * 128;
   int rc = make_map(&mq, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
   if (rc == 0) rc = make_map(&mdo, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
   if (rc == 0) rc = make_map(&mk, k, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
   if (rc == 0) rc = make_map(&mv, v, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
+  if (rc == 0) rc = make_map(&mq64, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 64);
+  if (rc == 0) rc = make_map(&mdo64, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 64);
   if (rc != 0) return rc - 100;
   static bool configured = false;
   static int sms = 0;
@@ -622,6 +658,6 @@ extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const
   a.items = B * nh * (S / 128);
   flash_bwd_dq_kernel<<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq, mk, mv, mdo, a);
   a.items = B * nkv * (S / 128);
-  flash_bwd_dkv_kernel<<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq, mk, mv, mdo, a);
+  flash_bwd_dkv_kernel<<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq64, mk, mv, mdo64, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -373,12 +373,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           for (int c8 = 0; c8 < 8; ++c8) {
             float p[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              // every fourth exponential runs on the FMA pipe: the XU pipe (one ex2 per 8 cycles and warp)
-              // is the busiest unit of this loop
-              const float xx = fmaf(__uint_as_float(r[c8 * 8 + i]), sl2, -mb);
-              p[i] = (i & 3) == 3 ? ex2_poly(xx) : ex2_approx(xx);
-            }
+            for (int i = 0; i < 8; ++i) p[i] = ex2_approx(fmaf(__uint_as_float(r[c8 * 8 + i]), sl2, -mb));
             rs0 += p[0] + p[4];
             rs1 += p[1] + p[5];
             rs2 += p[2] + p[6];

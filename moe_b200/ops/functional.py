@@ -302,9 +302,11 @@ _ATTN_STATE = {"library_backward_ok": None, "dummy": {}}
 
 class FlashAttnFn(torch.autograd.Function):
     """Causal GQA attention.  Forward: `csrc/attn/flash_fwd.cu` (returns the base-2 log-sum-exp per row).
-    Backward: the cuDNN flash-attention backward kernel (a library call), which takes the forward's
-    output and natural-log log-sum-exp as inputs; if that entry point is not usable in the running
-    torch build, the gradients are obtained by differentiating a recomputed library forward."""
+    Backward: `csrc/attn/flash_bwd.cu` (delta, dQ and dK/dV kernels).  MOE_B200_ATTN_BWD=library switches
+    the backward to the cuDNN flash-attention kernel, which takes the forward's output and natural-log
+    log-sum-exp as inputs (about 1.4x faster than the own kernels at B=8, S=2048, 16/8 heads); if that
+    entry point is not usable in the running torch build, the gradients then come from differentiating a
+    recomputed library forward."""
 
     @staticmethod
     def forward(ctx, q, k, v):
@@ -323,7 +325,7 @@ class FlashAttnFn(torch.autograd.Function):
         q, k, v, o, lse2 = ctx.saved_tensors
         B, S, nh, hd = q.shape
         do = do.contiguous()
-        if os.environ.get("MOE_B200_ATTN_BWD", "library") == "own":
+        if os.environ.get("MOE_B200_ATTN_BWD", "own") != "library":
             dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
             delta = torch.empty_like(lse2)
             ext().flash_bwd(q, k, v, o, do, lse2, delta, dq, dk, dv, ctx.scale, G.status_word(q.device))
