@@ -77,7 +77,8 @@ class FusedAllReduce:
         self.state_f = torch.zeros(2, dtype=torch.float32, device=device)
         self.epoch_base = torch.ones(1, dtype=torch.int32, device=device)
         self.status = status
-        self.blocks, self.limit_ns = blocks, limit_ns
+        # CTAs of the reduce kernel: enough loads in flight for NVLink, few enough to leave the SMs to backward
+        self.blocks, self.limit_ns = int(os.environ.get("MOE_B200_AR_BLOCKS", blocks)), limit_ns
         self.launched = 0  # buckets since the last `end_step`
 
     def reduce(self, off: int, n: int, final_bucket: bool, publish: bool = True) -> None:
