@@ -14,9 +14,9 @@ int b200_flash_fwd(const void* q, const void* k, const void* v, void* o, float* 
                    float softmax_scale, int* status, cudaStream_t stream);
 
 // Gradients of the same attention (same shape rules).  delta [B,nh,S] fp32 is scratch: it receives
-// softmax_scale * rowsum(dO * O).  dq [B,S,nh,128], dk/dv [B,S,nkv,128] bf16 are overwritten.  Two
-// launches: dQ (one query tile per work item, loops over key tiles; also produces delta) and dK/dV (one
-// key tile per work item, loops over the query heads of its group and their query tiles).
+// softmax_scale * rowsum(dO * O).  dq [B,S,nh,128], dk/dv [B,S,nkv,128] bf16 are overwritten.  Three
+// launches: delta, dQ (one query tile per work item, loops over key tiles) and dK/dV (one key tile per
+// work item, loops over the query heads of its group and their query tiles).
 int b200_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                    float* delta, void* dq, void* dk, void* dv, int B, int S, int nh, int nkv, float softmax_scale,
                    int* status, cudaStream_t stream);

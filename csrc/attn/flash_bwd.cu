@@ -1,7 +1,7 @@
-// Causal grouped-query flash attention, backward, for sm_100a (head_dim 128).  Two kernels:
+// Causal grouped-query flash attention, backward, for sm_100a (head_dim 128).  Three kernels:
 //
-//   dQ    : (first, per query row: Dsc = softmax_scale * sum_d dO * O, kept for the second kernel)
-//           work item = (batch, query head, 128 query rows); loops over key tiles j <= query tile:
+//   delta : Dsc[b,h,s] = softmax_scale * sum_d dO[b,s,h,d] * O[b,s,h,d]
+//   dQ    : work item = (batch, query head, 128 query rows); loops over key tiles j <= query tile:
 //             S = Q K_j^T, dP = dO V_j^T                       (both operands in shared memory)
 //             P = exp2(S*c - lse2), dS = P * (dP*scale - Dsc)   (one query row per pair of threads)
 //             dQ += dS K_j                                      (dS from TMEM, K_j read MN-major)
@@ -18,8 +18,12 @@
 // dQ kernel: 128 x 128 score tiles, the score buffer double-buffered in TMEM (S[2], dP, dQ = 512 columns).
 // Of a tile, warps 2..5 take columns 0..63 and warps 6..9 columns 64..127; a thread writes its 64 dS values
 // (bf16 pairs, tcgen05.st) over the first 32 of the score columns it has just read, and dQ += dS K_j takes
-// them as its A operand from TMEM.  Issue order: S(0) dP(0) S(1) | dP(1) dQ(0) S(2) | dP(2) dQ(1) S(3) | ...
+// them as its A operand from TMEM.  Issue order: S(0) dP(0) S(1) | dQ(0) dP(1) S(2) | dQ(1) dP(2) S(3) | ...
 // (MMAs of one thread execute in issue order, so S(j+2) may overwrite the columns dS(j) was read from).
+// dP(j+1) stays behind dQ(j) although the dP columns are free earlier: with the threads of tile j+1 reading
+// TMEM while the dQ(j) MMAs (TMEM operand) run, the kernel took 350 us instead of about 220 us.  Folding the
+// delta pre-pass into this kernel (per-row dot product at the start of a work item) cost 30 us more than
+// the separate 46 us kernel saves, so delta stays a kernel of its own.
 // K_j is one ring slot that is read K-major by the score MMA and MN-major by the gradient MMA.
 //
 // dK/dV kernel: all 512 TMEM columns would be live with 128-wide score tiles (S^T, dP^T, dV, dK) and
@@ -45,9 +49,7 @@ constexpr unsigned long long FB_LIMIT_NS = 2000000000ull;
 
 struct FbArgs {
   const float* lse2;  // [B, nh, S]
-  float* dsc;         // [B, nh, S]: written by the dQ kernel, read by the dK/dV kernel
-  const __nv_bfloat16* o;    // [B, S, nh, 128]
-  const __nv_bfloat16* d_o;  // [B, S, nh, 128]
+  const float* dsc;   // [B, nh, S]
   __nv_bfloat16* dq;  // [B, S, nh, 128]
   __nv_bfloat16* dk;  // [B, S, nkv, 128]
   __nv_bfloat16* dv;
@@ -59,6 +61,28 @@ struct FbArgs {
 
 __device__ __forceinline__ int fb_sched(int round, int cta, int ctas) {
   return round * ctas + ((round & 1) ? ctas - 1 - cta : cta);
+}
+
+// ----------------------------------------------------------------------------------------- delta
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ dsc, int B, int S, int nh, float scale) {
+  // one warp per (b, s, h): 128 elements, 4 per lane
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * nh;
+  if (w >= total) return;
+  const uint2 a = reinterpret_cast<const uint2*>(o + w * 128)[lane];
+  const uint2 b = reinterpret_cast<const uint2*>(d_o + w * 128)[lane];
+  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  s = warp_sum(s);
+  if (lane == 0) {
+    const long long bs = w / nh;
+    const int h = static_cast<int>(w - bs * nh);
+    const long long b_ = bs / S;
+    const int s_ = static_cast<int>(bs - b_ * S);
+    dsc[(b_ * nh + h) * S + s_] = s * scale;
+  }
 }
 
 // -------------------------------------------------------------------------------------------- dQ
@@ -87,12 +111,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   uint64_t& bar_drain = bars[17];
   uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 18);
   int& go = *reinterpret_cast<int*>(bars + 19);
-  uint64_t& bar_delta = bars[20];
-  float (*xdelta)[128] = reinterpret_cast<float (*)[128]>(base + 7 * FB_TILE + 256);  // [half][row]
 
   if (threadIdx.x == 0) {
     go = 1;
-    if (base + 7 * FB_TILE + 256 + 1024 > smem_raw + FB_SMEM) {
+    if (base + 7 * FB_TILE + 256 > smem_raw + FB_SMEM) {
       report(args.status, ST_BAD_ARGUMENT);
       go = 0;
     }
@@ -110,7 +132,6 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     mbar_init(&bar_s_full[1], 1);
     mbar_init(&bar_dp_full, 1);
     mbar_init(&bar_ds_full, 8);
-    mbar_init(&bar_delta, 8);
     mbar_init(&bar_dq_full, 1);
     mbar_init(&bar_drain, 1);
     fence_mbar_init();
@@ -214,6 +235,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         for (int j = 0; j < n; ++j) {
           if (!mbar_wait_ns(&bar_ds_full, (g + j) & 1, FB_LIMIT_NS)) { ok = false; break; }
           tc_fence_after();
+          // dQ += dS K_j : A = dS in TMEM (k-steps 0..3 at score columns 0..31, 4..7 at columns 64..95)
+          const uint32_t kj = k_slot(j);
+          const uint32_t ds_col = ((g + j) & 1) * 128;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_bf16_ts(tmem + 384, tmem + ds_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
+                         make_smem_desc(kj + ks * 2048, 16384, 1024), idesc_mn, (j | ks) != 0 ? 1u : 0u);
+          umma_commit(&bar_r_empty[(load + 2 * j) % DQ_RING]);
+          umma_commit(&bar_dq_full);
           // the threads are done with dP(j): the next dP goes first so that they can start on tile j+1
           // while dQ(j) runs (dS(j) sits in the score buffer of tile j, not in the dP columns)
           if (j + 1 < n) {
@@ -223,17 +253,6 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
             umma_commit(&bar_dp_full);
             if (j + 1 == n - 1) umma_commit(&bar_q_empty);
           }
-          // dQ += dS K_j : A = dS in TMEM (k-steps 0..3 at score columns 0..31, 4..7 at columns 64..95)
-          const uint32_t kj = k_slot(j);
-          const uint32_t ds_col = ((g + j) & 1) * 128;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_bf16_ts(tmem + 384, tmem + ds_col + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
-                         make_smem_desc(kj + ks * 2048, 16384, 1024), idesc_mn, (j | ks) != 0 ? 1u : 0u);
-          umma_commit(&bar_r_empty[(load + 2 * j) % DQ_RING]);
-          // one completion per work item: a per-tile completion could be a whole phase behind the threads,
-          // whose parity wait would then be satisfied by the phase before
-          if (j == n - 1) umma_commit(&bar_dq_full);
           if (j + 2 < n) {
             if (!ring_wait(load + 2 * (j + 2))) { ok = false; break; }
             issue_kk(((g + j + 2) & 1) * 128, q_addr, k_slot(j + 2));
@@ -260,36 +279,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       const int qt = n_qt - 1 - t / per_qt, r = t % per_qt, b = r / args.nh, h = r % args.nh;
       const int n = qt + 1;
       const long long stat = (static_cast<long long>(b) * args.nh + h) * args.S + qt * 128 + row_l;
-      const float lse2 = args.lse2[stat];
-      // delta = scale * sum_d dO * O of this row: each of the row's two threads sums 64 columns (the loads
-      // overlap with the first score MMAs), the halves meet in shared memory
-      float dsc;
-      {
-        const long long eo = ((static_cast<long long>(b) * args.S + qt * 128 + row_l) * args.nh + h) * 128 + half * 64;
-        const uint4* po = reinterpret_cast<const uint4*>(args.o + eo);
-        const uint4* pd = reinterpret_cast<const uint4*>(args.d_o + eo);
-        float acc = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint4 a = po[i], d = pd[i];
-          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 af = unpack_bf16x2(aw[e]), df = unpack_bf16x2(dw[e]);
-            acc = fmaf(af.x, df.x, acc);
-            acc = fmaf(af.y, df.y, acc);
-          }
-        }
-        xdelta[half][row_l] = acc;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_delta);
-        if (!mbar_wait_ns(&bar_delta, it_count & 1, FB_LIMIT_NS)) {
-          ok = false;
-          break;
-        }
-        dsc = (acc + xdelta[half ^ 1][row_l]) * scale;
-        if (half == 0) args.dsc[stat] = dsc;
-      }
+      const float lse2 = args.lse2[stat], dsc = args.dsc[stat];
       for (int j = 0; j < n; ++j, ++g) {
         if (!mbar_wait_ns(&bar_s_full[g & 1], (g >> 1) & 1, FB_LIMIT_NS) ||
             !mbar_wait_ns(&bar_dp_full, g & 1, FB_LIMIT_NS)) {
@@ -323,7 +313,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         if (lane == 0) mbar_arrive(&bar_ds_full);
       }
       if (!ok) break;
-      if (!mbar_wait_ns(&bar_dq_full, it_count & 1, FB_LIMIT_NS)) {
+      if (!mbar_wait_ns(&bar_dq_full, (g - 1) & 1, FB_LIMIT_NS)) {
         ok = false;
         break;
       }
@@ -655,11 +645,13 @@ extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     configured = true;
   }
+  const long long rows = static_cast<long long>(B) * S * nh;
+  attn_delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, nh,
+      softmax_scale);
   FbArgs a;
   a.lse2 = lse;
   a.dsc = delta;
-  a.o = reinterpret_cast<const __nv_bfloat16*>(o);
-  a.d_o = reinterpret_cast<const __nv_bfloat16*>(d_o);
   a.dq = reinterpret_cast<__nv_bfloat16*>(dq);
   a.dk = reinterpret_cast<__nv_bfloat16*>(dk);
   a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
