@@ -32,6 +32,9 @@ namespace b200 {
 constexpr int FA_THREADS = 320;
 constexpr int FA_TILE = 32768;   // 128 x 128 bf16
 constexpr int FA_RING = 5;       // K/V slots
+#ifndef FA_POLY_PAIRS
+#define FA_POLY_PAIRS 1           // of every four pairs of exponentials, how many run on the FMA pipe
+#endif
 constexpr int FA_EXTRA = 256;    // barriers
 constexpr int FA_SMEM = 232448;  // everything a CTA may have; the seven tiles alone take 224 KB
 constexpr unsigned long long FA_LIMIT_NS = 2000000000ull;  // nothing here waits on another GPU
@@ -41,7 +44,7 @@ struct FaFwdArgs {
   float* lse;
   int B, S, nh, nkv;
   int items;
-  float scale_log2;
+  float scale_log2, inv_scale_log2;
   int* status;
 };
 
@@ -348,7 +351,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         // pass 2: exponentials -> P as bf16 pairs over the first 64 columns of this row's scores.  Columns
         // [32 hh, 32 hh + 32) are written after score columns [64 hh, 64 hh + 64) have been read.
         const float mb = m_ref * sl2;
+        const float s_min = m_ref - 126.0f * args.inv_scale_log2;  // scores below it would underflow 2^-126
         float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+        uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
           uint32_t r[64];
@@ -369,22 +374,57 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
               if (hh * 64 + c > row_l) r[c] = 0xff800000u;
           }
           uint32_t pk[32];
+          if (diag) {
 #pragma unroll
-          for (int c8 = 0; c8 < 8; ++c8) {
-            float p[8];
+            for (int c8 = 0; c8 < 8; ++c8) {
+              float p[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) p[i] = ex2_approx(fmaf(__uint_as_float(r[c8 * 8 + i]), sl2, -mb));
-            rs0 += p[0] + p[4];
-            rs1 += p[1] + p[5];
-            rs2 += p[2] + p[6];
-            rs3 += p[3] + p[7];
+              for (int i = 0; i < 8; ++i) p[i] = ex2_approx(fmaf(__uint_as_float(r[c8 * 8 + i]), sl2, -mb));
+              rs0 += p[0] + p[4];
+              rs1 += p[1] + p[5];
+              rs2 += p[2] + p[6];
+              rs3 += p[3] + p[7];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) pk[c8 * 4 + i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+              for (int i = 0; i < 4; ++i) pk[c8 * 4 + i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
+            }
+          } else {
+            // two values per issue slot (f32x2) for the scale, the sums and a polynomial exp2 on the FMA
+            // pipe for FA_POLY_PAIRS of every four pairs: the XU pipe (one ex2 per 8 cycles and warp, two
+            // softmax warps per scheduler) is the unit this loop waits for
+            const uint64_t sl2_2 = pack2(sl2, sl2), nmb2 = pack2(-mb, -mb);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                float lo = __uint_as_float(r[c8 * 8 + 2 * k]), hi = __uint_as_float(r[c8 * 8 + 2 * k + 1]);
+                uint64_t p2;
+                if (k >= 4 - FA_POLY_PAIRS) {
+                  lo = fmaxf(lo, s_min);
+                  hi = fmaxf(hi, s_min);
+                  p2 = ex2_poly2(fma2(pack2(lo, hi), sl2_2, nmb2));
+                } else {
+                  float xl, xh;
+                  unpack2(fma2(pack2(lo, hi), sl2_2, nmb2), xl, xh);
+                  p2 = pack2(ex2_approx(xl), ex2_approx(xh));
+                }
+                acc2[k] = add2(acc2[k], p2);
+                float pl, ph;
+                unpack2(p2, pl, ph);
+                pk[c8 * 4 + k] = pack_bf16x2(pl, ph);
+              }
+            }
           }
           tmem_st_32x32(t_s + hh * 32, pk);
         }
         tmem_st_wait();
-        l_run += (rs0 + rs1) + (rs2 + rs3);
+        {
+          float a0, a1, a2, a3, a4, a5, a6, a7;
+          unpack2(acc2[0], a0, a1);
+          unpack2(acc2[1], a2, a3);
+          unpack2(acc2[2], a4, a5);
+          unpack2(acc2[3], a6, a7);
+          l_run += ((rs0 + rs1) + (rs2 + rs3)) + (((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7)));
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_p_full[x]);
@@ -456,6 +496,7 @@ extern "C" int b200_flash_fwd(const void* q, const void* k, const void* v, void*
   a.B = B; a.S = S; a.nh = nh; a.nkv = nkv;
   a.items = B * (nh / 2) * (S / 128);
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  a.inv_scale_log2 = 1.0f / a.scale_log2;
   a.status = status;
   const int grid = a.items < sms ? a.items : sms;
   flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(mq, mk, mv, a);

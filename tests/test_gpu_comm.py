@@ -130,9 +130,12 @@ def _ddp_rank(rank, world, port, out_dir):
     g = torch.Generator().manual_seed(0)
     full = [torch.randint(0, 2048, (4, 128), generator=g) for _ in range(3)]
     res = {}
-    for comm, overlap in (("nccl", False), ("p2p", False), ("p2p", True), ("zero", False), ("zero", True)):
+    # "p2p-again" repeats a configuration: what two runs of the same thing differ by (fp32 atomics) is the
+    # yardstick for the sharded optimizer
+    for comm, overlap in (("nccl", False), ("p2p", False), ("p2p", True), ("p2p-again", True), ("zero", False),
+                          ("zero", True)):
         model, _ = build_model(tiny_cfg("dense"), seed=3, device=f"cuda:{rank}")
-        eng = TrainEngine(model, lr=1e-3, comm="p2p" if comm == "zero" else comm, overlap_grad_reduce=overlap,
+        eng = TrainEngine(model, lr=1e-3, comm="nccl" if comm == "nccl" else "p2p", overlap_grad_reduce=overlap,
                           shard_optimizer=comm == "zero")
         for b in full:
             mine = b[rank * 2:(rank + 1) * 2].cuda()
@@ -147,7 +150,7 @@ def _ddp_rank(rank, world, port, out_dir):
             st = eng.optimizer_state_dict()
             res[(comm, overlap, "p16")] = (eng.p16.clone().cpu(), 0.0)
             res[(comm, overlap, "m")] = (torch.cat([v["exp_avg"].reshape(-1) for v in st["state"].values()]), 0.0)
-        elif comm == "p2p":
+        elif comm.startswith("p2p"):
             st = eng.optimizer_state_dict()
             res[(comm, overlap, "p16")] = (eng.p16.clone().cpu(), 0.0)
             res[(comm, overlap, "m")] = (torch.cat([v["exp_avg"].reshape(-1) for v in st["state"].values()]), 0.0)
@@ -173,11 +176,13 @@ def test_two_gpu_fused_allreduce_matches_nccl(tmp_path):
     # sharded optimizer: same arithmetic per element as the replicated one.  What differs run to run is the
     # order of fp32 atomics (embedding gradient, sum of squares); Adam's normalisation turns a residue of
     # 1e-9 in a gradient that should cancel to zero into an update of 1e-4 * lr, hence fractions, not maxima
+    noise = ((a[("p2p-again", True)][0] - a[("p2p", True)][0]).abs() > 1e-5).float().mean().item()
     for overlap in (False, True):
         for what in ((), ("m",)):
             z, r = a[("zero", overlap, *what)], a[("p2p", overlap, *what)]
             d = (z[0] - r[0]).abs()
-            assert d.max() < 5e-3 and (d > 1e-5).float().mean() < 1e-2, (overlap, what, d.max(), (d > 1e-5).float().mean())
+            frac = (d > 1e-5).float().mean().item()
+            assert d.max() < 5e-3 and frac < max(1e-2, 3 * noise), (overlap, what, d.max(), frac, noise)
         z, r = a[("zero", overlap, "p16")][0].float(), a[("p2p", overlap, "p16")][0].float()
         assert (z - r).abs().max() < 1e-2 and (z != r).float().mean() < 2e-2
         assert abs(a[("zero", overlap)][1] - a[("p2p", overlap)][1]) < 1e-4 * gn
