@@ -33,7 +33,8 @@ constexpr int FA_THREADS = 320;
 constexpr int FA_TILE = 32768;   // 128 x 128 bf16
 constexpr int FA_RING = 5;       // K/V slots
 #ifndef FA_POLY_PAIRS
-#define FA_POLY_PAIRS 1           // of every four pairs of exponentials, how many run on the FMA pipe
+#define FA_POLY_PAIRS 0           // of every four pairs of exponentials, how many run on the FMA pipe (measured
+                                  // at B=8, S=2048, 16/8 heads: 0 -> 0.148 ms, 1 -> 0.151, 2 -> 0.158, 3 -> 0.171)
 #endif
 constexpr int FA_EXTRA = 256;    // barriers
 constexpr int FA_SMEM = 232448;  // everything a CTA may have; the seven tiles alone take 224 KB
@@ -388,9 +389,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
               for (int i = 0; i < 4; ++i) pk[c8 * 4 + i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
             }
           } else {
-            // two values per issue slot (f32x2) for the scale, the sums and a polynomial exp2 on the FMA
-            // pipe for FA_POLY_PAIRS of every four pairs: the XU pipe (one ex2 per 8 cycles and warp, two
-            // softmax warps per scheduler) is the unit this loop waits for
+            // two values per issue slot (f32x2) for the scale and the sums: this loop is bound by issue
+            // slots (0.158 -> 0.148 ms).  FA_POLY_PAIRS of every four pairs could take a polynomial exp2 on
+            // the FMA pipe instead of the XU pipe; every share measured slower than none
             const uint64_t sl2_2 = pack2(sl2, sl2), nmb2 = pack2(-mb, -mb);
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
