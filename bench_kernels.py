@@ -187,7 +187,7 @@ def case_allreduce_emulated(small):
     bufs = [torch.randn(n, device="cuda") for _ in range(world)]
     flags = [torch.full((16,), 1 << 30, dtype=torch.int32, device="cuda") for _ in range(world)]
     norms = [torch.zeros(8, device="cuda") for _ in range(world)]
-    si, sf = torch.zeros(2, dtype=torch.int32, device="cuda"), torch.zeros(2, device="cuda")
+    si, sf = torch.zeros(2, dtype=torch.int32, device="cuda"), torch.zeros(150, device="cuda")
     ep = torch.ones(1, dtype=torch.int32, device="cuda")
     st = G.status_word(torch.device("cuda"))
     args = ([b.data_ptr() for b in bufs], [f.data_ptr() for f in flags], [x.data_ptr() for x in norms], 0)

@@ -288,6 +288,7 @@ void allreduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>& fla
                const Tensor& epoch_base, int64_t epoch_off, bool final_bucket, bool publish, bool use_multimem,
                int64_t blocks, Tensor& state_i, Tensor& state_f, Tensor& status, int64_t limit_ns) {
   i32c(epoch_base, "epoch_base"); i32c(state_i, "state_i"); f32c(state_f, "state_f"); i32c(status, "status");
+  need(state_f.numel() >= 2 + 148, "allreduce: state_f holds 2 + 148 floats");
   need((int64_t)bufs.size() >= world && (int64_t)flags.size() >= world && (int64_t)norms.size() >= world,
        "peer pointer lists shorter than world");
   c10::cuda::CUDAGuard g(status.device());

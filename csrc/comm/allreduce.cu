@@ -50,7 +50,8 @@ __device__ __forceinline__ void multimem_st_f4(float* mc, float4 v) {
                : "memory");
 }
 
-// state: local scratch, int[2] + float[2]: {blocks finished, unused} / {this bucket's sum, running sum of the step}
+// state: local scratch, int[2] + float[2 + 148]: {blocks finished, unused} / {unused, running sum of the step,
+// one partial sum of squares per block}
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(AR_THREADS)
 allreduce_kernel(ArPeers peers, float* mc_buf, int rank, int world, long long off, long long n, float scale,
@@ -154,12 +155,15 @@ allreduce_kernel(ArPeers peers, float* mc_buf, int rank, int world, long long of
   if (threadIdx.x == 0) {
     float s = 0.f;
     for (int i = 0; i < AR_THREADS / 32; ++i) s += sh[i];
-    atomicAdd(&state_f[0], s);
+    // per-block slots summed in block order by the last block: the same data always give the same
+    // bits, whatever order the blocks finish in (an atomic running sum would not)
+    state_f[2 + blockIdx.x] = s;
     __threadfence_system();
     const int ticket = atomicAdd(&state_i[0], 1);
     if (ticket == static_cast<int>(gridDim.x) - 1) {
       __threadfence();
-      const float bucket = atomicExch(&state_f[0], 0.f);
+      float bucket = 0.f;
+      for (unsigned b = 0; b < gridDim.x; ++b) bucket += *(reinterpret_cast<volatile float*>(state_f) + 2 + b);
       const float total = state_f[1] + bucket;
       state_f[1] = final_bucket ? 0.f : total;
       state_i[0] = 0;

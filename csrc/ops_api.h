@@ -73,7 +73,8 @@ typedef struct B200Peers {
 } B200Peers;
 // One bucket [off, off+n) of the gradient buffer: average over ranks in place on every rank.
 // epoch = *epoch_base + epoch_off must grow with every launch and agree across ranks.
-// state_i: int[2], state_f: float[2], both zero-initialised local scratch.
+// state_i: int[2], state_f: float[2 + 148] (running sum + one partial per block), both zero-initialised
+// local scratch.
 int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long long n, float scale,
                    const int* epoch_base, int epoch_off, int final_bucket, int publish, int use_multimem, int blocks,
                    int* state_i, float* state_f, int* status, unsigned long long limit_ns, cudaStream_t stream);

@@ -74,7 +74,7 @@ class FusedAllReduce:
         self.ext, self.rank, self.world = ext, rank, world
         self.grad_ptrs, self.flag_ptrs, self.norm_ptrs, self.mc = grad_ptrs, flag_ptrs, norm_ptrs, multicast_ptr
         self.state_i = torch.zeros(2, dtype=torch.int32, device=device)
-        self.state_f = torch.zeros(2, dtype=torch.float32, device=device)
+        self.state_f = torch.zeros(2 + 148, dtype=torch.float32, device=device)  # running sum + per-block partials
         self.epoch_base = torch.ones(1, dtype=torch.int32, device=device)
         self.status = status
         # CTAs of the reduce kernel: enough loads in flight for NVLink, few enough to leave the SMs to backward
