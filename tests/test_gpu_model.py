@@ -29,14 +29,17 @@ def tiny_cfg(mtype="standard_moe", **kw):
 
 
 @pytest.mark.parametrize("mtype", ["standard_moe", "global_moe", "deepseek_standard_moe", "deepseek_global_moe",
-                                   "dense"])
+                                   "dense", "dense-hd128"])
 def test_forward_backward_matches_oracle(mtype):
     from moe_b200 import ops
     from moe_b200.models import build_model
     from moe_b200.ops import gemm as G
 
     torch.manual_seed(0)
-    model, _ = build_model(tiny_cfg(mtype), seed=1, device="cuda")
+    extra = {}
+    if mtype == "dense-hd128":  # head_dim 128: the own flash-attention kernels instead of SDPA
+        mtype, extra = "dense", dict(head_dim=128)
+    model, _ = build_model(tiny_cfg(mtype, **extra), seed=1, device="cuda")
     with torch.no_grad():  # compare on bf16-representable weights
         for r in (model.routers() if mtype != "dense" else []):
             r.weight.mul_(4.0)  # wider routing margins: fewer tokens whose top-k flips between bf16 and fp32
