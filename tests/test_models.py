@@ -210,3 +210,35 @@ def test_generate_runs():
     m, _ = build_model(tiny_cfg("standard_moe"), seed=0)
     out = m.generate(batch(B=1, S=4), max_new_tokens=3)
     assert out.shape == (1, 7)
+
+
+def test_sharded_optimizer_slices_tile_every_bucket():
+    """The slice a rank owns in a gradient bucket (host arithmetic of `TrainEngine.owned_slice`) must be the
+    one the reduce kernel reduces on that rank: whole float4 groups, ceil-divided over the ranks, disjoint,
+    covering the bucket."""
+    from moe_b200.models import build_model
+    from moe_b200.parallel.engine import TrainEngine
+
+    cfg = {"model": dict(type="dense", vocab_size=512, hidden_size=64, num_hidden_layers=3, head_dim=16,
+                         num_attention_heads=4, num_key_value_heads=2, intermediate_size=128)}
+    model, _ = build_model(cfg, seed=0, device="cpu")
+    eng = TrainEngine(model, lr=1e-3)
+    offs = [o for o in eng.layer_offsets() if o is not None]
+    assert offs == sorted(offs) and len(offs) == 3
+    eng.overlap = True  # plan as a multi-rank CUDA run would: one bucket per decoder layer
+    buckets = eng.bucket_ranges()
+    assert buckets[0][1] == eng.decay_end and buckets[-1][0] == 0
+    assert all(a[0] == b[1] for a, b in zip(buckets, buckets[1:]))  # handed over from the top down, no gaps
+    for world in (2, 3, 8):
+        eng.world = world
+        for lo, hi in buckets:
+            n4 = (hi - lo) // 4
+            per = -(-n4 // world)
+            cover = []
+            for r in range(world):
+                a, b = eng.owned_slice(lo, hi, r)
+                k_lo, k_hi = min(per * r, n4), min(per * r + per, n4)  # what the kernel computes
+                assert (a, b) == (lo + 4 * k_lo, lo + 4 * k_hi)
+                cover.append((a, b))
+            assert cover[0][0] == lo and cover[-1][1] == lo + 4 * n4
+            assert all(x[1] == y[0] for x, y in zip(cover, cover[1:]))
