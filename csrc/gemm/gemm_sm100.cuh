@@ -354,13 +354,44 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
           const bool full = col0 + 32 <= args.N;
           if constexpr (EPI == EPI_LSE) {
             // statistics of the bf16-rounded logits, valid columns only
+            if (full) {
+              // two values per issue slot (f32x2) and four independent partial sums: this epilogue runs on
+              // one warp per scheduler and a serial chain of 32 adds per chunk was its longest dependency
+              constexpr float kLog2e = 1.4426950408889634f;
+              float cmax = -INFINITY;
+              uint64_t v2[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float2 f = unpack_bf16x2(p[j]);
+                v2[j] = pack2(f.x, f.y);
+                cmax = fmax3(cmax, f.x, f.y);
+              }
+              const float new_max = fmaxf(run_max, cmax);
+              const float nm = -new_max * kLog2e;
+              const uint64_t l2 = pack2(kLog2e, kLog2e), nm2 = pack2(nm, nm);
+              uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float xl, xh;
+                unpack2(fma2(v2[j], l2, nm2), xl, xh);
+                acc[j & 3] = add2(acc[j & 3], pack2(ex2_approx(xl), ex2_approx(xh)));
+              }
+              float a0, a1, a2, a3, a4, a5, a6, a7;
+              unpack2(acc[0], a0, a1);
+              unpack2(acc[1], a2, a3);
+              unpack2(acc[2], a4, a5);
+              unpack2(acc[3], a6, a7);
+              const float ssum = ((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7));
+              run_sum = run_sum * ex2_approx((run_max - new_max) * kLog2e) + ssum;
+              run_max = new_max;
+            } else {
             float cmax = -INFINITY;
             float v[32];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               float2 f = unpack_bf16x2(p[j]);
-              v[2 * j] = (full || col0 + 2 * j < args.N) ? f.x : -INFINITY;
-              v[2 * j + 1] = (full || col0 + 2 * j + 1 < args.N) ? f.y : -INFINITY;
+              v[2 * j] = (col0 + 2 * j < args.N) ? f.x : -INFINITY;
+              v[2 * j + 1] = (col0 + 2 * j + 1 < args.N) ? f.y : -INFINITY;
               cmax = fmaxf(cmax, fmaxf(v[2 * j], v[2 * j + 1]));
             }
             const float new_max = fmaxf(run_max, cmax);
@@ -369,6 +400,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
             for (int j = 0; j < 32; ++j) s += __expf(v[j] - new_max);
             run_sum = run_sum * __expf(run_max - new_max) + s;
             run_max = new_max;
+            }
           }
           if (row_ok) {
             if (full) {
