@@ -66,17 +66,26 @@ __device__ __forceinline__ int fb_sched(int round, int cta, int ctas) {
 // ----------------------------------------------------------------------------------------- delta
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                   float* __restrict__ dsc, int B, int S, int nh, float scale) {
-  // one warp per (b, s, h): 128 elements, 4 per lane
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  // half a warp per (b, s, h): 128 elements, 8 per lane (one 16-byte load from each tensor)
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const int l16 = threadIdx.x & 15;
   const long long total = static_cast<long long>(B) * S * nh;
-  if (w >= total) return;
-  const uint2 a = reinterpret_cast<const uint2*>(o + w * 128)[lane];
-  const uint2 b = reinterpret_cast<const uint2*>(d_o + w * 128)[lane];
-  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
-  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
-  s = warp_sum(s);
-  if (lane == 0) {
+  const bool live = w < total;
+  float s = 0.f;
+  if (live) {
+    const uint4 a = reinterpret_cast<const uint4*>(o + w * 128)[l16];
+    const uint4 b = reinterpret_cast<const uint4*>(d_o + w * 128)[l16];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 af = unpack_bf16x2(aw[e]), bf = unpack_bf16x2(bw[e]);
+      s = fmaf(af.x, bf.x, s);
+      s = fmaf(af.y, bf.y, s);
+    }
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (live && l16 == 0) {
     const long long bs = w / nh;
     const int h = static_cast<int>(w - bs * nh);
     const long long b_ = bs / S;
@@ -646,7 +655,7 @@ extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const
     configured = true;
   }
   const long long rows = static_cast<long long>(B) * S * nh;
-  attn_delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
+  attn_delta_kernel<<<static_cast<unsigned>((rows * 16 + 255) / 256), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, nh,
       softmax_scale);
   FbArgs a;
