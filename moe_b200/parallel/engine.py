@@ -60,6 +60,8 @@ class _LayerBoundary(torch.autograd.Function):
 
 
 class TrainEngine:
+    HYPER_SLOTS = 8  # steps the host may stage ahead of the device
+
     def __init__(self, model: nn.Module, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, process_group=None,
                  overlap_grad_reduce: bool = True, device: torch.device | str | None = None,
@@ -149,7 +151,12 @@ class TrainEngine:
             # {lr, 1 - beta1^t, 1 - beta2^t}: read by the AdamW kernel from device memory, refreshed by
             # an async copy from pinned memory before each step (so a captured graph can be replayed)
             self._hyper = torch.zeros(3, dtype=torch.float32, device=dev)
-            self._hyper_host = torch.zeros(3, dtype=torch.float32).pin_memory()
+            # The host runs ahead of the device, and an async copy reads pinned memory when it executes,
+            # not when it is enqueued: every staged step gets its own pinned slot, and a slot is rewritten
+            # only after the event recorded behind its copy has completed.
+            self._hyper_ring = torch.zeros(self.HYPER_SLOTS, 3, dtype=torch.float32).pin_memory()
+            self._hyper_events: list = [None] * self.HYPER_SLOTS
+            self._hyper_next = 0
             self._coef_ep = torch.ones(1, dtype=torch.float32, device=dev)
             from ..ops import _ext
 
@@ -173,6 +180,10 @@ class TrainEngine:
         self._reduced_upto = self.total  # everything at or above this offset has been handed to the reducer
         self._pending = []
         self._boundaries: dict[int, int] = {}
+        # True while a micro-batch other than the last one of the step runs: its gradients only
+        # accumulate locally, the buckets are reduced during the last micro-batch's backward
+        # (what `accelerator.accumulate` / DDP `no_sync` do in the reference, `train.py:546`)
+        self.accumulating = False
 
     # ------------------------------------------------------------------ set-up helpers
     def _fuse_adjacent(self) -> None:
@@ -272,7 +283,7 @@ class TrainEngine:
     def boundary(self, h: torch.Tensor, y: torch.Tensor, layer_idx: int):
         """Called by the decoder at the input of layer `layer_idx` with (residual stream, normed input).
         Backward reaches this node only after every gradient of layers >= layer_idx is complete."""
-        if not self.overlap or not (h.requires_grad and y.requires_grad):
+        if not self.overlap or self.accumulating or not (h.requires_grad and y.requires_grad):
             return h, y
         off = self._layer_offs[layer_idx]
         if off is None:
@@ -389,10 +400,19 @@ class TrainEngine:
             self.lr = lr
         if self.cuda:
             t = self.step_count + 1
-            self._hyper_host[0] = self.lr
-            self._hyper_host[1] = 1.0 - self.betas[0] ** t
-            self._hyper_host[2] = 1.0 - self.betas[1] ** t
-            self._hyper.copy_(self._hyper_host, non_blocking=True)
+            i = self._hyper_next
+            self._hyper_next = (i + 1) % self.HYPER_SLOTS
+            ev = self._hyper_events[i]
+            if ev is not None:
+                ev.synchronize()  # the copy that read this slot has run
+            slot = self._hyper_ring[i]
+            slot[0] = self.lr
+            slot[1] = 1.0 - self.betas[0] ** t
+            slot[2] = 1.0 - self.betas[1] ** t
+            self._hyper.copy_(slot, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._hyper_events[i] = ev
 
     def _account_ep_norm(self) -> None:
         """Expert shards are not reduced: every token of every rank already contributed to the owner's
@@ -528,7 +548,10 @@ class TrainEngine:
     def broadcast_parameters(self, src: int = 0) -> None:
         """Make rank `src` authoritative (the reference gets this from DDP's initial broadcast)."""
         if self.world > 1:
-            dist.broadcast(self.p32, src=src, group=self.group)
+            # expert-parallel shards [decay_end, ep_end) differ per rank by construction and stay untouched
+            for lo, hi in ((0, self.decay_end), (self.ep_end, self.total)):
+                if hi > lo:
+                    dist.broadcast(self.p32[lo:hi], src=src, group=self.group)
             for mod in self.model.modules():
                 for b in mod.buffers(recurse=False):
                     dist.broadcast(b, src=src, group=self.group)

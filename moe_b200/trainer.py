@@ -101,13 +101,18 @@ class Trainer:
             self.ep.begin_step()
         scale = 1.0 / n
         out, tokens = None, 0
-        for mb in dev_batches:
+        for i, mb in enumerate(dev_batches):
             ids, labels = mb["input_ids"], mb["labels"]
             tokens += ids.numel()
             kw = {"output_router_logits": True} if self.is_moe else {}
-            out = self.model(input_ids=ids, labels=labels, loss_scale=scale, **kw)
-            loss = out.loss * scale if n > 1 else out.loss
-            loss.backward()
+            # bucket reduces are launched from the backward of the last micro-batch only
+            self.engine.accumulating = i < n - 1
+            try:
+                out = self.model(input_ids=ids, labels=labels, loss_scale=scale, **kw)
+                loss = out.loss * scale if n > 1 else out.loss
+                loss.backward()
+            finally:
+                self.engine.accumulating = False
         return out, tokens
 
     def _result(self, out, gn, lr, tokens) -> StepResult:

@@ -327,3 +327,64 @@ def test_two_gpu_sharded_optimizer_checkpoint_resume(tmp_path):
         assert res["step"] == 2
         for a, b in zip(res["straight"], res["resumed"]):
             assert abs(a - b) < 2e-3 * abs(a), res
+
+
+def _accum_rank(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import dataclasses
+
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from test_gpu_model import tiny_cfg
+    from moe_b200.models import build_model
+    from moe_b200.ops import gemm as G
+    from moe_b200.trainer import Trainer
+    from moe_b200.utils.training import TrainingConfig
+
+    tcfg = TrainingConfig(learning_rate=1e-3, warmup_steps=0, max_steps=10, batch_size=2, gradient_accumulation=2,
+                          lr_scheduler="constant")
+    g = torch.Generator().manual_seed(0)
+    data = [torch.randint(0, 2048, (8, 128), generator=g) for _ in range(2)]  # 4 rows per rank and step
+    out = {}
+    for name, kw, accum in (("nccl", dict(comm="nccl", overlap_grad_reduce=False), 2),
+                            ("p2p-overlap", dict(comm="p2p", overlap_grad_reduce=True), 2),
+                            ("zero-overlap", dict(comm="p2p", overlap_grad_reduce=True, shard_optimizer=True), 2),
+                            ("one-batch", dict(comm="nccl", overlap_grad_reduce=False), 1)):
+        model, _ = build_model(tiny_cfg("dense"), seed=11, device=f"cuda:{rank}")
+        tr = Trainer(model, dataclasses.replace(tcfg, gradient_accumulation=accum), is_moe=False, **kw)
+        norms = []
+        for b in data:
+            mine = b[rank * 4:(rank + 1) * 4]
+            mbs = [{"input_ids": mine[i:i + 4 // accum], "labels": mine[i:i + 4 // accum]}
+                   for i in range(0, 4, 4 // accum)]
+            norms.append(float(tr.train_step(mbs).grad_norm))
+        torch.cuda.synchronize()
+        G.check_status()
+        tr.engine.sync_master()
+        out[name] = (tr.engine.p32.clone().cpu(), norms)
+        dist.barrier()
+    torch.save(out, os.path.join(out_dir, f"acc{rank}.pt"))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_gradient_accumulation_reduces_every_micro_batch(tmp_path):
+    """Two micro-batches per step with the overlapped bucket reduce: the buckets must be reduced once, after
+    the last micro-batch, so weights and gradient norm match the non-overlapped library all-reduce and the
+    same samples taken as one batch, and the ranks stay bit-identical."""
+    import torch.multiprocessing as mp
+
+    mp.spawn(_accum_rank, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    a, b = torch.load(tmp_path / "acc0.pt"), torch.load(tmp_path / "acc1.pt")
+    ref, ref_norms = a["nccl"]
+    for name in ("p2p-overlap", "zero-overlap", "one-batch"):
+        assert torch.equal(a[name][0], b[name][0]), name
+        d = (a[name][0] - ref).abs()
+        assert d.max() < 5e-3 and (d > 1e-4).float().mean() < 2e-2, (name, float(d.max()))
+        for x, y in zip(a[name][1], ref_norms):
+            assert abs(x - y) < 2e-2 * y, (name, a[name][1], ref_norms)
