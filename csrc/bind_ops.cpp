@@ -138,7 +138,8 @@ void router_bwd(const OptT& dscores, const Tensor& dtopk_w, const Tensor& scores
 // ----------------------------------------------------------------- dispatch
 int64_t moe_plan_blocks(int64_t n) { return b200_moe_plan_blocks((int)n); }
 void moe_plan(const Tensor& idx, int64_t E, Tensor& scratch, Tensor& counts, Tensor& seg_off, Tensor& tile_expert,
-              Tensor& num_m_tiles, Tensor& pos, Tensor& row_slot) {
+              Tensor& num_m_tiles, Tensor& pos, Tensor& row_slot, const OptT& pair_tiles,
+              const OptT& num_pair_tiles) {
   i32c(idx, "idx"); i32c(scratch, "scratch"); i32c(counts, "counts"); i32c(seg_off, "seg_off");
   i32c(tile_expert, "tile_expert"); i32c(num_m_tiles, "num_m_tiles"); i32c(pos, "pos"); i32c(row_slot, "row_slot");
   c10::cuda::CUDAGuard g(idx.device());
@@ -149,7 +150,9 @@ void moe_plan(const Tensor& idx, int64_t E, Tensor& scratch, Tensor& counts, Ten
        "plan output sizes");
   rc_ok(b200_moe_plan(idx.data_ptr<int>(), n, (int)E, scratch.data_ptr<int>(), counts.data_ptr<int>(),
                       seg_off.data_ptr<int>(), tile_expert.data_ptr<int>(), num_m_tiles.data_ptr<int>(),
-                      pos.data_ptr<int>(), row_slot.data_ptr<int>(), cap, stream()), "moe_plan");
+                      pos.data_ptr<int>(), row_slot.data_ptr<int>(), cap, optp<int>(pair_tiles),
+                      pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0,
+                      optp<int>(num_pair_tiles), stream()), "moe_plan");
 }
 void moe_gather(const Tensor& x, const Tensor& row_slot, const Tensor& seg_off, int64_t E, int64_t K, Tensor& xs) {
   bf16c(x, "x"); bf16c(xs, "xs"); i32c(row_slot, "row_slot"); i32c(seg_off, "seg_off");
@@ -340,7 +343,10 @@ void bind_ops(pybind11::module_& m) {
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);
   m.def("moe_plan_blocks", &moe_plan_blocks);
-  m.def("moe_plan", &moe_plan);
+  m.def("moe_plan", &moe_plan, pybind11::arg("idx"), pybind11::arg("E"), pybind11::arg("scratch"),
+        pybind11::arg("counts"), pybind11::arg("seg_off"), pybind11::arg("tile_expert"), pybind11::arg("num_m_tiles"),
+        pybind11::arg("pos"), pybind11::arg("row_slot"), pybind11::arg("pair_tiles") = pybind11::none(),
+        pybind11::arg("num_pair_tiles") = pybind11::none());
   m.def("moe_gather", &moe_gather);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);

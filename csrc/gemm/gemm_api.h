@@ -11,6 +11,7 @@ typedef struct B200GemmDesc {
   int mode;  // 0 dense, 1 grouped by rows (padded expert segments), 2 grouped by contraction (per-expert dW)
   int epi;   // 0 bf16, 1 fp32 (beta), 2 swiglu, 3 swiglu backward, 4 bf16 + softmax partials, 5 bf16 scatter to peers
   int bn;    // tile width: 256, 128 or 64
+  int cta2;  // 1: pair-tile kernel (two CTAs per 256-row tile, TMA-store epilogue); bn 256 or 128
   int a_mn;  // A stored with the M index contiguous (rows = contraction index)
   int b_mn;  // B stored with the N index contiguous (rows = contraction index)
   int M, N, K;
@@ -30,6 +31,10 @@ typedef struct B200GemmDesc {
   const int* tile_expert;
   const int* num_m_tiles;
   const int* seg_off;
+  // pair-tile kernel, grouped by rows: int2 per tile (first row, expert | live 128-row halves << 16);
+  // num_m_tiles then holds the number of pair tiles
+  const int* pair_tiles;
+  int max_pair_tiles;
   void* C;
   long long ldc, c_expert_stride;
   void* aux0;

@@ -1,6 +1,7 @@
 // Host side of the tcgen05 GEMM family: tensor-map construction and kernel dispatch.
 #include "gemm_api.h"
 #include "gemm_sm100.cuh"
+#include "gemm2_sm100.cuh"
 #include "../common/tma_host.h"
 
 #include <cudaTypedefs.h>
@@ -74,6 +75,42 @@ int make_map(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint6
   return 0;
 }
 
+// Store-side map: 3-D tensor {d0 inner, d1, d2} of 2- or 4-byte elements, box {b0, b1, 1}, 128-byte swizzle.
+int make_store_map(CUtensorMap* out, int elem_bytes, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                   uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0, uint32_t b1) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.d0 = d0; key.d1 = d1; key.d2 = d2; key.s1 = s1_bytes; key.s2 = s2_bytes; key.b0 = b0;
+  key.b1 = b1 | (static_cast<uint32_t>(elem_bytes) << 16);
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  auto fn = encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (s1_bytes & 15u) != 0 || (s2_bytes & 15u) != 0) return -2;
+  if (b0 * static_cast<uint32_t>(elem_bytes) != 128u) return -2;
+  cuuint64_t dims[3] = {d0, d1, d2 > 0 ? d2 : 1};
+  cuuint64_t strides[2] = {s1_bytes, s2_bytes > 0 ? s2_bytes : s1_bytes * d1};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -3;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
 static int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -99,6 +136,41 @@ static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmAr
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+// number of CTA pairs that can be resident at once (queried once per kernel variant)
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const CUtensorMap& mx,
+                       const GemmArgs& args, long long pair_tiles, cudaStream_t stream) {
+  auto kern = gemm2_sm100_kernel<BN, A_MN, B_MN, EPI>;
+  using Cfg = Gemm2Cfg<BN, EPI>;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return -10;
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(static_cast<unsigned>(sm_count() / 2 * 2));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2;
+    at.val.clusterDim.y = 1;
+    at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;
+  }
+  long long pairs = pair_tiles < max_pairs ? pair_tiles : max_pairs;
+  if (pairs <= 0) return 0;
+  kern<<<static_cast<unsigned>(2 * pairs), GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ma, mb, mc, mx, args);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -116,6 +188,8 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   a.tile_expert = d->tile_expert;
   a.num_m_tiles = d->num_m_tiles;
   a.seg_off = d->seg_off;
+  a.pair_tiles = d->pair_tiles;
+  a.max_pair_tiles = d->max_pair_tiles;
   a.C = d->C; a.ldc = d->ldc; a.c_expert_stride = d->c_expert_stride;
   a.aux0 = d->aux0; a.ld_aux0 = d->ld_aux0;
   a.aux1 = d->aux1; a.ld_aux1 = d->ld_aux1;
@@ -142,6 +216,63 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   // A: 2-D. K-major: dims {K, rows}; MN-major: dims {M extent, contraction rows}.
   rc = make_map(&ma, d->A, d->a_inner, d->a_rows, 0, static_cast<uint64_t>(d->lda) * 2, 0, 64, d->a_mn ? 64 : 128);
   if (rc) return rc;
+  if (d->cta2) {
+    // ---- pair-tile kernel: each CTA loads bn/2 rows (or columns) of B; C and the SwiGLU side tensors
+    // are written through TMA store maps
+    if (bn != 256 && bn != 128) return -20;
+    if (d->epi == EPI_BF16_SCATTER) return -21;
+    if (d->mode == MODE_GROUPED_M && (d->pair_tiles == nullptr || d->max_pair_tiles <= 0)) return -22;
+    rc = make_map(&mb, d->B, d->b_inner, d->b_rows, d->b_experts > 0 ? d->b_experts : 1,
+                  static_cast<uint64_t>(d->ldb) * 2,
+                  static_cast<uint64_t>(d->b_expert_stride > 0 ? d->b_expert_stride : d->ldb * (long long)d->b_rows) * 2,
+                  64, d->b_mn ? 64u : static_cast<uint32_t>(bn / 2));
+    if (rc) return rc - 3;
+    CUtensorMap mc, mx;
+    const bool f32 = d->epi == EPI_F32;
+    const int bn_out2 = d->epi == EPI_SWIGLU ? bn / 2 : bn;
+    const uint64_t c_rows = d->mode == MODE_GROUPED_K ? static_cast<uint64_t>(d->M) : static_cast<uint64_t>(d->M);
+    if (d->epi == EPI_SWIGLU_BWD) {
+      mc = ma;  // unused by this epilogue
+    } else {
+      rc = make_store_map(&mc, f32 ? 4 : 2, d->C, static_cast<uint64_t>(d->N), c_rows,
+                          d->mode == MODE_GROUPED_K ? static_cast<uint64_t>(d->num_experts) : 1,
+                          static_cast<uint64_t>(d->ldc) * (f32 ? 4 : 2),
+                          static_cast<uint64_t>(d->c_expert_stride) * (f32 ? 4 : 2), f32 ? 32 : 64, 32);
+      if (rc) return rc - 6;
+    }
+    if (d->epi == EPI_SWIGLU || d->epi == EPI_SWIGLU_BWD) {
+      // [2][rows][I] view of the pre-activation tensor: plane 0 = gate columns, plane 1 = up columns
+      void* xb = d->epi == EPI_SWIGLU ? d->aux0 : d->aux1;
+      const long long ldx = d->epi == EPI_SWIGLU ? d->ld_aux0 : d->ld_aux1;
+      if (xb == nullptr || (d->epi == EPI_SWIGLU_BWD && d->aux0 == nullptr)) return -22;
+      rc = make_store_map(&mx, 2, xb, static_cast<uint64_t>(d->N), static_cast<uint64_t>(d->M), 2,
+                          static_cast<uint64_t>(ldx) * 2, static_cast<uint64_t>(d->n_half) * 2, 64, 32);
+      if (rc) return rc - 9;
+    } else {
+      mx = mc;
+    }
+    long long ptiles;
+    if (d->mode == MODE_GROUPED_M)
+      ptiles = static_cast<long long>(d->max_pair_tiles) * ((d->N + bn_out2 - 1) / bn_out2);
+    else
+      ptiles = static_cast<long long>((d->M + GEMM2_BM - 1) / GEMM2_BM) * ((d->N + bn_out2 - 1) / bn_out2) *
+               (d->mode == MODE_GROUPED_K ? d->num_experts : 1);
+#define B200_CASE2(BN_, AMN_, BMN_, EPI_)                                                   \
+  if (bn == BN_ && d->a_mn == AMN_ && d->b_mn == BMN_ && d->epi == EPI_)                    \
+    return launch_pair<BN_, AMN_ != 0, BMN_ != 0, EPI_>(ma, mb, mc, mx, a, ptiles, stream);
+    B200_CASE2(256, 0, 0, EPI_BF16)
+    B200_CASE2(128, 0, 0, EPI_BF16)
+    B200_CASE2(256, 0, 1, EPI_BF16)
+    B200_CASE2(128, 0, 1, EPI_BF16)
+    B200_CASE2(256, 1, 1, EPI_F32)
+    B200_CASE2(128, 1, 1, EPI_F32)
+    B200_CASE2(256, 0, 0, EPI_F32)
+    B200_CASE2(256, 0, 0, EPI_SWIGLU)
+    B200_CASE2(256, 0, 1, EPI_SWIGLU_BWD)
+    B200_CASE2(256, 0, 0, EPI_LSE)
+#undef B200_CASE2
+    return -21;
+  }
   const uint32_t b_box_rows = d->b_mn ? 64u : (d->epi == EPI_SWIGLU ? bn / 2 : bn);
   rc = make_map(&mb, d->B, d->b_inner, d->b_rows, d->b_experts > 0 ? d->b_experts : 1,
                 static_cast<uint64_t>(d->ldb) * 2,

@@ -53,6 +53,8 @@ struct GemmArgs {
   const int* tile_expert;  // grouped_m: expert of each 128-row tile
   const int* num_m_tiles;  // grouped_m: device scalar, number of live 128-row tiles
   const int* seg_off;      // grouped_k: [E+1] padded row offsets (multiples of 128)
+  const int* pair_tiles;   // grouped_m, pair-tile kernel: per tile (first row, expert | live halves << 16)
+  int max_pair_tiles;      // capacity of pair_tiles; num_m_tiles then counts pair tiles
   void* C;
   long long ldc;
   long long c_expert_stride;  // grouped_k: elements between experts in C

@@ -29,12 +29,19 @@ __global__ void plan_hist_kernel(const int* __restrict__ idx, int n, int E, int*
 }
 
 // Single block: per-expert exclusive scan over blocks (in place), counts, padded segment offsets,
-// tile -> expert map and live tile count.
+// tile -> expert map and live tile count; and the same rows as a list of pair tiles (two consecutive
+// 128-row tiles of ONE expert, or a single last tile) for the pair-tile GEMM kernel.
+// The scan over experts is a block-wide scan (contiguous experts per thread, shuffles across threads).
 __global__ void plan_scan_kernel(int* __restrict__ block_hist, int nblocks, int E, int* __restrict__ counts,
                                  int* __restrict__ seg_off, int* __restrict__ tile_expert, int max_tiles,
-                                 int* __restrict__ num_m_tiles) {
-  extern __shared__ int sh[];  // [E] padded sizes -> offsets
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+                                 int* __restrict__ num_m_tiles, int* __restrict__ pair_tiles, int max_pairs,
+                                 int* __restrict__ num_pair_tiles) {
+  extern __shared__ int sh[];  // [E] padded sizes, then [E + 1] row offsets, then [E + 1] pair offsets
+  int* rows_off = sh + E;
+  int* pair_off = rows_off + E + 1;
+  __shared__ int wr[32], wp[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  for (int e = tid; e < E; e += blockDim.x) {
     int run = 0;
     for (int b = 0; b < nblocks; ++b) {
       const size_t o = static_cast<size_t>(b) * E + e;
@@ -46,23 +53,73 @@ __global__ void plan_scan_kernel(int* __restrict__ block_hist, int nblocks, int 
     sh[e] = (run + 127) / 128 * 128;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) {
-      const int p = sh[e];
-      seg_off[e] = run;
-      sh[e] = run;
-      run += p;
+  const int per = (E + blockDim.x - 1) / blockDim.x;
+  const int lo = tid * per < E ? tid * per : E;
+  const int hi = lo + per < E ? lo + per : E;
+  int r_sum = 0, p_sum = 0;
+  for (int e = lo; e < hi; ++e) {
+    r_sum += sh[e];
+    p_sum += (sh[e] / 128 + 1) / 2;
+  }
+  int r_inc = r_sum, p_inc = p_sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, r_inc, o), b = __shfl_up_sync(0xffffffffu, p_inc, o);
+    if (lane >= o) {
+      r_inc += a;
+      p_inc += b;
     }
-    seg_off[E] = run;
-    int nt = run / 128;
-    if (nt > max_tiles) nt = max_tiles;
-    *num_m_tiles = nt;
+  }
+  if (lane == 31) {
+    wr[warp] = r_inc;
+    wp[warp] = p_inc;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    const int t0 = seg_off[e] / 128, t1 = seg_off[e + 1] / 128;
-    for (int t = t0; t < t1 && t < max_tiles; ++t) tile_expert[t] = e;
+  if (warp == 0) {
+    int a = lane < nwarps ? wr[lane] : 0, b = lane < nwarps ? wp[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int x = __shfl_up_sync(0xffffffffu, a, o), y = __shfl_up_sync(0xffffffffu, b, o);
+      if (lane >= o) {
+        a += x;
+        b += y;
+      }
+    }
+    wr[lane] = a;  // inclusive over warps
+    wp[lane] = b;
+  }
+  __syncthreads();
+  int r_run = r_inc - r_sum + (warp > 0 ? wr[warp - 1] : 0);
+  int p_run = p_inc - p_sum + (warp > 0 ? wp[warp - 1] : 0);
+  for (int e = lo; e < hi; ++e) {
+    rows_off[e] = r_run;
+    pair_off[e] = p_run;
+    seg_off[e] = r_run;
+    r_run += sh[e];
+    p_run += (sh[e] / 128 + 1) / 2;
+  }
+  if (tid == blockDim.x - 1) {  // the last thread's running totals are the grand totals
+    rows_off[E] = r_run;
+    pair_off[E] = p_run;
+    seg_off[E] = r_run;
+    int nt = r_run / 128;
+    *num_m_tiles = nt > max_tiles ? max_tiles : nt;
+    if (num_pair_tiles != nullptr) *num_pair_tiles = p_run > max_pairs ? max_pairs : p_run;
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += nwarps) {
+    const int t0 = rows_off[e] / 128, t1 = rows_off[e + 1] / 128;
+    for (int t = t0 + lane; t < t1 && t < max_tiles; t += 32) tile_expert[t] = e;
+    if (pair_tiles != nullptr) {
+      const int p0 = pair_off[e], np = pair_off[e + 1] - p0, n128 = t1 - t0;
+      for (int i = lane; i < np; i += 32) {
+        if (p0 + i < max_pairs) {
+          const int halves = (2 * i + 2 <= n128) ? 2 : 1;
+          pair_tiles[2 * (p0 + i)] = (t0 + 2 * i) * 128;
+          pair_tiles[2 * (p0 + i) + 1] = e | (halves << 16);
+        }
+      }
+    }
   }
 }
 
@@ -226,15 +283,26 @@ extern "C" int b200_moe_plan_blocks(int n) { return (n + PLAN_CHUNK - 1) / PLAN_
 
 // scratch: int32[plan_blocks(n) * E].  row_slot must hold `capacity` ints; it is reset to -1 here.
 extern "C" int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* seg_off, int* tile_expert,
-                             int* num_m_tiles, int* pos, int* row_slot, int capacity, cudaStream_t stream) {
-  if (n <= 0 || E <= 0 || capacity % 128 != 0) return -1;
-  if (static_cast<size_t>(E) * sizeof(int) > 48 * 1024) return -1;
+                             int* num_m_tiles, int* pos, int* row_slot, int capacity, int* pair_tiles, int max_pairs,
+                             int* num_pair_tiles, cudaStream_t stream) {
+  if (n <= 0 || E <= 0 || E > 65535 || capacity % 128 != 0) return -1;
+  const size_t scan_sm = (3 * static_cast<size_t>(E) + 2) * sizeof(int);
+  if (static_cast<size_t>(E) * sizeof(int) > 48 * 1024 || scan_sm > 200 * 1024) return -1;
+  if (scan_sm > 48 * 1024) {
+    static bool raised = false;
+    if (!raised) {
+      if (cudaFuncSetAttribute(plan_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        return -3;
+      raised = true;
+    }
+  }
   const int nb = b200_moe_plan_blocks(n);
   const size_t sm = static_cast<size_t>(E) * sizeof(int);
   cudaMemsetAsync(row_slot, 0xff, static_cast<size_t>(capacity) * sizeof(int), stream);
   plan_hist_kernel<<<nb, 256, sm, stream>>>(idx, n, E, scratch);
-  plan_scan_kernel<<<1, 1024, sm, stream>>>(scratch, nb, E, counts, seg_off, tile_expert, capacity / 128,
-                                            num_m_tiles);
+  plan_scan_kernel<<<1, 1024, scan_sm, stream>>>(
+      scratch, nb, E, counts, seg_off, tile_expert, capacity / 128, num_m_tiles, pair_tiles, max_pairs,
+      num_pair_tiles);
   plan_scatter_kernel<<<nb, 32, sm, stream>>>(idx, n, E, scratch, seg_off, pos, row_slot, capacity);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

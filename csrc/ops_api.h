@@ -33,8 +33,10 @@ int b200_router_bwd(const float* dscores, const float* dtopk_w, const float* sco
 
 // ---- moe/dispatch.cu
 int b200_moe_plan_blocks(int n);  // plan scratch: int[blocks * E]
+// pair_tiles (optional): int2 per pair tile for the pair-tile GEMM kernel, capacity max_pairs
 int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* seg_off, int* tile_expert,
-                  int* num_m_tiles, int* pos, int* row_slot, int capacity, cudaStream_t stream);
+                  int* num_m_tiles, int* pos, int* row_slot, int capacity, int* pair_tiles, int max_pairs,
+                  int* num_pair_tiles, cudaStream_t stream);
 int b200_moe_gather(const void* x, const int* row_slot, const int* seg_off, int E, int K, int H, void* xs,
                     int capacity, cudaStream_t stream);
 int b200_moe_combine(const void* ys, const int* pos, const float* w, const void* res, int T, int K, int H, void* out,

@@ -432,9 +432,13 @@ class MoEPlan:
         self.num_m_tiles = torch.empty(1, dtype=torch.int32, device=dev)
         self.pos = torch.empty(n, dtype=torch.int32, device=dev)
         self.row_slot = torch.empty(self.cap, dtype=torch.int32, device=dev)
+        # the same rows as pair tiles (two 128-row tiles of one expert, or its last single one)
+        self.pair_tiles = torch.empty((self.cap // 128 + E + 1) // 2, 2, dtype=torch.int32, device=dev)
+        self.num_pair_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+        self.pair = (self.pair_tiles, self.num_pair_tiles)
         scratch = _scratch("moe_plan", e.moe_plan_blocks(n) * E, torch.int32, dev)
         e.moe_plan(idx32.reshape(-1), E, scratch, self.counts, self.seg_off, self.tile_expert, self.num_m_tiles,
-                   self.pos, self.row_slot)
+                   self.pos, self.row_slot, self.pair_tiles, self.num_pair_tiles)
 
 
 class MoEExpertsFn(torch.autograd.Function):
@@ -457,9 +461,9 @@ class MoEExpertsFn(torch.autograd.Function):
         e.moe_gather(x2, plan.row_slot, plan.seg_off, E, K, xs)
         act = torch.empty(cap, I, dtype=BF16, device=dev)
         gu = torch.empty(cap, I2, dtype=BF16, device=dev)
-        G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu)
+        G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair)
         ys = torch.empty(cap, H, dtype=BF16, device=dev)
-        G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys)
+        G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys, pair=plan.pair)
         out = torch.empty(T, H, dtype=BF16, device=dev)
         e.moe_combine(ys, plan.pos, tw, None, out, K, None, 0, None, 0, None)
         ctx.save_for_backward(xs, gu, act, ys, tw)
@@ -488,12 +492,12 @@ class MoEExpertsFn(torch.autograd.Function):
         dw = torch.zeros(T * K, dtype=torch.float32, device=dev)
         e.moe_combine_bwd(d2, ys, plan.row_slot, plan.seg_off, tw.view(-1), E, K, dys, dw)
         dgu = torch.empty_like(gu)
-        G.grouped_nn_swiglu_bwd(dys, w2, plan.tile_expert, plan.num_m_tiles, gu, dgu)
+        G.grouped_nn_swiglu_bwd(dys, w2, plan.tile_expert, plan.num_m_tiles, gu, dgu, pair=plan.pair)
         s2 = GradSink(down)
         t2, b2 = s2.target()
         G.grouped_tn(dys, act, plan.seg_off, t2, beta=b2)
         dxs = dys  # reuse: dys is dead after the two GEMMs above
-        G.grouped_nn(dgu, w1, plan.tile_expert, plan.num_m_tiles, dxs)
+        G.grouped_nn(dgu, w1, plan.tile_expert, plan.num_m_tiles, dxs, pair=plan.pair)
         s1 = GradSink(gate_up)
         t1, b1 = s1.target()
         G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1)

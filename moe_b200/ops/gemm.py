@@ -7,6 +7,8 @@ kernel reads each layout directly through TMA and the tcgen05 descriptors.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _ext
@@ -43,6 +45,16 @@ def check_status(device: torch.device | None = None) -> None:
             raise RuntimeError(f"moe_b200 kernel status {v}: {STATUS_NAMES.get(v, 'unknown')}")
 
 
+def pair_tiles_enabled() -> bool:
+    """Pair-tile (`cta_group::2`) kernels are the default; MOE_B200_GEMM_PAIR=0 selects the one-CTA tiles."""
+    return os.environ.get("MOE_B200_GEMM_PAIR", "1") != "0"
+
+
+def _use_pair(M: int, N: int, bn: int | None) -> bool:
+    # a pair tile is 256 rows; narrow outputs (router logits) stay on the 64-wide one-CTA tiles
+    return pair_tiles_enabled() and M >= 256 and N >= 128 and (bn is None or bn >= 128)
+
+
 def _pick_bn(n: int) -> int:
     if n <= 64:
         return 64
@@ -53,11 +65,13 @@ def _pick_bn(n: int) -> int:
 
 def _launch(*, mode, epi, bn, a_mn, b_mn, M, N, K, A, lda, a_inner, a_rows, B, ldb, b_expert_stride, b_inner,
             b_rows, b_experts, C, ldc, num_experts=1, m_fast=1, beta=0, n_half=0, tile_expert=None,
-            num_m_tiles=None, seg_off=None, c_expert_stride=0, aux0=None, ld_aux0=0, aux1=None, ld_aux1=0, ep=None):
+            num_m_tiles=None, seg_off=None, c_expert_stride=0, aux0=None, ld_aux0=0, aux1=None, ld_aux1=0, ep=None,
+            cta2=0, pair_tiles=None):
     ext = _ext.load()
     ext.gemm(mode, epi, bn, a_mn, b_mn, M, N, K, num_experts, m_fast, beta, n_half, A, lda, a_inner, a_rows, B, ldb,
              b_expert_stride, b_inner, b_rows, b_experts, tile_expert, num_m_tiles, seg_off, C, ldc,
-             c_expert_stride, aux0, ld_aux0, aux1, ld_aux1, status_word(A.device), **(ep or {}))
+             c_expert_stride, aux0, ld_aux0, aux1, ld_aux1, status_word(A.device), cta2=cta2, pair_tiles=pair_tiles,
+             **(ep or {}))
 
 
 def _check2d(t: torch.Tensor, name: str) -> None:
@@ -68,7 +82,7 @@ def _check2d(t: torch.Tensor, name: str) -> None:
 
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, out_dtype=torch.bfloat16,
-            beta: int = 0, bn: int | None = None, m_fast: int = 1) -> torch.Tensor:
+            beta: int = 0, bn: int | None = None, m_fast: int = 1, pair: bool | None = None) -> torch.Tensor:
     """`a[M,K] @ b[N,K]^T` -> `[M,N]` (bf16, or fp32 with optional accumulate)."""
     _check2d(a, "a"); _check2d(b, "b")
     M, K = a.shape
@@ -77,14 +91,16 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
     epi = EPI_BF16 if out.dtype == torch.bfloat16 else EPI_F32
-    _launch(mode=MODE_DENSE, epi=epi, bn=bn or _pick_bn(N), a_mn=0, b_mn=0, M=M, N=N, K=K, A=a, lda=a.stride(0),
-            a_inner=K, a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=K, b_rows=N, b_experts=1, C=out,
-            ldc=out.stride(0), beta=beta, m_fast=m_fast)
+    pair = (_use_pair(M, N, bn) and (epi == EPI_BF16 or N > 128) and (pair is not False)
+            and out.stride(0) % (8 if epi == EPI_BF16 else 4) == 0)
+    _launch(mode=MODE_DENSE, epi=epi, bn=(256 if N > 128 else 128) if pair else (bn or _pick_bn(N)), a_mn=0, b_mn=0,
+            M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K, a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0,
+            b_inner=K, b_rows=N, b_experts=1, C=out, ldc=out.stride(0), beta=beta, m_fast=m_fast, cta2=int(pair))
     return out
 
 
 def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, bn: int | None = None,
-            m_fast: int = 0) -> torch.Tensor:
+            m_fast: int = 0, pair: bool | None = None) -> torch.Tensor:
     """`a[M,K] @ b[K,N]` -> bf16 `[M,N]`; `b` is read in place (N contiguous)."""
     _check2d(a, "a"); _check2d(b, "b")
     M, K = a.shape
@@ -92,24 +108,26 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     assert b.shape[0] == K
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
-    bn = bn or (128 if N <= 128 else 256)
+    pair = _use_pair(M, N, bn) and (pair is not False)
+    bn = (128 if N <= 128 else 256) if pair else (bn or (128 if N <= 128 else 256))
     _launch(mode=MODE_DENSE, epi=EPI_BF16, bn=bn, a_mn=0, b_mn=1, M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K,
             a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N, b_rows=K, b_experts=1, C=out,
-            ldc=out.stride(0), m_fast=m_fast)
+            ldc=out.stride(0), m_fast=m_fast, cta2=int(pair))
     return out
 
 
-def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, beta: int = 0, bn: int | None = None
-            ) -> torch.Tensor:
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, beta: int = 0, bn: int | None = None,
+            pair: bool | None = None) -> torch.Tensor:
     """`out[M,N] (+)= a[Kc,M]^T @ b[Kc,N]`, fp32 output (weight-gradient shape)."""
     _check2d(a, "a"); _check2d(b, "b")
     Kc, M = a.shape
     N = b.shape[1]
     assert b.shape[0] == Kc and out.dtype == torch.float32 and out.stride(1) == 1
-    bn = bn or (128 if N <= 128 else 256)
+    pair = _use_pair(M, N, bn) and out.stride(0) % 4 == 0 and (pair is not False)
+    bn = (128 if N <= 128 else 256) if pair else (bn or (128 if N <= 128 else 256))
     _launch(mode=MODE_DENSE, epi=EPI_F32, bn=bn, a_mn=1, b_mn=1, M=M, N=N, K=Kc, A=a, lda=a.stride(0), a_inner=M,
             a_rows=Kc, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N, b_rows=Kc, b_experts=1, C=out,
-            ldc=out.stride(0), beta=beta, m_fast=0)
+            ldc=out.stride(0), beta=beta, m_fast=0, cta2=int(pair))
     return out
 
 
@@ -125,57 +143,76 @@ def gemm_nt_lse(a: torch.Tensor, b: torch.Tensor, logits: torch.Tensor | None = 
     part = torch.empty(M, n_tiles, 2, dtype=torch.float32, device=a.device)
     _launch(mode=MODE_DENSE, epi=EPI_LSE, bn=256, a_mn=0, b_mn=0, M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K,
             a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=K, b_rows=N, b_experts=1, C=logits,
-            ldc=logits.stride(0), aux0=part, m_fast=1)
+            ldc=logits.stride(0), aux0=part, m_fast=1, cta2=int(_use_pair(M, N, 256)))
     return logits, part
 
 
 # ------------------------------------------------------------------ grouped (MoE)
+def _pair_kw(pair, N: int) -> dict:
+    """Arguments that switch a grouped-by-rows GEMM to the pair-tile kernel.  `pair` = (pair_tiles int32
+    [P, 2], num_pair_tiles int32 [1]) from the dispatch plan, or None."""
+    if pair is None or not pair_tiles_enabled() or N < 128:
+        return {}
+    return dict(cta2=1, pair_tiles=pair[0], num_m_tiles=pair[1], bn=256)
+
+
 def grouped_up_swiglu(xs: torch.Tensor, w_gate_up: torch.Tensor, tile_expert: torch.Tensor,
-                      num_m_tiles: torch.Tensor, act: torch.Tensor, gu: torch.Tensor, bn: int = 256, ep=None) -> None:
+                      num_m_tiles: torch.Tensor, act: torch.Tensor, gu: torch.Tensor, bn: int = 256, ep=None,
+                      pair=None) -> None:
     """`xs[R,H]` (expert-sorted, 128-row padded) x `w_gate_up[E,2I,H]` -> `act[R,I]`, pre-activations `gu[R,2I]`."""
     R, H = xs.shape
     E, I2, _ = w_gate_up.shape
     I = I2 // 2
-    _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU, bn=bn, a_mn=0, b_mn=0, M=R, N=I, K=H, A=xs, lda=xs.stride(0),
+    kw = dict(bn=bn, num_m_tiles=num_m_tiles)
+    kw.update(_pair_kw(pair, 2 * I))
+    _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU, a_mn=0, b_mn=0, M=R, N=I, K=H, A=xs, lda=xs.stride(0),
             a_inner=H, a_rows=R, B=w_gate_up, ldb=w_gate_up.stride(1), b_expert_stride=w_gate_up.stride(0),
             b_inner=H, b_rows=I2, b_experts=E, C=act, ldc=act.stride(0), n_half=I, tile_expert=tile_expert,
-            num_m_tiles=num_m_tiles, aux0=gu, ld_aux0=gu.stride(0), m_fast=0, ep=ep)
+            aux0=gu, ld_aux0=gu.stride(0), m_fast=0, ep=ep, **kw)
 
 
 def grouped_nt(xs: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, num_m_tiles: torch.Tensor,
-               out: torch.Tensor, bn: int | None = None, ep=None, scatter: bool = False) -> None:
+               out: torch.Tensor, bn: int | None = None, ep=None, scatter: bool = False, pair=None) -> None:
     """`out[R,N] = xs[R,K] @ w[e(row)][N,K]^T` (down projection).  `scatter=True`: rows go to the peers'
     return buffers named in `ep` instead of `out` (only `out.stride(0)` is used)."""
     R, K = xs.shape
     E, N, _ = w.shape
-    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16_SCATTER if scatter else EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=0, M=R, N=N, K=K,
+    kw = dict(bn=bn or (128 if N <= 128 else 256), num_m_tiles=num_m_tiles)
+    if not scatter:
+        kw.update(_pair_kw(pair, N))
+    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16_SCATTER if scatter else EPI_BF16, a_mn=0, b_mn=0, M=R, N=N, K=K,
             A=xs, lda=xs.stride(0), a_inner=K, a_rows=R, B=w, ldb=w.stride(1), b_expert_stride=w.stride(0),
             b_inner=K, b_rows=N, b_experts=E, C=out, ldc=out.stride(0), tile_expert=tile_expert,
-            num_m_tiles=num_m_tiles, m_fast=0, ep=ep)
+            m_fast=0, ep=ep, **kw)
 
 
 def grouped_nn(xs: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, num_m_tiles: torch.Tensor,
-               out: torch.Tensor, bn: int | None = None, ep=None, scatter: bool = False) -> None:
+               out: torch.Tensor, bn: int | None = None, ep=None, scatter: bool = False, pair=None) -> None:
     """`out[R,N] = xs[R,K] @ w[e(row)][K,N]` (input gradients; weights read in place)."""
     R, K = xs.shape
     E, _, N = w.shape
-    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16_SCATTER if scatter else EPI_BF16, bn=bn or (128 if N <= 128 else 256), a_mn=0, b_mn=1, M=R, N=N, K=K,
+    kw = dict(bn=bn or (128 if N <= 128 else 256), num_m_tiles=num_m_tiles)
+    if not scatter:
+        kw.update(_pair_kw(pair, N))
+    _launch(mode=MODE_GROUPED_M, epi=EPI_BF16_SCATTER if scatter else EPI_BF16, a_mn=0, b_mn=1, M=R, N=N, K=K,
             A=xs, lda=xs.stride(0), a_inner=K, a_rows=R, B=w, ldb=w.stride(1), b_expert_stride=w.stride(0),
             b_inner=N, b_rows=K, b_experts=E, C=out, ldc=out.stride(0), tile_expert=tile_expert,
-            num_m_tiles=num_m_tiles, m_fast=0, ep=ep)
+            m_fast=0, ep=ep, **kw)
 
 
 def grouped_nn_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, tile_expert: torch.Tensor,
                           num_m_tiles: torch.Tensor, gu: torch.Tensor, dgu: torch.Tensor,
-                          bn: int | None = None, ep=None) -> None:
+                          bn: int | None = None, ep=None, pair=None) -> None:
     """`d(act) = dy[R,H] @ w_down[e][H,I]`, fused with the SwiGLU backward: writes `dgu[R,2I]`."""
     R, H = dy.shape
     E, _, I = w_down.shape
-    _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU_BWD, bn=bn or (128 if I <= 128 else 256), a_mn=0, b_mn=1, M=R, N=I,
+    kw = dict(bn=bn or (128 if I <= 128 else 256), num_m_tiles=num_m_tiles)
+    kw.update(_pair_kw(pair, I if I > 128 else 0))
+    _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU_BWD, a_mn=0, b_mn=1, M=R, N=I,
             K=H, A=dy, lda=dy.stride(0), a_inner=H, a_rows=R, B=w_down, ldb=w_down.stride(1),
             b_expert_stride=w_down.stride(0), b_inner=I, b_rows=H, b_experts=E, C=dgu, ldc=dgu.stride(0),
-            n_half=I, tile_expert=tile_expert, num_m_tiles=num_m_tiles, aux0=gu, ld_aux0=gu.stride(0), aux1=dgu,
-            ld_aux1=dgu.stride(0), m_fast=0, ep=ep)
+            n_half=I, tile_expert=tile_expert, aux0=gu, ld_aux0=gu.stride(0), aux1=dgu,
+            ld_aux1=dgu.stride(0), m_fast=0, ep=ep, **kw)
 
 
 def grouped_tn(a: torch.Tensor, b: torch.Tensor, seg_off: torch.Tensor, out: torch.Tensor, beta: int = 0,
@@ -184,7 +221,9 @@ def grouped_tn(a: torch.Tensor, b: torch.Tensor, seg_off: torch.Tensor, out: tor
     R, M = a.shape
     N = b.shape[1]
     E = out.shape[0]
-    _launch(mode=MODE_GROUPED_K, epi=EPI_F32, bn=bn or (128 if N <= 128 else 256), a_mn=1, b_mn=1, M=M, N=N, K=0,
+    pair = _use_pair(M, N, bn) and out.stride(1) % 4 == 0 and out.stride(0) % 4 == 0
+    _launch(mode=MODE_GROUPED_K, epi=EPI_F32, bn=(128 if N <= 128 else 256) if pair else (bn or (128 if N <= 128 else 256)),
+            a_mn=1, b_mn=1, M=M, N=N, K=0,
             A=a, lda=a.stride(0), a_inner=M, a_rows=R, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N, b_rows=R,
             b_experts=1, C=out, ldc=out.stride(1), c_expert_stride=out.stride(0), num_experts=E, seg_off=seg_off,
-            beta=beta, m_fast=0)
+            beta=beta, m_fast=0, cta2=int(pair))

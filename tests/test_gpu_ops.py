@@ -28,8 +28,16 @@ def _sync_status():
     G.check_status()
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1000, 520, 264), (2048, 1024, 1024), (300, 48, 512)])
-def test_gemm_nt(dev, M, N, K):
+@pytest.fixture(params=["pair", "single"])
+def tile_kind(request, monkeypatch):
+    """Run a GEMM test on the pair-tile (`cta_group::2`) kernels and on the one-CTA kernels."""
+    monkeypatch.setenv("MOE_B200_GEMM_PAIR", "1" if request.param == "pair" else "0")
+    return request.param
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1000, 520, 264), (2048, 1024, 1024), (300, 48, 512),
+                                   (257, 136, 72), (513, 264, 1032), (4096, 384, 128)])
+def test_gemm_nt(dev, tile_kind, M, N, K):
     from moe_b200.ops import gemm as G
 
     torch.manual_seed(0)
@@ -42,8 +50,8 @@ def test_gemm_nt(dev, M, N, K):
     assert relerr(c32, a.float() @ b.float().T) < 1e-5
 
 
-@pytest.mark.parametrize("M,N,K", [(384, 512, 192), (1000, 264, 520), (256, 128, 16)])
-def test_gemm_nn_and_tn(dev, M, N, K):
+@pytest.mark.parametrize("M,N,K", [(384, 512, 192), (1000, 264, 520), (256, 128, 16), (777, 1032, 328)])
+def test_gemm_nn_and_tn(dev, tile_kind, M, N, K):
     from moe_b200.ops import gemm as G
 
     torch.manual_seed(1)
@@ -55,6 +63,9 @@ def test_gemm_nn_and_tn(dev, M, N, K):
     G.gemm_tn(at, bt, out, beta=1)
     _sync_status()
     assert relerr(out, ref) < 1e-5
+    G.gemm_tn(at, bt, out, beta=0)
+    _sync_status()
+    assert relerr(out, at.float().T @ bt.float()) < 1e-5
 
 
 def test_rmsnorm_fwd_bwd(dev):
@@ -141,8 +152,9 @@ def test_router(dev, mode, E, K, groups):
     assert relerr(wk.grad, wo.grad) < 5e-2
 
 
-@pytest.mark.parametrize("T,H,I,E,K", [(300, 256, 192, 8, 2), (1024, 512, 256, 16, 4), (64, 128, 64, 32, 8)])
-def test_moe_experts(dev, T, H, I, E, K):
+@pytest.mark.parametrize("T,H,I,E,K", [(300, 256, 192, 8, 2), (1024, 512, 256, 16, 4), (64, 128, 64, 32, 8),
+                                       (2000, 256, 320, 4, 2)])
+def test_moe_experts(dev, tile_kind, T, H, I, E, K):
     from moe_b200 import ops
 
     torch.manual_seed(5)
@@ -187,6 +199,18 @@ def test_moe_plan_is_stable_sort(dev):
         assert torch.equal(pos[slots], seg[e] + torch.arange(len(slots)))  # token order kept inside an expert
         assert (seg[e + 1] - seg[e]) == (counts[e].item() + 127) // 128 * 128
     assert plan.num_m_tiles.item() == seg[E].item() // 128
+    # pair tiles: every 128-row tile of every expert exactly once, never two experts in one pair
+    npair = plan.num_pair_tiles.item()
+    pt = plan.pair_tiles[:npair].cpu()
+    te = plan.tile_expert[:plan.num_m_tiles.item()].cpu()
+    seen = []
+    for m0, info in pt.tolist():
+        e, halves = info & 0xffff, info >> 16
+        assert m0 % 128 == 0 and halves in (1, 2)
+        for h in range(halves):
+            assert te[m0 // 128 + h].item() == e
+            seen.append(m0 // 128 + h)
+    assert sorted(seen) == list(range(plan.num_m_tiles.item()))
 
 
 @pytest.mark.parametrize("T,H,V", [(512, 256, 1000), (300, 128, 4096)])
