@@ -218,9 +218,23 @@ void moe_combine_bwd(const Tensor& dout, const Tensor& ys, const Tensor& row_slo
 }
 
 // ---------------------------------------------------------------------- lce
+void lce_reduce(const OptT& row_loss, const Tensor& labels, int64_t ignore_index, int64_t V, Tensor& acc) {
+  f32c(acc, "acc");
+  need(acc.numel() >= 3, "acc must hold 3 floats");
+  need(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.is_contiguous(), "labels must be int64");
+  c10::cuda::CUDAGuard g(labels.device());
+  const int T = (int)labels.numel();
+  if (row_loss.has_value() && row_loss->defined()) {
+    f32c(*row_loss, "row_loss");
+    need(row_loss->numel() >= T, "row_loss size");
+  }
+  rc_ok(b200_lce_reduce(optp<const float>(row_loss), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                        (int)ignore_index, T, (int)V, acc.data_ptr<float>(), stream()), "lce_reduce");
+}
 void lse_loss(const Tensor& part, const Tensor& logits, const Tensor& labels, int64_t ignore_index, Tensor& lse,
               Tensor& loss_acc) {
-  f32c(part, "part"); f32c(lse, "lse"); f32c(loss_acc, "loss_acc");
+  f32c(part, "part"); f32c(lse, "lse"); f32c(loss_acc, "row_loss");
+  need(lse.numel() >= logits.size(0) && loss_acc.numel() >= logits.size(0), "lse / row_loss size");
   need(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.is_contiguous(), "labels must be int64");
   c10::cuda::CUDAGuard g(logits.device());
   const int T = (int)logits.size(0), V = (int)logits.size(1);
@@ -351,6 +365,7 @@ void bind_ops(pybind11::module_& m) {
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);
   m.def("lse_loss", &lse_loss);
+  m.def("lce_reduce", &lce_reduce);
   m.def("dlogits_", &dlogits_);
   m.def("embed_fwd", &embed_fwd);
   m.def("embed_bwd", &embed_bwd);

@@ -8,14 +8,13 @@
 
 namespace b200 {
 
-// One warp per row.  loss_acc[0] += sum of row losses, loss_acc[1] += number of valid rows.
+// One warp per row: row log-sum-exp and row loss (0 for an ignored label).  No atomics: the sum over rows
+// is taken afterwards in a fixed order by lce_reduce_kernel, so the loss has the same bits on every run.
 __global__ void lse_loss_kernel(const float2* __restrict__ part, int n_tiles, const __nv_bfloat16* __restrict__ logits,
                                 long long ld, const long long* __restrict__ labels, int ignore_index, int T, int V,
-                                float* __restrict__ lse_out, float* __restrict__ loss_acc) {
-  __shared__ float s_loss[8], s_cnt[8];
+                                float* __restrict__ lse_out, float* __restrict__ row_loss) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 8 + warp;
-  float loss = 0.f, cnt = 0.f;
   if (row < T) {
     const float2* pr = part + static_cast<size_t>(row) * n_tiles;
     float mx = -INFINITY;
@@ -31,27 +30,42 @@ __global__ void lse_loss_kernel(const float2* __restrict__ part, int n_tiles, co
     if (lane == 0) {
       lse_out[row] = lse;
       const long long lab = labels[row];
-      if (lab != ignore_index && lab >= 0 && lab < V) {
+      float loss = 0.f;
+      if (lab != ignore_index && lab >= 0 && lab < V)
         loss = lse - __bfloat162float(logits[static_cast<size_t>(row) * ld + lab]);
-        cnt = 1.f;
-      }
+      row_loss[row] = loss;
     }
   }
-  if (lane == 0) {
-    s_loss[warp] = loss;
-    s_cnt[warp] = cnt;
+}
+
+// Single block, fixed order.  row_loss == null: acc[1] = number of rows with a valid label (needed before
+// the first gradient tile can be scaled).  Otherwise acc[0] = sum of row losses, acc[2] = mean loss.
+__global__ void lce_reduce_kernel(const float* __restrict__ row_loss, const long long* __restrict__ labels,
+                                  int ignore_index, int T, int V, float* __restrict__ acc) {
+  __shared__ float sh[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float v = 0.f;
+  for (int i = threadIdx.x; i < T; i += blockDim.x) {
+    if (row_loss != nullptr) {
+      v += row_loss[i];
+    } else {
+      const long long lab = labels[i];
+      v += (lab != ignore_index && lab >= 0 && lab < V) ? 1.f : 0.f;
+    }
   }
+  v = warp_sum(v);
+  if (lane == 0) sh[warp] = v;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float a = 0.f, b = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      a += s_loss[i];
-      b += s_cnt[i];
-    }
-    if (b > 0.f) {
-      atomicAdd(&loss_acc[0], a);
-      atomicAdd(&loss_acc[1], b);
+  if (warp == 0) {
+    float t = lane < (blockDim.x >> 5) ? sh[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) {
+      if (row_loss != nullptr) {
+        acc[0] = t;
+        acc[2] = t / fmaxf(acc[1], 1.f);
+      } else {
+        acc[1] = t;
+      }
     }
   }
 }
@@ -128,11 +142,18 @@ __global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_b
 using namespace b200;
 
 extern "C" int b200_lse_loss(const float* part, int n_tiles, const void* logits, long long ld, const long long* labels,
-                             int ignore_index, int T, int V, float* lse, float* loss_acc, cudaStream_t stream) {
+                             int ignore_index, int T, int V, float* lse, float* row_loss, cudaStream_t stream) {
   if (T <= 0) return 0;
   lse_loss_kernel<<<(T + 7) / 8, 256, 0, stream>>>(reinterpret_cast<const float2*>(part), n_tiles,
                                                    reinterpret_cast<const __nv_bfloat16*>(logits), ld, labels,
-                                                   ignore_index, T, V, lse, loss_acc);
+                                                   ignore_index, T, V, lse, row_loss);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_lce_reduce(const float* row_loss, const long long* labels, int ignore_index, int T, int V,
+                               float* acc, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  lce_reduce_kernel<<<1, 1024, 0, stream>>>(row_loss, labels, ignore_index, T, V, acc);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -46,8 +46,12 @@ int b200_moe_combine_bwd(const void* dout, const void* ys, const int* row_slot, 
                          int E, int K, int H, void* dys, float* dw, int capacity, cudaStream_t stream);
 
 // ---- lce/lce.cu
+// per row: log-sum-exp and loss (0 where the label is ignored); no atomics
 int b200_lse_loss(const float* part, int n_tiles, const void* logits, long long ld, const long long* labels,
-                  int ignore_index, int T, int V, float* lse, float* loss_acc, cudaStream_t stream);
+                  int ignore_index, int T, int V, float* lse, float* row_loss, cudaStream_t stream);
+// fixed-order reductions into acc[3]: row_loss == null -> acc[1] = valid labels; else acc[0] = sum, acc[2] = mean
+int b200_lce_reduce(const float* row_loss, const long long* labels, int ignore_index, int T, int V, float* acc,
+                    cudaStream_t stream);
 int b200_dlogits(void* logits, long long ld, const float* lse, const long long* labels, int ignore_index, int T, int V,
                  const float* loss_acc, float upstream, cudaStream_t stream);
 int b200_embed_fwd(const long long* ids, const void* table, int T, int H, int V, void* out, cudaStream_t stream);

@@ -511,13 +511,22 @@ def moe_experts(x, topk_idx, topk_w, gate_up, down):
 
 
 # --------------------------------------------------- fused linear + cross entropy
-class LinearCrossEntropyFn(torch.autograd.Function):
-    """Mean cross entropy of `h @ W^T` against aligned labels.
+LCE_CHUNK_ROWS = int(os.environ.get("MOE_B200_LCE_CHUNK", "4096"))
 
-    The vocabulary GEMM stores bf16 logits once (HBM is large enough) together with softmax
-    partials from its epilogue; the gradient w.r.t. logits is formed in place and the two
-    gradient GEMMs run inside forward, so nothing of size [T, V] survives the call.
-    `upstream` is d(total loss)/d(this loss), which must be known when forward runs.
+
+class LinearCrossEntropyFn(torch.autograd.Function):
+    """Mean cross entropy of `h @ W^T` against aligned labels, without a `[T, V]` tensor.
+
+    Tokens are processed in chunks of `LCE_CHUNK_ROWS` rows that share one reusable bf16 logits scratch
+    (`chunk x V`): vocabulary GEMM with softmax partials from its epilogue -> row log-sum-exp and loss ->
+    gradient w.r.t. the logits formed in place -> the two gradient GEMMs (dH rows of the chunk; dW
+    accumulated over the chunks by the fp32-add epilogue).  Row losses are summed in a fixed order, so the
+    loss has the same bits on every run.
+
+    The gradients are produced inside forward, so `upstream` = d(total loss)/d(this loss) must be known
+    when forward runs; backward only rescales dH by `dloss / upstream`.  A forward pass under grad mode
+    therefore writes into the weight's gradient accumulator even if backward is never called: run
+    evaluation passes under `torch.no_grad()`.
     """
 
     @staticmethod
@@ -527,29 +536,43 @@ class LinearCrossEntropyFn(torch.autograd.Function):
         if h2.dtype != BF16:
             h2 = h2.to(BF16)
         h2 = h2.contiguous()
-        T = h2.shape[0]
+        T, H = h2.shape
+        dev = h2.device
         wmat = w16(weight)
         V = wmat.shape[0]
         lab = labels.reshape(-1).contiguous()
-        logits, part = G.gemm_nt_lse(h2, wmat)
-        lse = torch.empty(T, dtype=torch.float32, device=h2.device)
-        acc = torch.zeros(2, dtype=torch.float32, device=h2.device)
-        e.lse_loss(part, logits, lab, ignore_index, lse, acc)
-        loss = acc[0] / acc[1].clamp_min(1.0)
         need_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])
         ctx.have_grad = need_grad
+        chunk = min(T, max(256, LCE_CHUNK_ROWS))
+        n_tiles = (V + 255) // 256
+        logits_buf = _scratch("lce_logits", chunk * V, BF16, dev)
+        part_buf = _scratch("lce_part", chunk * n_tiles * 2, torch.float32, dev)
+        lse = torch.empty(T, dtype=torch.float32, device=dev)
+        row_loss = torch.empty(T, dtype=torch.float32, device=dev)
+        acc = torch.empty(3, dtype=torch.float32, device=dev)
+        e.lce_reduce(None, lab, ignore_index, V, acc)  # number of valid labels, needed by every gradient tile
         if need_grad:
-            e.dlogits_(logits, lse, lab, ignore_index, acc, float(upstream))
-            dh = G.gemm_nn(logits, wmat, m_fast=0)
+            dh = torch.empty(T, H, dtype=BF16, device=dev)
             sink = GradSink(weight)
             tgt, beta = sink.target()
-            G.gemm_tn(logits, h2, tgt, beta=beta)
+        for c0 in range(0, T, chunk):
+            rows = min(chunk, T - c0)
+            logits = logits_buf[:rows * V].view(rows, V)
+            part = part_buf[:rows * n_tiles * 2].view(rows, n_tiles, 2)
+            hc, lc = h2[c0:c0 + rows], lab[c0:c0 + rows]
+            G.gemm_nt_lse(hc, wmat, logits, part)
+            e.lse_loss(part, logits, lc, ignore_index, lse[c0:c0 + rows], row_loss[c0:c0 + rows])
+            if need_grad:
+                e.dlogits_(logits, lse[c0:c0 + rows], lc, ignore_index, acc, float(upstream))
+                G.gemm_nn(logits, wmat, out=dh[c0:c0 + rows], m_fast=0)
+                G.gemm_tn(logits, hc, tgt, beta=beta if c0 == 0 else 1)
+        e.lce_reduce(row_loss, lab, ignore_index, V, acc)
+        if need_grad:
             ctx.dw = sink.done(tgt)
             ctx.save_for_backward(dh)
             ctx.in_shape = tuple(h.shape)
             ctx.upstream = float(upstream)
-        del logits
-        return loss
+        return acc[2]
 
     @staticmethod
     def backward(ctx, dloss):

@@ -131,8 +131,8 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, beta: int = 
     return out
 
 
-def gemm_nt_lse(a: torch.Tensor, b: torch.Tensor, logits: torch.Tensor | None = None
-                ) -> tuple[torch.Tensor, torch.Tensor]:
+def gemm_nt_lse(a: torch.Tensor, b: torch.Tensor, logits: torch.Tensor | None = None,
+                part: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """Vocabulary projection: bf16 logits plus per-(row, 256-column tile) `(max, sum exp)` partials."""
     _check2d(a, "a"); _check2d(b, "b")
     M, K = a.shape
@@ -140,7 +140,9 @@ def gemm_nt_lse(a: torch.Tensor, b: torch.Tensor, logits: torch.Tensor | None = 
     if logits is None:
         logits = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
     n_tiles = (N + 255) // 256
-    part = torch.empty(M, n_tiles, 2, dtype=torch.float32, device=a.device)
+    if part is None:
+        part = torch.empty(M, n_tiles, 2, dtype=torch.float32, device=a.device)
+    assert part.shape == (M, n_tiles, 2) and part.is_contiguous()
     _launch(mode=MODE_DENSE, epi=EPI_LSE, bn=256, a_mn=0, b_mn=0, M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K,
             a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=K, b_rows=N, b_experts=1, C=logits,
             ldc=logits.stride(0), aux0=part, m_fast=1, cta2=int(_use_pair(M, N, 256)))
