@@ -117,22 +117,70 @@ void flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& 
 
 // ------------------------------------------------------------------- router
 void router_fwd(const Tensor& logits, const OptT& bias, Tensor& scores, Tensor& topk_w, Tensor& topk_idx, int64_t K,
-                int64_t mode, bool norm, double scale, int64_t num_groups, int64_t group_topk) {
+                int64_t mode, bool norm, double scale, int64_t num_groups, int64_t group_topk, const OptT& cnt_sel,
+                const OptT& cnt_unb, const OptT& tokens_acc, const OptT& rsum, const OptT& margin, int64_t S) {
   f32c(logits, "logits"); f32c(scores, "scores"); f32c(topk_w, "topk_w"); i32c(topk_idx, "topk_idx");
   c10::cuda::CUDAGuard g(logits.device());
   const int T = (int)logits.size(0), E = (int)logits.size(1);
+  const bool stats = cnt_sel.has_value() && cnt_sel->defined();
+  if (stats) {
+    i32c(*cnt_sel, "cnt_sel");
+    need(S > 0 && T % S == 0 && cnt_sel->numel() == (int64_t)(T / S) * E, "cnt_sel must be int32 [T / S, E]");
+    if (cnt_unb.has_value() && cnt_unb->defined()) {
+      i32c(*cnt_unb, "cnt_unb");
+      need(cnt_unb->numel() == cnt_sel->numel(), "cnt_unb size");
+    }
+  }
+  if (tokens_acc.has_value() && tokens_acc->defined()) { f32c(*tokens_acc, "tokens_acc"); need(tokens_acc->numel() == E, "tokens_acc size"); }
+  if (rsum.has_value() && rsum->defined()) { f32c(*rsum, "rsum"); need(rsum->numel() >= T, "rsum size"); }
+  if (margin.has_value() && margin->defined()) { f32c(*margin, "margin"); need(margin->numel() >= T, "margin size"); }
   rc_ok(b200_router_fwd(logits.data_ptr<float>(), optp<const float>(bias), scores.data_ptr<float>(),
                         topk_w.data_ptr<float>(), topk_idx.data_ptr<int>(), T, E, (int)K, (int)mode, norm ? 1 : 0,
-                        (float)scale, (int)num_groups, (int)group_topk, stream()), "router_fwd");
+                        (float)scale, (int)num_groups, (int)group_topk, optp<int>(cnt_sel), optp<int>(cnt_unb),
+                        optp<float>(tokens_acc), optp<float>(rsum), optp<float>(margin), (int)S, stream()),
+        "router_fwd");
+}
+void router_colsum(const Tensor& scores, const OptT& rsum, int64_t S, Tensor& psum, const OptT& pn) {
+  f32c(scores, "scores"); f32c(psum, "psum");
+  c10::cuda::CUDAGuard g(scores.device());
+  const int T = (int)scores.size(0), E = (int)scores.size(1);
+  need(S > 0 && T % S == 0, "router_colsum: T must be a multiple of S");
+  const int B = T / (int)S;
+  need(psum.numel() == (int64_t)B * E, "psum must be [T / S, E]");
+  if (pn.has_value() && pn->defined()) { f32c(*pn, "pn"); need(pn->numel() == psum.numel(), "pn size"); }
+  rc_ok(b200_router_colsum(scores.data_ptr<float>(), optp<const float>(rsum), B, (int)S, E, psum.data_ptr<float>(),
+                           optp<float>(pn), stream()), "router_colsum");
+}
+void moe_aux(const Tensor& cnt_unb, const OptT& cnt_sel, const Tensor& psum, const OptT& pn, int64_t K, int64_t S,
+             const OptT& gvec, Tensor& out) {
+  i32c(cnt_unb, "cnt_unb"); f32c(psum, "psum"); f32c(out, "out");
+  need(cnt_unb.dim() == 3 && psum.sizes() == cnt_unb.sizes() && out.numel() >= 2, "moe_aux: [L, B, E] statistics");
+  c10::cuda::CUDAGuard g(psum.device());
+  const int L = (int)cnt_unb.size(0), B = (int)cnt_unb.size(1), E = (int)cnt_unb.size(2);
+  if (cnt_sel.has_value() && cnt_sel->defined()) { i32c(*cnt_sel, "cnt_sel"); need(cnt_sel->sizes() == cnt_unb.sizes(), "cnt_sel shape"); }
+  if (pn.has_value() && pn->defined()) { f32c(*pn, "pn"); need(pn->sizes() == cnt_unb.sizes(), "pn shape"); }
+  if (gvec.has_value() && gvec->defined()) { f32c(*gvec, "g"); need(gvec->numel() == E, "g size"); }
+  rc_ok(b200_moe_aux(cnt_unb.data_ptr<int>(), optp<const int>(cnt_sel), psum.data_ptr<float>(), optp<const float>(pn),
+                     L, B, E, (int)K, (int)S, optp<float>(gvec), out.data_ptr<float>(), stream()), "moe_aux");
 }
 void router_bwd(const OptT& dscores, const Tensor& dtopk_w, const Tensor& scores, const Tensor& topk_idx,
-                Tensor& dlogits, int64_t K, int64_t mode, bool norm, double scale) {
+                Tensor& dlogits, int64_t K, int64_t mode, bool norm, double scale, const OptT& aux_g,
+                const OptT& d_aux, const OptT& seq_cnt, const OptT& rsum, double seq_scale, int64_t S) {
   f32c(dtopk_w, "dtopk_w"); f32c(scores, "scores"); i32c(topk_idx, "topk_idx"); bf16c(dlogits, "dlogits");
   c10::cuda::CUDAGuard g(scores.device());
   const int T = (int)scores.size(0), E = (int)scores.size(1);
+  if (dscores.has_value() && dscores->defined()) { f32c(*dscores, "dscores"); need(dscores->numel() == scores.numel(), "dscores size"); }
+  if (aux_g.has_value() && aux_g->defined()) { f32c(*aux_g, "aux_g"); need(aux_g->numel() == E, "aux_g size"); }
+  if (d_aux.has_value() && d_aux->defined()) { f32c(*d_aux, "d_aux"); need(d_aux->numel() >= 2, "d_aux holds two floats"); }
+  if (seq_cnt.has_value() && seq_cnt->defined()) {
+    i32c(*seq_cnt, "seq_cnt");
+    need(S > 0 && T % S == 0 && seq_cnt->numel() == (int64_t)(T / S) * E, "seq_cnt must be int32 [T / S, E]");
+  }
+  if (rsum.has_value() && rsum->defined()) { f32c(*rsum, "rsum"); need(rsum->numel() >= T, "rsum size"); }
   rc_ok(b200_router_bwd(optp<const float>(dscores), dtopk_w.data_ptr<float>(), scores.data_ptr<float>(),
                         topk_idx.data_ptr<int>(), dlogits.data_ptr(), T, E, (int)K, (int)mode, norm ? 1 : 0,
-                        (float)scale, stream()), "router_bwd");
+                        (float)scale, optp<const float>(aux_g), optp<const float>(d_aux), optp<const int>(seq_cnt),
+                        optp<const float>(rsum), (float)seq_scale, (int)S, stream()), "router_bwd");
 }
 
 // ----------------------------------------------------------------- dispatch
@@ -258,12 +306,17 @@ void embed_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
                        (int)ids.numel(), (int)table.size(1), (int)table.size(0), out.data_ptr(), stream()),
         "embed_fwd");
 }
-void embed_bwd(const Tensor& ids, const Tensor& dout, Tensor& grad) {
+int64_t embed_sort_capacity() { return b200_embed_sort_capacity(); }
+void embed_bwd(const Tensor& ids, const Tensor& dout, Tensor& grad, Tensor& keys, bool presorted, bool accumulate) {
   bf16c(dout, "dout"); f32c(grad, "grad");
-  c10::cuda::CUDAGuard g(grad.device());
+  need(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids must be int64");
+  need(keys.is_cuda() && keys.scalar_type() == at::kLong && keys.is_contiguous() && keys.numel() >= ids.numel(),
+       "keys must be an int64 scratch of at least ids.numel() elements");
+  c10::cuda::CUDAGuard g(dout.device());
   rc_ok(b200_embed_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), dout.data_ptr(),
-                       (int)ids.numel(), (int)grad.size(1), (int)grad.size(0), grad.data_ptr<float>(), stream()),
-        "embed_bwd");
+                       (int)ids.numel(), (int)dout.size(-1), (int)grad.size(0), grad.data_ptr<float>(),
+                       reinterpret_cast<unsigned long long*>(keys.data_ptr<int64_t>()), presorted ? 1 : 0,
+                       accumulate ? 1 : 0, stream()), "embed_bwd");
 }
 
 // -------------------------------------------------------------------- optim
@@ -354,8 +407,23 @@ void bind_ops(pybind11::module_& m) {
   m.def("qknorm_rope_bwd", &qknorm_rope_bwd);
   m.def("flash_fwd", &flash_fwd);
   m.def("flash_bwd", &flash_bwd);
-  m.def("router_fwd", &router_fwd);
-  m.def("router_bwd", &router_bwd);
+  {
+    namespace py = pybind11;
+    m.def("router_fwd", &router_fwd, py::arg("logits"), py::arg("bias"), py::arg("scores"), py::arg("topk_w"),
+          py::arg("topk_idx"), py::arg("K"), py::arg("mode"), py::arg("norm"), py::arg("scale"),
+          py::arg("num_groups"), py::arg("group_topk"), py::arg("cnt_sel") = py::none(),
+          py::arg("cnt_unb") = py::none(), py::arg("tokens_acc") = py::none(), py::arg("rsum") = py::none(),
+          py::arg("margin") = py::none(), py::arg("S") = 0);
+    m.def("router_colsum", &router_colsum);
+    m.def("moe_aux", &moe_aux);
+  }
+  {
+    namespace py = pybind11;
+    m.def("router_bwd", &router_bwd, py::arg("dscores"), py::arg("dtopk_w"), py::arg("scores"), py::arg("topk_idx"),
+          py::arg("dlogits"), py::arg("K"), py::arg("mode"), py::arg("norm"), py::arg("scale"),
+          py::arg("aux_g") = py::none(), py::arg("d_aux") = py::none(), py::arg("seq_cnt") = py::none(),
+          py::arg("rsum") = py::none(), py::arg("seq_scale") = 0.0, py::arg("S") = 0);
+  }
   m.def("moe_plan_blocks", &moe_plan_blocks);
   m.def("moe_plan", &moe_plan, pybind11::arg("idx"), pybind11::arg("E"), pybind11::arg("scratch"),
         pybind11::arg("counts"), pybind11::arg("seg_off"), pybind11::arg("tile_expert"), pybind11::arg("num_m_tiles"),
@@ -369,6 +437,7 @@ void bind_ops(pybind11::module_& m) {
   m.def("dlogits_", &dlogits_);
   m.def("embed_fwd", &embed_fwd);
   m.def("embed_bwd", &embed_bwd);
+  m.def("embed_sort_capacity", &embed_sort_capacity);
   m.def("sumsq_blocks", &sumsq_blocks);
   m.def("sumsq", &sumsq);
   m.def("clip_coef", &clip_coef);

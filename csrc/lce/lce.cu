@@ -119,20 +119,78 @@ __global__ void embed_fwd_kernel(const long long* __restrict__ ids, const __nv_b
   }
 }
 
-// grad[ids[t]] += dout[t]  (fp32 accumulation buffer; float atomics, order not fixed)
-__global__ void embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout, int T,
-                                 int H, int V, float* __restrict__ grad) {
-  const int nch = H >> 1;
+// ---- embedding backward, deterministic: sort (id, position) keys, then one warp per run of equal ids
+// adds that id's rows in position order.  No atomics, so the gradient has the same bits on every run.
+
+// Single block bitonic sort of n <= capacity 64-bit keys in shared memory (capacity = power of two).
+__global__ void embed_sort_kernel(const long long* __restrict__ ids, int T, int V, int capacity,
+                                  unsigned long long* __restrict__ keys_out) {
+  extern __shared__ unsigned long long keys[];
+  for (int i = threadIdx.x; i < capacity; i += blockDim.x) {
+    unsigned long long k = ~0ull;  // padding sorts last
+    if (i < T) {
+      const long long id = ids[i];
+      if (id >= 0 && id < V) k = (static_cast<unsigned long long>(id) << 32) | static_cast<unsigned>(i);
+    }
+    keys[i] = k;
+  }
+  __syncthreads();
+  for (int size = 2; size <= capacity; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = threadIdx.x; i < capacity / 2; i += blockDim.x) {
+        const int lo = 2 * i - (i & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = (lo & size) == 0;
+        const unsigned long long a = keys[lo], b = keys[hi];
+        if ((a > b) == up) {
+          keys[lo] = b;
+          keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = threadIdx.x; i < T; i += blockDim.x) keys_out[i] = keys[i];
+}
+
+// keys sorted ascending, (id << 32 | position), invalid ids as ~0.  Warp w looks at sorted slot w; if a run
+// of one id starts there it sums the run's rows in order and writes (or adds to) grad[id].
+__global__ void embed_bwd_sorted_kernel(const unsigned long long* __restrict__ keys, const __nv_bfloat16* __restrict__ dout,
+                                        int T, int H, float* __restrict__ grad, int accumulate) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  for (int t = blockIdx.x * wpb + warp; t < T; t += gridDim.x * wpb) {
-    const long long id = ids[t];
-    if (id < 0 || id >= V) continue;
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(dout + static_cast<size_t>(t) * H);
+  const int nch = H >> 3;
+  for (int i = blockIdx.x * wpb + warp; i < T; i += gridDim.x * wpb) {
+    const unsigned long long k = keys[i];
+    if (k == ~0ull) continue;
+    const unsigned id = static_cast<unsigned>(k >> 32);
+    if (i > 0 && static_cast<unsigned>(keys[i - 1] >> 32) == id) continue;  // not the start of a run
     float* dst = grad + static_cast<size_t>(id) * H;
     for (int c = lane; c < nch; c += 32) {
-      const float2 f = unpack_bf16x2(src[c]);
-      atomicAdd(dst + 2 * c, f.x);
-      atomicAdd(dst + 2 * c + 1, f.y);
+      float acc[8];
+      if (accumulate) {
+        const float4 a = *reinterpret_cast<const float4*>(dst + c * 8);
+        const float4 b = *reinterpret_cast<const float4*>(dst + c * 8 + 4);
+        acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w;
+        acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      }
+      for (int r = i; r < T; ++r) {
+        const unsigned long long kr = keys[r];
+        if (static_cast<unsigned>(kr >> 32) != id || kr == ~0ull) break;
+        const unsigned t = static_cast<unsigned>(kr & 0xffffffffu);
+        const uint4 q = *reinterpret_cast<const uint4*>(dout + static_cast<size_t>(t) * H + c * 8);
+        const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(u[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      *reinterpret_cast<float4*>(dst + c * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(dst + c * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
 }
@@ -177,12 +235,34 @@ extern "C" int b200_embed_fwd(const long long* ids, const void* table, int T, in
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// Largest token count the single-block sort handles (64-bit keys in shared memory).
+extern "C" int b200_embed_sort_capacity() { return 16384; }
+
+// keys: uint64[T] scratch.  The caller zeroes `grad` first unless `accumulate`; rows of ids that do not
+// occur are left as they are.
 extern "C" int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, float* grad,
-                              cudaStream_t stream) {
+                              unsigned long long* keys, int presorted, int accumulate, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (H % 2 != 0) return -1;
+  if (H % 8 != 0 || keys == nullptr) return -1;
+  if (!presorted) {
+    if (T > b200_embed_sort_capacity()) return -3;
+    int cap = 1;
+    while (cap < T) cap <<= 1;
+    const size_t smem = static_cast<size_t>(cap) * sizeof(unsigned long long);
+    if (smem > 48 * 1024) {
+      static bool raised = false;
+      if (!raised) {
+        if (cudaFuncSetAttribute(embed_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) !=
+            cudaSuccess)
+          return -4;
+        raised = true;
+      }
+    }
+    embed_sort_kernel<<<1, 1024, smem, stream>>>(ids, T, V, cap, keys);
+  }
   int grid = (T + 7) / 8;
-  if (grid > 1184) grid = 1184;
-  embed_bwd_kernel<<<grid, 256, 0, stream>>>(ids, reinterpret_cast<const __nv_bfloat16*>(dout), T, H, V, grad);
+  if (grid > 2368) grid = 2368;
+  embed_bwd_sorted_kernel<<<grid, 256, 0, stream>>>(keys, reinterpret_cast<const __nv_bfloat16*>(dout), T, H, grad,
+                                                    accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

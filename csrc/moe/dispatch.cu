@@ -41,16 +41,26 @@ __global__ void plan_scan_kernel(int* __restrict__ block_hist, int nblocks, int 
   int* pair_off = rows_off + E + 1;
   __shared__ int wr[32], wp[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  for (int e = tid; e < E; e += blockDim.x) {
+  // exclusive scan over the chunk histograms, one warp per expert, 32 chunks per shuffle scan
+  for (int e = warp; e < E; e += nwarps) {
     int run = 0;
-    for (int b = 0; b < nblocks; ++b) {
+    for (int b0 = 0; b0 < nblocks; b0 += 32) {
+      const int b = b0 + lane;
       const size_t o = static_cast<size_t>(b) * E + e;
-      const int c = block_hist[o];
-      block_hist[o] = run;
-      run += c;
+      const int c = b < nblocks ? block_hist[o] : 0;
+      int inc = c;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int x = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += x;
+      }
+      if (b < nblocks) block_hist[o] = run + inc - c;
+      run += __shfl_sync(0xffffffffu, inc, 31);
     }
-    counts[e] = run;
-    sh[e] = (run + 127) / 128 * 128;
+    if (lane == 0) {
+      counts[e] = run;
+      sh[e] = (run + 127) / 128 * 128;
+    }
   }
   __syncthreads();
   const int per = (E + blockDim.x - 1) / blockDim.x;

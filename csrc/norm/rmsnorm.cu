@@ -218,26 +218,30 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, const void* x, const float* rstd
 // The per-block partial sums live in a file-scope device array instead of caller memory.
 #include "rmsnorm_noalloc.h"
 
+#include <atomic>
+
 namespace b200 {
 static __device__ __align__(256) float g_noalloc_dw_scratch[B200_NOALLOC_MAX_BLOCKS * B200_NOALLOC_MAX_H];
 }
 
 // In host code the array's name is only a handle: the device address has to be asked for, once per
 // device and with that device current.
+// Host threads may make the first call on a device at the same time: the per-device slots are atomics
+// (every thread that looks the address up stores the same value).
 static float* noalloc_scratch_for_current_device() {
   constexpr int kMaxDevices = 64;
-  static float* cache[kMaxDevices] = {nullptr};
+  static std::atomic<float*> cache[kMaxDevices];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  if (cache[dev] == nullptr) {
-    float* p = nullptr;
+  float* p = cache[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), b200::g_noalloc_dw_scratch) != cudaSuccess) {
       (void)cudaGetLastError();
       return nullptr;
     }
-    cache[dev] = p;
+    cache[dev].store(p, std::memory_order_release);
   }
-  return cache[dev];
+  return p;
 }
 
 extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const float* rstd, const float* w,
@@ -246,6 +250,8 @@ extern "C" int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const flo
   if (T < 0 || H <= 0 || H % 8 != 0 || H > B200_NOALLOC_MAX_H) return B200_NOALLOC_ERR_SIZE;
   if (T == 0) return B200_NOALLOC_OK;
   if (!dy || !x || !rstd || !w || !dx || !dw_out) return B200_NOALLOC_ERR_ARG;
+  // an error left behind by an earlier, unrelated call must not be reported as a failed launch of ours
+  if (cudaPeekAtLastError() != cudaSuccess) return B200_NOALLOC_ERR_PRIOR;
   float* scratch = noalloc_scratch_for_current_device();
   if (scratch == nullptr) return B200_NOALLOC_ERR_SETUP;
   const int grid = b200_rmsnorm_bwd_blocks(T);  // <= B200_NOALLOC_MAX_BLOCKS; rows [0, grid) are rewritten below
@@ -272,6 +278,8 @@ extern "C" const char* b200_rmsnorm_bwd_noalloc_strerror(int code) {
     case B200_NOALLOC_ERR_SETUP: return "could not obtain the device address of the built-in scratch array";
     case B200_NOALLOC_ERR_LAUNCH: return "a kernel launch was refused by the CUDA runtime";
     case B200_NOALLOC_ERR_ARG: return "a required pointer argument is null";
+    case B200_NOALLOC_ERR_PRIOR:
+      return "a CUDA error from an earlier call is pending on this thread; nothing was enqueued";
     default: return "unknown code";
   }
 }

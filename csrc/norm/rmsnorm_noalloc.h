@@ -39,6 +39,7 @@ extern "C" {
 #define B200_NOALLOC_ERR_SETUP (-2)   /* the scratch array's address could not be obtained */
 #define B200_NOALLOC_ERR_LAUNCH (-3)  /* a kernel launch was refused */
 #define B200_NOALLOC_ERR_ARG (-4)     /* a required pointer is null */
+#define B200_NOALLOC_ERR_PRIOR (-5)   /* an earlier CUDA error is still pending on this thread; nothing enqueued */
 
 // dx[T,H] (bf16) = rstd * (w*dy - xhat * mean(w*dy*xhat)) (+ dres);   dw_out[H] (fp32) (+)= sum_t dy*xhat
 //   dy, x, dx : bf16 [T, H]      rstd : fp32 [T]      w : fp32 [H]

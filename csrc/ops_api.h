@@ -26,10 +26,22 @@ int b200_qknorm_rope_bwd(const void* dq, const void* dk, const void* dv, const v
                          float* dkw, int dw_accumulate, int T, int S, int nh, int nkv, int hd, cudaStream_t stream);
 
 // ---- moe/router.cu
+// Optional statistics (null = off): cnt_sel / cnt_unb int [B, E] (zeroed by the caller; pass the same pointer
+// for both when there is neither bias nor group-limited routing), tokens_acc float [E], rsum / margin float [T].
 int b200_router_fwd(const float* logits, const float* bias, float* scores, float* topk_w, int* topk_idx, int T, int E,
-                    int K, int mode, int norm, float scale, int num_groups, int group_topk, cudaStream_t stream);
+                    int K, int mode, int norm, float scale, int num_groups, int group_topk, int* cnt_sel,
+                    int* cnt_unb, float* tokens_acc, float* rsum, float* margin, int S, cudaStream_t stream);
+// per-sequence column sums of the scores (psum) and of the row-normalised scores (pn, optional), [B, E]
+int b200_router_colsum(const float* scores, const float* rsum, int B, int S, int E, float* psum, float* pn,
+                       cudaStream_t stream);
+// Switch loss and sequence-level loss from stacked [L, B, E] statistics; g[E] = d(aux)/d(score of expert e)
+int b200_moe_aux(const int* cnt_unb, const int* cnt_sel, const float* psum, const float* pn, int L, int B, int E,
+                 int K, int S, float* g, float* out, cudaStream_t stream);
+// aux_g / seq_cnt (optional) add the balance-loss gradients; d_aux = device pair of upstream gradients
 int b200_router_bwd(const float* dscores, const float* dtopk_w, const float* scores, const int* topk_idx,
-                    void* dlogits, int T, int E, int K, int mode, int norm, float scale, cudaStream_t stream);
+                    void* dlogits, int T, int E, int K, int mode, int norm, float scale, const float* aux_g,
+                    const float* d_aux, const int* seq_cnt, const float* rsum, float seq_scale, int S,
+                    cudaStream_t stream);
 
 // ---- moe/dispatch.cu
 int b200_moe_plan_blocks(int n);  // plan scratch: int[blocks * E]
@@ -55,7 +67,11 @@ int b200_lce_reduce(const float* row_loss, const long long* labels, int ignore_i
 int b200_dlogits(void* logits, long long ld, const float* lse, const long long* labels, int ignore_index, int T, int V,
                  const float* loss_acc, float upstream, cudaStream_t stream);
 int b200_embed_fwd(const long long* ids, const void* table, int T, int H, int V, void* out, cudaStream_t stream);
-int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, float* grad, cudaStream_t stream);
+int b200_embed_sort_capacity();  // tokens the built-in key sort handles
+// deterministic: (id, position) keys are sorted (here, or by the caller: presorted) and every id's rows are
+// added in position order by one warp; keys = uint64[T] scratch
+int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, float* grad,
+                   unsigned long long* keys, int presorted, int accumulate, cudaStream_t stream);
 
 // ---- optim/optim.cu
 int b200_sumsq_blocks(long long n);  // scratch: float[blocks]

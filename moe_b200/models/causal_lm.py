@@ -30,6 +30,7 @@ class MoeCausalLMOutput:
         self.ce_loss = None
         self.seq_aux_loss = None
         self.hidden_states = None
+        self.router_stats = None  # kernel path: the `MoeStatsHolder` with this pass's routing statistics
         self.__dict__.update(kw)
 
     def __getitem__(self, k):
@@ -101,6 +102,11 @@ class _CausalLM(nn.Module):
         loss_scale = float(kwargs.get("loss_scale", 1.0))
         if input_ids is None:
             raise ValueError("input_ids is required")
+        holder = self._begin_stats(input_ids, attention_mask) if (self.is_moe and want_router) else None
+        if holder is None and self.is_moe:
+            for r in self.routers():
+                r._site = None
+        # (the sites stay attached after the call: a checkpointed layer is recomputed during backward)
         hidden, scores = self.model(input_ids)
         out = MoeCausalLMOutput()
         if kwargs.get("output_hidden_states"):
@@ -113,7 +119,19 @@ class _CausalLM(nn.Module):
             out.loss = ce
         if labels is None or kwargs.get("return_logits"):
             out.logits = ops.linear(hidden, self.lm_head.weight)
-        if self.is_moe and want_router and len(scores) > 0:
+        if self.is_moe and want_router and len(scores) > 0 and holder is not None:
+            # kernel path: both losses come from the statistics the router kernels left behind
+            out.router_logits = scores
+            out.router_stats = holder
+            seq_coef = getattr(self, "_seq_aux_loss_coef", 0.0)
+            aux, seq_aux = ops.moe_aux_losses(holder, scores, seq_on=seq_coef > 0)
+            out.aux_loss = aux
+            if out.loss is not None:
+                out.loss = out.loss + self.router_aux_loss_coef * aux
+                if seq_coef > 0:
+                    out.seq_aux_loss = seq_aux
+                    out.loss = out.loss + seq_coef * seq_aux
+        elif self.is_moe and want_router and len(scores) > 0:
             out.router_logits = scores
             sel_unbiased = None
             routers = self.routers()
@@ -132,6 +150,29 @@ class _CausalLM(nn.Module):
                 out.seq_aux_loss = seq_aux
                 out.loss = out.loss + seq_coef * seq_aux
         return out
+
+    def _begin_stats(self, input_ids, attention_mask):
+        """Kernel path only: hand every router its slot of the stacked statistics buffers."""
+        weight = self.model.embed_tokens.weight
+        if attention_mask is not None or not ops.kernel_path(weight) or input_ids.dim() != 2:
+            return None
+        routers = self.routers()
+        if not routers:
+            return None
+        from ..ops.functional import MoeStatsHolder
+
+        B, S = input_ids.shape
+        key = (B, S, weight.device)
+        cache = self.__dict__.setdefault("_stats_holders", {})
+        holder = cache.get(key)
+        if holder is None:
+            holder = MoeStatsHolder(len(routers), B, S, self.num_experts, self.num_experts_per_tok, weight.device,
+                                    any(r.separate_unbiased() for r in routers))
+            cache[key] = holder
+        holder.begin()
+        for r, site in zip(routers, holder.sites):
+            r._site = site
+        return holder
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 16, temperature: float = 0.0,

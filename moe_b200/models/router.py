@@ -57,6 +57,12 @@ class TopKRouter(nn.Module):
         self.register_buffer("local_tokens_per_expert", torch.zeros(self.num_experts, dtype=torch.float32),
                              persistent=False)
         self._last_top_k_idx = None
+        # set by the model for one forward pass on the kernel path: where this router's statistics go
+        self._site = None
+
+    def separate_unbiased(self) -> bool:
+        """Whether the unbiased top-k of the scores can differ from the selection."""
+        return bool(self.use_bias or (self.num_groups or 0) > 1)
 
     def _uses_deepseek_extras(self) -> bool:
         return self.use_bias or self.score_fn == "sigmoid"
@@ -64,11 +70,15 @@ class TopKRouter(nn.Module):
     def forward(self, hidden_states: torch.Tensor):
         x = hidden_states.reshape(-1, self.hidden_dim)
         bias = self.expert_bias if self.use_bias else None
+        count = torch.is_grad_enabled() and not _RECOMPUTING
+        site = self._site if ops.kernel_path(x) else None
         scores, weights, idx = ops.router(
             x, self.weight, bias, top_k=self.top_k, score_fn=self.score_fn, norm_topk_prob=self.norm_topk_prob,
-            scaling_factor=self.scaling_factor, num_groups=self.num_groups, group_topk=self.group_topk)
+            scaling_factor=self.scaling_factor, num_groups=self.num_groups, group_topk=self.group_topk, site=site,
+            tokens_acc=self.local_tokens_per_expert if (site is not None and count) else None,
+            collect=not _RECOMPUTING)
         self._last_top_k_idx = idx.detach()
-        if torch.is_grad_enabled() and not _RECOMPUTING:
+        if count and site is None:
             with torch.no_grad():
                 ones = torch.ones(idx.numel(), dtype=torch.float32, device=idx.device)
                 self.local_tokens_per_expert.index_add_(0, idx.reshape(-1).long(), ones)

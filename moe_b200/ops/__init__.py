@@ -78,11 +78,20 @@ def attention(q, k, v):
     return oracle.causal_gqa_attention(q, k, v)
 
 
-def router(x, weight, bias, *, top_k, score_fn, norm_topk_prob, scaling_factor, num_groups, group_topk):
-    """Returns (scores fp32 [T,E], weights fp32 [T,K], indices [T,K])."""
+def kernel_path(x: torch.Tensor) -> bool:
+    """True when ops on `x` run the sm_100a kernels (CUDA tensor, oracle not forced)."""
+    return _k(x)
+
+
+def router(x, weight, bias, *, top_k, score_fn, norm_topk_prob, scaling_factor, num_groups, group_topk, site=None,
+           tokens_acc=None, collect=True):
+    """Returns (scores fp32 [T,E], weights fp32 [T,K], indices [T,K]).  Kernel path only: `site` (a
+    `functional.RouterSite`) receives the routing statistics of this call, `tokens_acc` the selection counts;
+    `collect=False` (recomputation of a checkpointed layer) leaves both untouched."""
     if _k(x):
         mode = 0 if score_fn == "softmax" else 1
-        return _f().router(x, weight, bias, top_k, mode, norm_topk_prob, scaling_factor, num_groups, group_topk)
+        return _f().router(x, weight, bias, top_k, mode, norm_topk_prob, scaling_factor, num_groups, group_topk,
+                           site, tokens_acc, collect)
     if score_fn == "softmax" and bias is None and num_groups is None:
         s, w, i = oracle.router_softmax(x, weight, top_k, norm_topk_prob)
         if scaling_factor is not None:
@@ -102,6 +111,11 @@ def router(x, weight, bias, *, top_k, score_fn, norm_topk_prob, scaling_factor, 
             w = w * scaling_factor
         return probs, w, idx
     return oracle.router_sigmoid(x, weight, bias, top_k, norm_topk_prob, scaling_factor, num_groups, group_topk)
+
+
+def moe_aux_losses(holder, scores, seq_on: bool):
+    """(Switch loss, sequence-level loss) from the statistics the router kernels wrote into `holder`."""
+    return _f().moe_aux_losses(holder, scores, seq_on)
 
 
 def set_moe_site(mlp, global_experts, layer_idx: int) -> None:
@@ -127,10 +141,7 @@ def moe_experts(x, idx, w, gate_up, down):
 
 def swiglu_mlp(x, gate_w, up_w, down_w, fused_gate_up=None):
     if _k(x):
-        f = _f()
-        gu = f.linear(x, gate_w, up_w, fused=fused_gate_up)
-        g, u = gu.chunk(2, dim=-1)
-        return f.linear(TF.silu(g) * u, down_w)
+        return _f().swiglu_mlp(x, gate_w, up_w, down_w, fused_gate_up)
     return oracle.swiglu_mlp(x, gate_w.to(x.dtype), up_w.to(x.dtype), down_w.to(x.dtype))
 
 

@@ -85,11 +85,25 @@ class EmbeddingFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         (flat,) = ctx.saved_tensors
+        e = ext()
         sink = GradSink(ctx.weight)
         tgt, beta = sink.target()
         if beta == 0:
             tgt.zero_()
-        ext().embed_bwd(flat, dout.reshape(flat.numel(), -1).contiguous(), tgt)
+        n = flat.numel()
+        # deterministic: (id, position) keys are sorted and each id's rows are added in position order
+        if n <= e.embed_sort_capacity():
+            keys = _scratch("embed_keys", n, torch.int64, flat.device)
+            presorted = False
+        else:  # beyond the single-block sort: library radix sort of the same keys
+            V = tgt.shape[0]
+            big = torch.iinfo(torch.int64).max
+            k = torch.where((flat >= 0) & (flat < V), (flat << 32) | torch.arange(n, device=flat.device),
+                            torch.full_like(flat, big))
+            keys = torch.sort(k).values  # invalid ids last ...
+            keys = torch.where(keys == big, torch.full_like(keys, -1), keys).contiguous()  # ... as all-ones keys
+            presorted = True
+        e.embed_bwd(flat, dout.reshape(n, -1).contiguous(), tgt, keys, presorted, True)
         return None, sink.done(tgt)
 
 
@@ -213,6 +227,75 @@ class LinearFn(torch.autograd.Function):
 
 def linear(x, *weights, fused=None):
     return LinearFn.apply(x, fused, *weights)
+
+
+# ------------------------------------------------------------ dense SwiGLU MLP
+class SwiGLUMLPFn(torch.autograd.Function):
+    """`down(silu(gate(x)) * up(x))`: the gate|up projection is one GEMM whose epilogue applies SwiGLU, the
+    input-gradient GEMM of the down projection applies its derivative (same epilogues as the expert path)."""
+
+    @staticmethod
+    def forward(ctx, x, gate_w, up_w, down_w, fused):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        if x2.dtype != BF16:
+            x2 = x2.to(BF16)
+        x2 = x2.contiguous()
+        T = x2.shape[0]
+        wgu = fused[0] if fused is not None else torch.cat([w16(gate_w), w16(up_w)], dim=0)
+        wd = w16(down_w)
+        I = wgu.shape[0] // 2
+        act = torch.empty(T, I, dtype=BF16, device=x2.device)
+        gu = torch.empty(T, 2 * I, dtype=BF16, device=x2.device)
+        G.dense_up_swiglu(x2, wgu, act, gu)
+        y = G.gemm_nt(act, wd)
+        ctx.save_for_backward(x2, gu, act)
+        ctx.w = (wgu, wd)
+        ctx.params = (gate_w, up_w, down_w)
+        ctx.fused = fused
+        ctx.in_shape = tuple(x.shape)
+        return y.view(*x.shape[:-1], wd.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, gu, act = ctx.saved_tensors
+        wgu, wd = ctx.w
+        gate_w, up_w, down_w = ctx.params
+        T, H = x2.shape
+        dy2 = dy.reshape(T, -1)
+        if dy2.dtype != BF16:
+            dy2 = dy2.to(BF16)
+        dy2 = dy2.contiguous()
+        dgu = torch.empty_like(gu)
+        G.dense_swiglu_bwd(dy2, wd, gu, dgu)
+        sd = GradSink(down_w)
+        td, bd = sd.target()
+        G.gemm_tn(dy2, act, td, beta=bd)
+        dx = G.gemm_nn(dgu, wgu).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        I = wgu.shape[0] // 2
+        if ctx.fused is not None:
+            live = [getattr(w, "_grad_live", False) for w in (gate_w, up_w)]
+            if live[0] != live[1]:
+                raise RuntimeError("fused gate/up weights have inconsistent gradient state")
+            G.gemm_tn(dgu, x2, ctx.fused[1], beta=1 if live[0] else 0)
+            gate_w._grad_live = up_w._grad_live = True
+            return dx, None, None, sd.done(td), None
+        full = torch.empty(2 * I, H, dtype=torch.float32, device=x2.device)
+        G.gemm_tn(dgu, x2, full)
+        outs = []
+        for w, piece in ((gate_w, full[:I]), (up_w, full[I:])):
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                mg.add_(piece) if getattr(w, "_grad_live", False) else mg.copy_(piece)
+                w._grad_live = True
+                outs.append(None)
+            else:
+                outs.append(piece.to(w.dtype))
+        return dx, outs[0], outs[1], sd.done(td), None
+
+
+def swiglu_mlp(x, gate_w, up_w, down_w, fused_gate_up=None):
+    return SwiGLUMLPFn.apply(x, gate_w, up_w, down_w, fused_gate_up)
 
 
 # ------------------------------------------------------------ qk-norm + rope
@@ -365,11 +448,26 @@ def attention(q, k, v):
 
 
 # ---------------------------------------------------------------------- router
+class RouterSite:
+    """Where one router leaves its per-forward statistics: views into the model's stacked buffers.
+
+    Filled by the router kernels (`csrc/moe/router.cu`): per-sequence expert counts of the actual selection
+    and of the unbiased top-k, per-sequence column sums of the scores (raw and row-normalised), per-token
+    score sums and top-k margins.  The balance losses are computed from these, and their gradient reaches
+    the scores through `grad` (set by `AuxLossFn.backward`, read by `RouterFn.backward`), so no `[T, E]`
+    gradient tensor and no one-hot tensor is ever built."""
+
+    def __init__(self, cnt_sel, cnt_unb, psum, pn, rsum, margin, S):
+        self.cnt_sel, self.cnt_unb, self.psum, self.pn = cnt_sel, cnt_unb, psum, pn
+        self.rsum, self.margin, self.S = rsum, margin, S
+        self.grad = None  # (g [E], d_aux [2], seq_on, seq_scale)
+
+
 class RouterFn(torch.autograd.Function):
     """Router GEMM (fp32 logits) + scoring / top-k kernel.  Returns (scores fp32, weights fp32, idx int32)."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, K, mode, norm, scale, num_groups, group_topk):
+    def forward(ctx, x, weight, bias, K, mode, norm, scale, num_groups, group_topk, site, tokens_acc, collect):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         wmat = w16(weight)
         E = wmat.shape[0]
@@ -379,13 +477,21 @@ class RouterFn(torch.autograd.Function):
         tw = torch.empty(T, K, dtype=torch.float32, device=x2.device)
         ti = torch.empty(T, K, dtype=torch.int32, device=x2.device)
         b = bias.detach().float().contiguous() if bias is not None else None
-        ext().router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
+        e = ext()
+        if site is not None and collect:
+            e.router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
+                         int(group_topk or 0), site.cnt_sel, site.cnt_unb, tokens_acc, site.rsum, site.margin,
+                         site.S)
+            e.router_colsum(scores, site.rsum, site.S, site.psum, site.pn)
+        else:
+            e.router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
                          int(group_topk or 0))
         ctx.save_for_backward(x2, scores, ti)
         ctx.weight = weight
         ctx.wmat = wmat
         ctx.cfg = (K, mode, bool(norm), float(scale))
         ctx.in_shape = tuple(x.shape)
+        ctx.site = site
         ctx.mark_non_differentiable(ti)
         return scores, tw, ti
 
@@ -398,16 +504,80 @@ class RouterFn(torch.autograd.Function):
             dtw = torch.zeros(T, K, dtype=torch.float32, device=x2.device)
         dlogits = torch.empty(T, E, dtype=BF16, device=x2.device)
         ds = dscores.contiguous().float() if dscores is not None else None
-        ext().router_bwd(ds, dtw.contiguous().float(), scores, ti, dlogits, K, mode, norm, scale)
+        kw = {}
+        site = ctx.site
+        if site is not None and site.grad is not None:
+            g, d_aux, seq_on, seq_scale = site.grad
+            kw = dict(aux_g=g, d_aux=d_aux)
+            if seq_on:
+                kw.update(seq_cnt=site.cnt_sel, rsum=site.rsum, seq_scale=seq_scale, S=site.S)
+        ext().router_bwd(ds, dtw.contiguous().float(), scores, ti, dlogits, K, mode, norm, scale, **kw)
         dx = G.gemm_nn(dlogits, ctx.wmat).view(ctx.in_shape)
         sink = GradSink(ctx.weight)
         tgt, beta = sink.target()
         G.gemm_tn(dlogits, x2, tgt, beta=beta)
-        return dx, sink.done(tgt), None, None, None, None, None, None, None
+        return (dx, sink.done(tgt)) + (None,) * 10
 
 
-def router(x, weight, bias, K, mode, norm, scale, num_groups, group_topk):
-    return RouterFn.apply(x, weight, bias, K, mode, norm, 1.0 if scale is None else scale, num_groups, group_topk)
+def router(x, weight, bias, K, mode, norm, scale, num_groups, group_topk, site=None, tokens_acc=None, collect=True):
+    return RouterFn.apply(x, weight, bias, K, mode, norm, 1.0 if scale is None else scale, num_groups, group_topk,
+                          site, tokens_acc, collect)
+
+
+class MoeStatsHolder:
+    """Stacked statistics buffers of all routers of a model for one forward pass (`[L, B, E]`)."""
+
+    def __init__(self, L, B, S, E, K, device, separate_unb: bool):
+        self.L, self.B, self.S, self.E, self.K = L, B, S, E, K
+        self.cnt = torch.zeros(2 if separate_unb else 1, L, B, E, dtype=torch.int32, device=device)
+        self.cnt_sel = self.cnt[0]
+        self.cnt_unb = self.cnt[1] if separate_unb else self.cnt[0]
+        self.psum = torch.zeros(L, B, E, dtype=torch.float32, device=device)
+        self.pn = torch.zeros(L, B, E, dtype=torch.float32, device=device)
+        self.rsum = torch.zeros(L, B * S, dtype=torch.float32, device=device)
+        self.margin = torch.zeros(L, B * S, dtype=torch.float32, device=device)
+        self.g = torch.zeros(E, dtype=torch.float32, device=device)
+        self.out = torch.zeros(2, dtype=torch.float32, device=device)
+        self.sites = [RouterSite(self.cnt_sel[l], self.cnt_unb[l], self.psum[l], self.pn[l], self.rsum[l],
+                                 self.margin[l], S) for l in range(L)]
+
+    def begin(self) -> None:
+        self.cnt.zero_()
+        for s in self.sites:
+            s.grad = None
+
+    def expert_counts(self) -> torch.Tensor:
+        """`[L, E]` token counts by the unbiased top-k (what the routing report and the Switch loss use)."""
+        return self.cnt_unb.sum(dim=1).float()
+
+
+class AuxLossFn(torch.autograd.Function):
+    """Switch and sequence-level balance losses from the router kernels' statistics.  Returns
+    (aux, seq_aux); the gradient w.r.t. the scores is handed to the routers' backward kernels through
+    their `RouterSite` (this node itself returns no tensor gradient)."""
+
+    @staticmethod
+    def forward(ctx, holder, seq_on, *scores):
+        h = holder
+        ext().moe_aux(h.cnt_unb, h.cnt_sel if seq_on else None, h.psum, h.pn if seq_on else None, h.K, h.S, h.g,
+                      h.out)
+        ctx.holder, ctx.seq_on, ctx.n = h, bool(seq_on), len(scores)
+        aux, seq = h.out.unbind(0)
+        return aux.clone(), seq.clone()
+
+    @staticmethod
+    def backward(ctx, d_aux, d_seq):
+        h = ctx.holder
+        z = torch.zeros((), dtype=torch.float32, device=h.g.device)
+        pair = torch.stack([d_aux.float() if d_aux is not None else z, d_seq.float() if d_seq is not None else z])
+        seq_scale = h.E / (h.K * h.S) / (h.L * h.B * h.S)
+        for s in h.sites:
+            s.grad = (h.g, pair, ctx.seq_on, seq_scale)
+        return (None, None) + (None,) * ctx.n
+
+
+def moe_aux_losses(holder, scores, seq_on: bool):
+    return AuxLossFn.apply(holder, seq_on, *scores)
 
 
 # --------------------------------------------------------------------- experts
@@ -512,6 +682,17 @@ def moe_experts(x, topk_idx, topk_w, gate_up, down):
 
 # --------------------------------------------------- fused linear + cross entropy
 LCE_CHUNK_ROWS = int(os.environ.get("MOE_B200_LCE_CHUNK", "4096"))
+LCE_OVERLAP = os.environ.get("MOE_B200_LCE_OVERLAP", "1") != "0"
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(dev) -> torch.cuda.Stream:
+    """One extra stream per device for memory-bound passes that run under a GEMM of the main stream."""
+    s = _SIDE_STREAMS.get(dev)
+    if s is None:
+        s = torch.cuda.Stream(device=dev)
+        _SIDE_STREAMS[dev] = s
+    return s
 
 
 class LinearCrossEntropyFn(torch.autograd.Function):
@@ -545,7 +726,12 @@ class LinearCrossEntropyFn(torch.autograd.Function):
         ctx.have_grad = need_grad
         chunk = min(T, max(256, LCE_CHUNK_ROWS))
         n_tiles = (V + 255) // 256
-        logits_buf = _scratch("lce_logits", chunk * V, BF16, dev)
+        n_chunks = (T + chunk - 1) // chunk
+        # two logits buffers when there is more than one chunk: the memory-bound softmax-gradient pass of
+        # chunk c runs on a side stream under the (compute-bound) vocabulary GEMM of chunk c + 1
+        overlap = need_grad and n_chunks > 1 and LCE_OVERLAP
+        nbuf = 2 if overlap else 1
+        logits_bufs = [_scratch(f"lce_logits{i}", chunk * V, BF16, dev) for i in range(nbuf)]
         part_buf = _scratch("lce_part", chunk * n_tiles * 2, torch.float32, dev)
         lse = torch.empty(T, dtype=torch.float32, device=dev)
         row_loss = torch.empty(T, dtype=torch.float32, device=dev)
@@ -555,17 +741,53 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             dh = torch.empty(T, H, dtype=BF16, device=dev)
             sink = GradSink(weight)
             tgt, beta = sink.target()
-        for c0 in range(0, T, chunk):
-            rows = min(chunk, T - c0)
-            logits = logits_buf[:rows * V].view(rows, V)
+        main = torch.cuda.current_stream(dev)
+        side = _side_stream(dev) if overlap else None
+        spans = [(c0, min(chunk, T - c0)) for c0 in range(0, T, chunk)]
+
+        def logits_of(i):
+            return logits_bufs[i % nbuf][:spans[i][1] * V].view(spans[i][1], V)
+
+        def front(i):  # vocabulary GEMM + row statistics (+ gradient w.r.t. the logits, in place)
+            c0, rows = spans[i]
+            logits = logits_of(i)
             part = part_buf[:rows * n_tiles * 2].view(rows, n_tiles, 2)
-            hc, lc = h2[c0:c0 + rows], lab[c0:c0 + rows]
-            G.gemm_nt_lse(hc, wmat, logits, part)
-            e.lse_loss(part, logits, lc, ignore_index, lse[c0:c0 + rows], row_loss[c0:c0 + rows])
+            G.gemm_nt_lse(h2[c0:c0 + rows], wmat, logits, part)
+            e.lse_loss(part, logits, lab[c0:c0 + rows], ignore_index, lse[c0:c0 + rows], row_loss[c0:c0 + rows])
+            if not need_grad:
+                return None
+            if side is None:
+                e.dlogits_(logits, lse[c0:c0 + rows], lab[c0:c0 + rows], ignore_index, acc, float(upstream))
+                return None
+            ready = torch.cuda.Event()
+            ready.record(main)
+            done = torch.cuda.Event()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                e.dlogits_(logits, lse[c0:c0 + rows], lab[c0:c0 + rows], ignore_index, acc, float(upstream))
+                done.record(side)
+            return done
+
+        def back(i, done):  # the two gradient GEMMs of chunk i
+            c0, rows = spans[i]
+            if done is not None:
+                main.wait_event(done)
+            logits = logits_of(i)
+            G.gemm_nn(logits, wmat, out=dh[c0:c0 + rows], m_fast=0)
+            G.gemm_tn(logits, h2[c0:c0 + rows], tgt, beta=beta if i == 0 else 1)
+
+        pending = None
+        for i in range(n_chunks):
+            done = front(i)
             if need_grad:
-                e.dlogits_(logits, lse[c0:c0 + rows], lc, ignore_index, acc, float(upstream))
-                G.gemm_nn(logits, wmat, out=dh[c0:c0 + rows], m_fast=0)
-                G.gemm_tn(logits, hc, tgt, beta=beta if c0 == 0 else 1)
+                if overlap:
+                    if pending is not None:
+                        back(*pending)
+                    pending = (i, done)
+                else:
+                    back(i, done)
+        if pending is not None:
+            back(*pending)
         e.lce_reduce(row_loss, lab, ignore_index, V, acc)
         if need_grad:
             ctx.dw = sink.done(tgt)

@@ -149,6 +149,30 @@ def gemm_nt_lse(a: torch.Tensor, b: torch.Tensor, logits: torch.Tensor | None = 
     return logits, part
 
 
+# ------------------------------------------------------------------ dense SwiGLU MLP
+def dense_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, gu: torch.Tensor) -> None:
+    """`x[T,H]` x `w_gate_up[2I,H]` (gate rows, then up rows) -> `act[T,I] = silu(gate) * up`, `gu[T,2I]`."""
+    _check2d(x, "x"); _check2d(w_gate_up, "w_gate_up")
+    T, H = x.shape
+    I = w_gate_up.shape[0] // 2
+    pair = _use_pair(T, 2 * I, None)
+    _launch(mode=MODE_DENSE, epi=EPI_SWIGLU, bn=256, a_mn=0, b_mn=0, M=T, N=I, K=H, A=x, lda=x.stride(0), a_inner=H,
+            a_rows=T, B=w_gate_up, ldb=w_gate_up.stride(0), b_expert_stride=0, b_inner=H, b_rows=2 * I, b_experts=1,
+            C=act, ldc=act.stride(0), n_half=I, aux0=gu, ld_aux0=gu.stride(0), m_fast=0, cta2=int(pair))
+
+
+def dense_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gu: torch.Tensor, dgu: torch.Tensor) -> None:
+    """`d(act) = dy[T,H] @ w_down[H,I]` fused with the SwiGLU backward: writes `dgu[T,2I]`."""
+    _check2d(dy, "dy"); _check2d(w_down, "w_down")
+    T, H = dy.shape
+    I = w_down.shape[1]
+    pair = _use_pair(T, I, None) and I > 128
+    _launch(mode=MODE_DENSE, epi=EPI_SWIGLU_BWD, bn=256 if I > 128 else 128, a_mn=0, b_mn=1, M=T, N=I, K=H, A=dy,
+            lda=dy.stride(0), a_inner=H, a_rows=T, B=w_down, ldb=w_down.stride(0), b_expert_stride=0, b_inner=I,
+            b_rows=H, b_experts=1, C=dgu, ldc=dgu.stride(0), n_half=I, aux0=gu, ld_aux0=gu.stride(0), aux1=dgu,
+            ld_aux1=dgu.stride(0), m_fast=0, cta2=int(pair))
+
+
 # ------------------------------------------------------------------ grouped (MoE)
 def _pair_kw(pair, N: int) -> dict:
     """Arguments that switch a grouped-by-rows GEMM to the pair-tile kernel.  `pair` = (pair_tiles int32

@@ -32,7 +32,7 @@ from .utils.watchdog import StepWatchdog
 
 _DATA_KEYS = {"data_dir", "text_column", "seq_len", "tokenizer_name", "num_workers", "source", "seed",
               "reference_double_shift", "prefetch"}
-_PARALLEL_KEYS = {"mode", "ep_size", "bucket_mb", "overlap"}
+_PARALLEL_KEYS = {"mode", "ep_size", "bucket_mb", "overlap", "cuda_graph"}
 _TOP_KEYS = {"experiment_name", "model", "training", "data", "checkpoint", "parallel"}
 
 
@@ -171,10 +171,12 @@ def main(argv=None) -> None:
     pcfg = cfg.get("parallel", {})
     # "ddp": replicated optimizer state; "zero" (alias "fsdp"): Adam moments and the update sharded over the
     # ranks, new bf16 weights stored to every rank by the update kernel
-    pmode = str(pcfg.get("mode", "ddp")).lower()
+    # Defaults are what `bench.py` measures: sharded optimizer on more than one GPU, whole-step CUDA graph.
+    pmode = str(pcfg.get("mode", "zero" if (world > 1 and device == "cuda") else "ddp")).lower()
     if pmode not in ("ddp", "zero", "fsdp"):
         raise ValueError(f"parallel.mode={pcfg.get('mode')!r}: expected ddp, zero or fsdp")
     shard_opt = pmode in ("zero", "fsdp") and world > 1 and device == "cuda"
+    use_graph = bool(pcfg.get("cuda_graph", True)) and device == "cuda" and not args.profile
     if main_proc:
         print(f"\n{'=' * 60}\n  Model     : {mtype}\n  Params    : {params['total'] / 1e9:.3f}B total  |  "
               f"{expert_params / 1e9:.3f}B expert\n  Dist type : {('ZeRO-1' if shard_opt else 'DDP') if world > 1 else 'single'} ({device})\n"
@@ -182,7 +184,7 @@ def main(argv=None) -> None:
               f"{'=' * 60}\n", flush=True)
 
     trainer = Trainer(model, tcfg, is_moe=not is_dense, overlap_grad_reduce=pcfg.get("overlap", True),
-                      shard_optimizer=shard_opt)
+                      shard_optimizer=shard_opt, cuda_graph=use_graph)
     trainer.engine.broadcast_parameters(0)
     dataset = build_dataset(ddict, cfg["model"]["vocab_size"], rank, world)
     if resume_from:
@@ -252,9 +254,13 @@ def main(argv=None) -> None:
                 logger.log(log, gstep)
 
         if res.router_logits is not None:
-            sel = get_selected_experts_for_seq_aux(model) if mtype.startswith("deepseek") is False else None
-            count_accum = accumulate_expert_counts(res.router_logits, mcfg.num_experts_per_tok, count_accum,
-                                                   selected_experts=sel)
+            if res.router_stats is not None:  # the router kernels already counted
+                c = res.router_stats.expert_counts()
+                count_accum = {l: (count_accum[l] + c[l] if count_accum else c[l].clone()) for l in range(c.shape[0])}
+            else:
+                sel = get_selected_experts_for_seq_aux(model) if mtype.startswith("deepseek") is False else None
+                count_accum = accumulate_expert_counts(res.router_logits, mcfg.num_experts_per_tok, count_accum,
+                                                       selected_experts=sel)
             if gstep % tcfg.routing_log_every == 0:
                 _routing_snapshot(res, count_accum, mcfg, is_global, tcfg, gstep, world, main_proc, logger)
                 count_accum = None
@@ -295,9 +301,13 @@ def _routing_snapshot(res, count_accum, mcfg, is_global, tcfg, gstep, world, mai
         dist.all_reduce(stacked, op=dist.ReduceOp.SUM)
         for k, row in zip(keys, stacked.unbind(0)):
             count_accum[k] = row
+    hs = res.router_stats
+    # statistics of the last micro-batch of every rank, summed over the ranks (a collective)
+    rstats = compute_routing_stats(res.router_logits, mcfg.num_experts_per_tok, is_global=is_global,
+                                   counts=None if hs is None else hs.expert_counts(),
+                                   margins=None if hs is None else hs.margin, reduce_ranks=world > 1)
     if not main_proc:
         return
-    rstats = compute_routing_stats(res.router_logits, mcfg.num_experts_per_tok, is_global=is_global)
     logger.log({k: v for k, v in rstats.items() if not k.startswith("_hist/")}, gstep)
     rdir = os.path.join(tcfg.output_dir, "routing_logs")
     os.makedirs(rdir, exist_ok=True)

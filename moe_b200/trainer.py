@@ -30,6 +30,7 @@ class StepResult:
     lr: float
     router_logits: tuple | None = None
     tokens: int = 0
+    router_stats: object | None = None  # kernel path: per-layer routing statistics of the last micro-batch
 
 
 class Trainer:
@@ -119,7 +120,7 @@ class Trainer:
         return StepResult(loss=out.loss.detach(), ce_loss=_d(out.ce_loss), aux_loss=_d(out.aux_loss),
                           seq_aux_loss=_d(out.seq_aux_loss), grad_norm=gn, lr=lr,
                           router_logits=None if out.router_logits is None else tuple(t.detach() for t in out.router_logits),
-                          tokens=tokens * self.world)
+                          tokens=tokens * self.world, router_stats=getattr(out, "router_stats", None))
 
     def _graph_step(self, micro_batches) -> StepResult:
         key = tuple((tuple(mb["input_ids"].shape), tuple(mb["labels"].shape)) for mb in micro_batches)

@@ -70,38 +70,68 @@ def _entropy(dist_: torch.Tensor) -> torch.Tensor:
 
 
 def compute_routing_stats(router_logits: Sequence[torch.Tensor], num_experts_per_tok: int,
-                          is_global: bool = False) -> dict:
+                          is_global: bool = False, counts: torch.Tensor | None = None,
+                          margins: torch.Tensor | None = None, group=None, reduce_ranks: bool = False) -> dict:
+    """`counts` (`[L, E]`) and `margins` (`[L, T]`, k-th minus (k+1)-th score per token) may come from the
+    router kernels; otherwise both are taken from the recorded scores.  `reduce_ranks=True` sums the counts
+    and margin statistics over the data-parallel ranks first (a collective: every rank must call), so the
+    report describes the global batch and not only the calling rank's last micro-batch (the reference
+    reports rank 0's, `train.py:638-643`)."""
     stats: dict = {}
     scalars: dict[str, torch.Tensor] = {}
     ints: set[str] = set()
     hists: dict[str, torch.Tensor] = {}
     loads = []
     K = num_experts_per_tok
-    for li, probs in enumerate(router_logits):
-        probs = probs.detach().float()
-        T, E = probs.shape
+    L = len(router_logits)
+    if L == 0:
+        return stats
+    E = router_logits[0].shape[1]
+    dev = router_logits[0].device
+    if counts is None:
+        counts = torch.stack([_counts_from_probs(p.detach().float(), K) for p in router_logits])
+    counts = counts.float().clone()
+    n_tok = torch.tensor([float(p.shape[0]) for p in router_logits], device=dev)
+    have_margin = E > K
+    if have_margin:
+        if margins is None:
+            tops = [topk_lowest_index(p.detach().float(), K + 1)[0] for p in router_logits]
+            margins_l = [t[:, K - 1] - t[:, K] for t in tops]
+            m_sum = torch.stack([m.sum() for m in margins_l])
+            m_min = torch.stack([m.min() for m in margins_l])
+        else:
+            m_sum, m_min = margins.float().sum(dim=1), margins.float().min(dim=1).values
+    if reduce_ranks and torch.distributed.is_available() and torch.distributed.is_initialized() \
+            and torch.distributed.get_world_size(group) > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(counts, group=group)
+        dist.all_reduce(n_tok, group=group)
+        if have_margin:
+            m_sum, m_min = m_sum.clone(), m_min.clone()
+            dist.all_reduce(m_sum, group=group)
+            dist.all_reduce(m_min, op=dist.ReduceOp.MIN, group=group)
+    for li in range(L):
         tag = f"routing/layer_{li:02d}"
-        counts = _counts_from_probs(probs, K)
-        total = float(T * K)
+        c = counts[li]
+        total = n_tok[li] * K
         ideal = total / E
-        mean = counts.mean()
-        scalars[f"{tag}_load_imbalance"] = counts.max() / ideal
-        scalars[f"{tag}_load_cv"] = torch.where(mean > 0, counts.std() / mean.clamp_min(1e-30), torch.zeros_like(mean))
-        active = (counts > 0).sum().float()
+        mean = c.mean()
+        scalars[f"{tag}_load_imbalance"] = c.max() / ideal
+        scalars[f"{tag}_load_cv"] = torch.where(mean > 0, c.std() / mean.clamp_min(1e-30), torch.zeros_like(mean))
+        active = (c > 0).sum().float()
         scalars[f"{tag}_num_active_experts"] = active
         ints.add(f"{tag}_num_active_experts")
         scalars[f"{tag}_utilization"] = active / E
-        scalars[f"{tag}_top_expert"] = counts.argmax().float()
+        scalars[f"{tag}_top_expert"] = c.argmax().float()
         ints.add(f"{tag}_top_expert")
-        hists[f"_hist/{tag}_expert_load_frac"] = counts / total
-        ent = _entropy(counts / (counts.sum() + 1e-10))
+        hists[f"_hist/{tag}_expert_load_frac"] = c / total
+        ent = _entropy(c / (c.sum() + 1e-10))
         scalars[f"{tag}_entropy"] = ent / math.log(E) if E > 1 else torch.zeros_like(ent)
-        if E > K:
-            top = topk_lowest_index(probs, K + 1)[0]
-            margin = top[:, K - 1] - top[:, K]
-            scalars[f"{tag}_router_margin_mean"] = margin.mean()
-            scalars[f"{tag}_router_margin_min"] = margin.min()
-        loads.append(counts)
+        if have_margin:
+            scalars[f"{tag}_router_margin_mean"] = m_sum[li] / n_tok[li]
+            scalars[f"{tag}_router_margin_min"] = m_min[li]
+        loads.append(c)
     if is_global and len(loads) > 1:
         mat = torch.stack(loads).float()
         L, E = mat.shape

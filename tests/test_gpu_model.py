@@ -14,7 +14,8 @@ def relerr(a, b):
 
 
 def tiny_cfg(mtype="standard_moe", **kw):
-    m = dict(type=mtype, vocab_size=2048, hidden_size=256, num_hidden_layers=2, head_dim=64, num_attention_heads=4,
+    # head_dim 128: every model test runs the own tcgen05 attention kernels
+    m = dict(type=mtype, vocab_size=2048, hidden_size=256, num_hidden_layers=2, head_dim=128, num_attention_heads=4,
              num_key_value_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
     if mtype == "dense":
         m["intermediate_size"] = 512
@@ -29,7 +30,7 @@ def tiny_cfg(mtype="standard_moe", **kw):
 
 
 @pytest.mark.parametrize("mtype", ["standard_moe", "global_moe", "deepseek_standard_moe", "deepseek_global_moe",
-                                   "dense", "dense-hd128"])
+                                   "dense", "dense-hd64"])
 def test_forward_backward_matches_oracle(mtype):
     from moe_b200 import ops
     from moe_b200.models import build_model
@@ -37,8 +38,8 @@ def test_forward_backward_matches_oracle(mtype):
 
     torch.manual_seed(0)
     extra = {}
-    if mtype == "dense-hd128":  # head_dim 128: the own flash-attention kernels instead of SDPA
-        mtype, extra = "dense", dict(head_dim=128)
+    if mtype == "dense-hd64":  # a head size without an own attention kernel: library attention
+        mtype, extra = "dense", dict(head_dim=64)
     model, _ = build_model(tiny_cfg(mtype, **extra), seed=1, device="cuda")
     with torch.no_grad():  # compare on bf16-representable weights
         for r in (model.routers() if mtype != "dense" else []):
@@ -66,10 +67,10 @@ def test_forward_backward_matches_oracle(mtype):
         cos = torch.nn.functional.cosine_similarity(p.grad.flatten().float(), q.grad.flatten().float(), dim=0).item()
         num += (p.grad.float() - q.grad.float()).pow(2).sum().item()
         den += q.grad.float().pow(2).sum().item()
-        if cos < 0.97:
+        if cos < 0.985:
             bad.append((n, cos))
     assert not bad, bad
-    assert (num / den) ** 0.5 < 0.15
+    assert (num / den) ** 0.5 < 0.10
 
 
 def test_engine_training_steps_reduce_loss():

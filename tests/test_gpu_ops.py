@@ -243,22 +243,103 @@ def test_linear_cross_entropy(dev, monkeypatch, T, H, V, chunk):
     assert ops.linear_cross_entropy(hk2, wk2, labels).item() == loss.item()
 
 
-def test_embedding(dev):
+@pytest.mark.parametrize("n_tok", [400, 20000])
+def test_embedding(dev, n_tok):
+    """Gather, and the sorted segmented-sum backward (20000 tokens: past the built-in key sort); ids repeat
+    many times, and two runs must give the same bits."""
     from moe_b200 import ops
 
     torch.manual_seed(8)
     V, H = 1000, 256
     w = torch.randn(V, H, device=dev)
-    ids = torch.randint(0, V, (4, 100), device=dev)
-    wk = w.clone().requires_grad_()
-    out = ops.embedding(ids, wk)
-    g = _bf(4, 100, H)
-    (out.float() * g.float()).sum().backward()
+    ids = torch.randint(0, V, (4, n_tok // 4), device=dev)
+    ids[0, :50] = 7  # a long run of one id
+    g = _bf(4, n_tok // 4, H)
+    grads = []
+    for _ in range(2):
+        wk = w.clone().requires_grad_()
+        out = ops.embedding(ids, wk)
+        (out.float() * g.float()).sum().backward()
+        grads.append(wk.grad.clone())
     wo = w.bfloat16().float().requires_grad_()
     out2 = torch.nn.functional.embedding(ids, wo)
     (out2 * g.float()).sum().backward()
     assert relerr(out, out2) < 1e-6
-    assert relerr(wk.grad, wo.grad) < 1e-5
+    assert relerr(grads[0], wo.grad) < 1e-5
+    assert torch.equal(grads[0], grads[1])
+
+
+@pytest.mark.parametrize("mtype,E,K,groups,B,S", [("softmax", 16, 4, None, 4, 128), ("sigmoid", 64, 4, (8, 4), 2, 256),
+                                                   ("sigmoid", 32, 2, None, 3, 96)])
+def test_router_statistics_and_balance_losses(dev, mtype, E, K, groups, B, S):
+    """The router kernels' statistics against the plain-PyTorch losses: counts, Switch loss, sequence-level
+    loss, margins, and the gradient both losses send into the router weight."""
+    from moe_b200 import ops
+    from moe_b200.models.load_balancing import load_balancing_loss_func, seq_load_balancing_loss_func
+    from moe_b200.ops import functional as F
+    from moe_b200.ops.oracle import topk_lowest_index
+
+    torch.manual_seed(11)
+    T, H, L = B * S, 128, 2
+    ng, gt = groups if groups else (None, None)
+    bias = [torch.randn(E, device=dev) * 0.05 if mtype == "sigmoid" else None for _ in range(L)]
+    xs = [_bf(T, H) for _ in range(L)]
+    ws = [(torch.randn(E, H, device=dev) * 0.2).bfloat16().float() for _ in range(L)]
+    holder = F.MoeStatsHolder(L, B, S, E, K, dev, separate_unb=mtype == "sigmoid")
+    holder.begin()
+    acc = [torch.zeros(E, device=dev) for _ in range(L)]
+    wk = [w.clone().requires_grad_() for w in ws]
+    outs = [ops.router(xs[l], wk[l], bias[l], top_k=K, score_fn=mtype, norm_topk_prob=True, scaling_factor=None,
+                       num_groups=ng, group_topk=gt, site=holder.sites[l], tokens_acc=acc[l]) for l in range(L)]
+    scores = tuple(o[0] for o in outs)
+    aux, seq = ops.moe_aux_losses(holder, scores, seq_on=True)
+    (0.7 * aux + 0.3 * seq).backward()
+    _sync_status()
+    # plain PyTorch on the kernel's own scores and selections (so near-ties cannot differ)
+    wo = [w.clone().requires_grad_() for w in ws]
+    sc2 = []
+    for l in range(L):
+        logit = xs[l].float() @ wo[l].T
+        sc2.append(torch.softmax(logit, -1) if mtype == "softmax" else torch.sigmoid(logit))
+    sel = tuple(o[2].long() for o in outs)
+    unb = tuple(topk_lowest_index(s.detach(), K)[1] for s in scores)
+    aux2 = load_balancing_loss_func(tuple(sc2), E, K, selected_experts=unb)
+    seq2 = seq_load_balancing_loss_func(tuple(sc2), E, K, batch_size=B, selected_experts=sel)
+    (0.7 * aux2 + 0.3 * seq2).backward()
+    assert abs(aux.item() - aux2.item()) < 1e-3 * abs(aux2.item())
+    assert abs(seq.item() - seq2.item()) < 1e-3 * abs(seq2.item())
+    for l in range(L):
+        cnt_sel = torch.bincount(sel[l].reshape(-1), minlength=E)
+        assert torch.equal(holder.cnt_sel[l].sum(0).long(), cnt_sel)
+        assert torch.equal(acc[l].long(), cnt_sel)
+        assert torch.equal(holder.cnt_unb[l].sum(0).long(), torch.bincount(unb[l].reshape(-1), minlength=E))
+        per_seq = torch.stack([torch.bincount(sel[l][b * S:(b + 1) * S].reshape(-1), minlength=E) for b in range(B)])
+        assert torch.equal(holder.cnt_sel[l].long(), per_seq)
+        top = topk_lowest_index(scores[l].detach(), K + 1)[0]
+        assert torch.allclose(holder.margin[l], top[:, K - 1] - top[:, K], atol=1e-6)
+        assert relerr(wk[l].grad, wo[l].grad) < 3e-2, (l, relerr(wk[l].grad, wo[l].grad))
+
+
+def test_dense_swiglu_mlp(dev, tile_kind):
+    from moe_b200 import ops
+
+    torch.manual_seed(12)
+    T, H, I = 600, 256, 384
+    x = _bf(T, H)
+    wg, wu, wd = (torch.randn(I, H, device=dev) * 0.05, torch.randn(I, H, device=dev) * 0.05,
+                  torch.randn(H, I, device=dev) * 0.05)
+    ks = [t.clone().requires_grad_() for t in (x, wg, wu, wd)]
+    y = ops.swiglu_mlp(*ks)
+    g = _bf(T, H)
+    (y.float() * g.float()).sum().backward()
+    os_ = [x.float().requires_grad_()] + [t.bfloat16().float().requires_grad_() for t in (wg, wu, wd)]
+    with ops.force_oracle():
+        y2 = ops.swiglu_mlp(*os_)
+    (y2 * g.float()).sum().backward()
+    _sync_status()
+    assert relerr(y, y2) < 2e-2
+    for a, b in zip(ks, os_):
+        assert relerr(a.grad, b.grad) < 3e-2
 
 
 def test_adamw_and_norm(dev):
