@@ -42,6 +42,8 @@ def parse_args():
     ap.add_argument("--ep", action="store_true", help="shard the experts over all ranks (expert parallelism)")
     ap.add_argument("--no-zero", action="store_true",
                     help="replicate Adam moments and the update on every rank (default for N > 1: sharded, ZeRO-1)")
+    ap.add_argument("--fsdp", action="store_true",
+                    help="shard parameters, gradients and optimizer state (ZeRO-3) instead of ZeRO-1")
     ap.add_argument("--layers", type=int, default=None, help="override num_hidden_layers (shape debugging only)")
     ap.add_argument("--checkpoint", action="store_true", help="recompute each decoder layer in backward")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no whole-step CUDA graph)")
@@ -193,7 +195,8 @@ def run_ours(args) -> dict:
         raise SystemExit("bench.py runs expert parallelism over all ranks (ep_size == number of GPUs)")
     model, mcfg = build_model(cfg, seed=42, device=f"cuda:{local}", ep=ep)
     trainer = Trainer(model, tcfg, is_moe=cfg["model"]["type"] != "dense", overlap_grad_reduce=not args.no_overlap,
-                      cuda_graph=not args.no_graph, shard_optimizer=(not args.no_zero) and world > 1)
+                      cuda_graph=not args.no_graph,
+                      shard_optimizer=(not args.no_zero) and world > 1 and not args.fsdp, shard_params=args.fsdp)
     n_params = sum(p.numel() * (ep_size if getattr(p, "_ep_shard", None) else 1) for p in model.parameters())
     K, W = args.steps, args.warmup
     host = make_batches(W + 2 * K, B, S, V, rank, cfg["data"].get("seed", 0))
@@ -227,7 +230,9 @@ def run_ours(args) -> dict:
     value = tokens / (ms / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
     par = f"dp{world}" + (f"+ep{ep_size}" if ep else "")
-    if trainer.engine.sharded:
+    if getattr(trainer.engine, "sharded_params", False):
+        par += ", parameters, gradients and Adam state sharded over the ranks (ZeRO-3)"
+    elif trainer.engine.sharded:
         par += ", Adam state and update sharded over the ranks (ZeRO-1)"
     return {
         "metric": "train_tokens_per_sec", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,

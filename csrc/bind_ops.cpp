@@ -384,6 +384,15 @@ void peer_barrier(const std::vector<int64_t>& flags, int64_t rank, int64_t world
   rc_ok(b200_peer_barrier(&p, (int)rank, (int)world, (int)chan, epoch_base.data_ptr<int>(), (int)epoch_off,
                           status.data_ptr<int>(), 0, stream()), "peer_barrier");
 }
+void allgather_bf16(const std::vector<int64_t>& shards, int64_t per, int64_t n, Tensor& dst, int64_t blocks) {
+  bf16c(dst, "dst");
+  need(dst.numel() >= n, "allgather_bf16: destination too small");
+  need(!shards.empty() && (int)shards.size() <= B200_MAX_RANKS, "allgather_bf16: 1..8 ranks");
+  c10::cuda::CUDAGuard g(dst.device());
+  const void* ptrs[B200_MAX_RANKS] = {nullptr};
+  for (size_t r = 0; r < shards.size(); ++r) ptrs[r] = reinterpret_cast<const void*>(shards[r]);
+  rc_ok(b200_allgather_bf16(ptrs, (int)shards.size(), per, n, dst.data_ptr(), (int)blocks, stream()), "allgather_bf16");
+}
 void clip_coef_multi(const Tensor& parts, int64_t world, double max_norm, Tensor& coef) {
   f32c(parts, "parts"); f32c(coef, "coef");
   c10::cuda::CUDAGuard g(parts.device());
@@ -396,6 +405,7 @@ void clip_coef_multi(const Tensor& parts, int64_t world, double max_norm, Tensor
 void bind_ops(pybind11::module_& m) {
   m.def("allreduce", &allreduce);
   m.def("peer_barrier", &peer_barrier);
+  m.def("allgather_bf16", &allgather_bf16);
   m.def("ep_exchange", &ep_exchange);
   m.def("ep_dispatch", &ep_dispatch);
   m.def("clip_coef_multi", &clip_coef_multi);

@@ -201,9 +201,58 @@ __global__ void peer_barrier_kernel(ArPeers peers, int rank, int world, int chan
   if (!ok) report(status, ST_TIMEOUT_PEER);
 }
 
+// Parameter all-gather for sharded parameters: every rank keeps `per` bf16 elements of a unit at the same
+// offset of its shard buffer (symmetric memory); this rank pulls all ranks' pieces with plain 16-byte peer
+// loads (no TMA, no waits: the pieces are stable between two optimizer steps) into a LOCAL staging buffer,
+// which is what the GEMMs' TMA then reads.  dst[r * per + i] = shard_r[i], clipped to `n` elements.
+struct AgPeers {
+  const uint4* shard[B200_MAX_RANKS];
+};
+__global__ void __launch_bounds__(512)
+allgather_bf16_kernel(AgPeers peers, int world, long long per16, long long n16, uint4* __restrict__ dst) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int U = 4;
+  for (int r0 = 0; r0 < world; ++r0) {
+    const int r = (r0 + blockIdx.x) % world;  // blocks start on different peers
+    const uint4* src = peers.shard[r];
+    const long long base = static_cast<long long>(r) * per16;
+    long long len = n16 - base;
+    if (len > per16) len = per16;
+    for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < len; i0 += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < len)
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                       : "l"(src + i));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < len) dst[base + i] = v[u];
+      }
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+// shards: every rank's pointer to the unit's piece (bf16, 16-byte aligned); per / n in elements, multiples of 8
+extern "C" int b200_allgather_bf16(const void* const* shards, int world, long long per, long long n, void* dst,
+                                   int blocks, cudaStream_t stream) {
+  if (world < 1 || world > B200_MAX_RANKS || (per & 7) != 0 || (n & 7) != 0) return -1;
+  if (n <= 0) return 0;
+  AgPeers ap;
+  for (int r = 0; r < B200_MAX_RANKS; ++r) ap.shard[r] = r < world ? reinterpret_cast<const uint4*>(shards[r]) : nullptr;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 296) blocks = 296;
+  allgather_bf16_kernel<<<blocks, 512, 0, stream>>>(ap, world, per >> 3, n >> 3, reinterpret_cast<uint4*>(dst));
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long long n, float scale,
                               const int* epoch_base, int epoch_off, int final_bucket, int publish, int use_multimem,

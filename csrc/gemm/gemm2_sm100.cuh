@@ -310,27 +310,52 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             if constexpr (EPI == EPI_LSE) {
               // statistics of the bf16-rounded logits, valid columns only
               constexpr float kLog2e = 1.4426950408889634f;
-              float v[32];
-              float cmax = -INFINITY;
+              if (col0 + 32 <= args.N) {
+                // two values per issue slot (f32x2) and four independent partial sums
+                float cmax = -INFINITY;
+                uint64_t v2[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float2 f = unpack_bf16x2(p[j]);
-                v[2 * j] = (col0 + 2 * j < args.N) ? f.x : -INFINITY;
-                v[2 * j + 1] = (col0 + 2 * j + 1 < args.N) ? f.y : -INFINITY;
-                cmax = fmax3(cmax, v[2 * j], v[2 * j + 1]);
-              }
-              const float new_max = fmaxf(run_max, cmax);
-              const float nm = -new_max * kLog2e;
-              float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+                for (int j = 0; j < 16; ++j) {
+                  const float2 f = unpack_bf16x2(p[j]);
+                  v2[j] = pack2(f.x, f.y);
+                  cmax = fmax3(cmax, f.x, f.y);
+                }
+                const float new_max = fmaxf(run_max, cmax);
+                const float nm = -new_max * kLog2e;
+                const uint64_t l2 = pack2(kLog2e, kLog2e), nm2 = pack2(nm, nm);
+                uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                s0 += ex2_approx(fmaf(v[4 * j], kLog2e, nm));
-                s1 += ex2_approx(fmaf(v[4 * j + 1], kLog2e, nm));
-                s2 += ex2_approx(fmaf(v[4 * j + 2], kLog2e, nm));
-                s3 += ex2_approx(fmaf(v[4 * j + 3], kLog2e, nm));
+                for (int j = 0; j < 16; ++j) {
+                  float xl, xh;
+                  unpack2(fma2(v2[j], l2, nm2), xl, xh);
+                  acc2[j & 3] = add2(acc2[j & 3], pack2(ex2_approx(xl), ex2_approx(xh)));
+                }
+                float a0, a1, a2, a3, a4, a5, a6, a7;
+                unpack2(acc2[0], a0, a1);
+                unpack2(acc2[1], a2, a3);
+                unpack2(acc2[2], a4, a5);
+                unpack2(acc2[3], a6, a7);
+                const float ssum = ((a0 + a1) + (a2 + a3)) + ((a4 + a5) + (a6 + a7));
+                run_sum = run_sum * ex2_approx((run_max - new_max) * kLog2e) + ssum;
+                run_max = new_max;
+              } else {
+                float v[32];
+                float cmax = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const float2 f = unpack_bf16x2(p[j]);
+                  v[2 * j] = (col0 + 2 * j < args.N) ? f.x : -INFINITY;
+                  v[2 * j + 1] = (col0 + 2 * j + 1 < args.N) ? f.y : -INFINITY;
+                  cmax = fmax3(cmax, v[2 * j], v[2 * j + 1]);
+                }
+                const float new_max = fmaxf(run_max, cmax);
+                const float nm = -new_max * kLog2e;
+                float ssum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ssum += ex2_approx(fmaf(v[j], kLog2e, nm));
+                run_sum = run_sum * ex2_approx((run_max - new_max) * kLog2e) + ssum;
+                run_max = new_max;
               }
-              run_sum = run_sum * ex2_approx((run_max - new_max) * kLog2e) + ((s0 + s1) + (s2 + s3));
-              run_max = new_max;
             }
             if (live) {
 #pragma unroll

@@ -104,6 +104,10 @@ int b200_allreduce(const B200Peers* p, int rank, int world, long long off, long 
 int b200_peer_barrier(const B200Peers* p, int rank, int world, int chan, const int* epoch_base, int epoch_off,
                       int* status, unsigned long long limit_ns, cudaStream_t stream);
 int b200_clip_coef_multi(const float* parts, int world, float max_norm, float* coef, cudaStream_t stream);
+// all-gather of one sharded parameter unit into a local buffer: dst[r * per + i] = shards[r][i], i < per,
+// clipped to n elements overall (bf16; per and n multiples of 8)
+int b200_allgather_bf16(const void* const* shards, int world, long long per, long long n, void* dst, int blocks,
+                        cudaStream_t stream);
 
 // ---- moe/ep.cu (expert parallelism over peer memory; pointer arrays have B200_MAX_RANKS entries)
 #define B200_EP_CH_COUNTS 0

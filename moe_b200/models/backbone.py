@@ -187,7 +187,8 @@ class DecoderModel(nn.Module):
         self.layers = nn.ModuleList(layers)
         self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
         self.gradient_checkpointing = False
-        self._boundary_fn = None  # installed by the training engine (gradient-reduce overlap)
+        self._boundary_fn = None  # installed by the training engine (gradient-reduce overlap, parameter pulls)
+        self._boundary_after_last = False  # engines that shard parameters also want a call in front of the head
 
     def forward(self, input_ids):
         """Returns (final normalised hidden states [B,S,H], tuple of per-layer router scores)."""
@@ -207,6 +208,8 @@ class DecoderModel(nn.Module):
                 h, y, scores = layer(h, y, nxt, ge)
             if scores is not None:
                 all_scores.append(scores)
+        if self._boundary_fn is not None and self._boundary_after_last:
+            h, y = self._boundary_fn(h, y, n)
         return y, tuple(all_scores)
 
 

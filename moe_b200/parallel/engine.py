@@ -61,6 +61,7 @@ class _LayerBoundary(torch.autograd.Function):
 
 class TrainEngine:
     HYPER_SLOTS = 8  # steps the host may stage ahead of the device
+    sharded_params = False  # True in FsdpEngine: parameters exist only as per-rank slices
 
     def __init__(self, model: nn.Module, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, process_group=None,
@@ -540,6 +541,15 @@ class TrainEngine:
             for p_lo, p_hi, m_lo, _, _ in self._segments:
                 self.m[m_lo:m_lo + p_hi - p_lo].copy_(m[p_lo:p_hi])
                 self.v[m_lo:m_lo + p_hi - p_lo].copy_(v[p_lo:p_hi])
+
+    def model_state_dict(self) -> dict:
+        """Name -> tensor with the fp32 master values (call `sync_master()` first when the optimizer is sharded)."""
+        return self.model.state_dict()
+
+    def full_master(self) -> torch.Tensor:
+        """The flat fp32 master buffer in parameter layout."""
+        self.sync_master()
+        return self.p32
 
     def load_model_state_dict(self, sd: dict, strict: bool = True) -> None:
         self.model.load_state_dict(sd, strict=strict)

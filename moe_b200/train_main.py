@@ -169,22 +169,26 @@ def main(argv=None) -> None:
     bias_interp = cfg["model"].get("bias_interpolation", False)
     seq_coef = cfg["model"].get("seq_aux_loss_coef", 0.0) or 0.0
     pcfg = cfg.get("parallel", {})
-    # "ddp": replicated optimizer state; "zero" (alias "fsdp"): Adam moments and the update sharded over the
-    # ranks, new bf16 weights stored to every rank by the update kernel
+    # "ddp": everything replicated; "zero": Adam moments and the update sharded over the ranks (ZeRO-1), new bf16
+    # weights stored to every rank by the update kernel; "fsdp": parameters, gradients and optimizer state
+    # sharded, each layer's weights pulled from the peers right before use (ZeRO-3)
     # Defaults are what `bench.py` measures: sharded optimizer on more than one GPU, whole-step CUDA graph.
     pmode = str(pcfg.get("mode", "zero" if (world > 1 and device == "cuda") else "ddp")).lower()
     if pmode not in ("ddp", "zero", "fsdp"):
         raise ValueError(f"parallel.mode={pcfg.get('mode')!r}: expected ddp, zero or fsdp")
-    shard_opt = pmode in ("zero", "fsdp") and world > 1 and device == "cuda"
+    shard_opt = pmode == "zero" and world > 1 and device == "cuda"
+    shard_par = pmode == "fsdp" and device == "cuda"
+    if pmode == "fsdp" and device != "cuda":
+        raise ValueError("parallel.mode: fsdp needs CUDA (parameters are pulled over NVLink peer memory)")
     use_graph = bool(pcfg.get("cuda_graph", True)) and device == "cuda" and not args.profile
     if main_proc:
         print(f"\n{'=' * 60}\n  Model     : {mtype}\n  Params    : {params['total'] / 1e9:.3f}B total  |  "
-              f"{expert_params / 1e9:.3f}B expert\n  Dist type : {('ZeRO-1' if shard_opt else 'DDP') if world > 1 else 'single'} ({device})\n"
+              f"{expert_params / 1e9:.3f}B expert\n  Dist type : {('FSDP (ZeRO-3)' if shard_par else 'ZeRO-1' if shard_opt else 'DDP') if world > 1 else 'single'} ({device})\n"
               f"  Precision : {'bf16 compute, fp32 master' if device == 'cuda' else 'fp32'}\n  GPUs      : {world}\n"
               f"{'=' * 60}\n", flush=True)
 
     trainer = Trainer(model, tcfg, is_moe=not is_dense, overlap_grad_reduce=pcfg.get("overlap", True),
-                      shard_optimizer=shard_opt, cuda_graph=use_graph)
+                      shard_optimizer=shard_opt, shard_params=shard_par, cuda_graph=use_graph)
     trainer.engine.broadcast_parameters(0)
     dataset = build_dataset(ddict, cfg["model"]["vocab_size"], rank, world)
     if resume_from:

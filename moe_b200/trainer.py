@@ -36,15 +36,23 @@ class StepResult:
 class Trainer:
     def __init__(self, model, cfg: TrainingConfig, *, device=None, process_group=None, is_moe: bool = True,
                  overlap_grad_reduce: bool = True, cuda_graph: bool = False, graph_warmup_steps: int = 2,
-                 ep_capacity_factor: float = 2.0, comm: str | None = None, shard_optimizer: bool = False):
+                 ep_capacity_factor: float = 2.0, comm: str | None = None, shard_optimizer: bool = False,
+                 shard_params: bool = False):
         self.model = model
         self.cfg = cfg
         self.is_moe = is_moe
-        self.engine = TrainEngine(model, lr=cfg.learning_rate, betas=(cfg.beta1, cfg.beta2), eps=cfg.eps,
-                                  weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
-                                  process_group=process_group, device=device,
-                                  overlap_grad_reduce=overlap_grad_reduce, comm=comm,
-                                  shard_optimizer=shard_optimizer)
+        if shard_params:  # ZeRO-3: parameters, gradients and optimizer state sharded, pulled per layer
+            from .parallel.fsdp import FsdpEngine
+
+            self.engine = FsdpEngine(model, lr=cfg.learning_rate, betas=(cfg.beta1, cfg.beta2), eps=cfg.eps,
+                                     weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
+                                     process_group=process_group, device=device)
+        else:
+            self.engine = TrainEngine(model, lr=cfg.learning_rate, betas=(cfg.beta1, cfg.beta2), eps=cfg.eps,
+                                      weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm,
+                                      process_group=process_group, device=device,
+                                      overlap_grad_reduce=overlap_grad_reduce, comm=comm,
+                                      shard_optimizer=shard_optimizer)
         self.device = self.engine.device
         # expert parallelism: parameters that are shards of an expert bank get the peer-memory context
         self.ep = None

@@ -97,7 +97,7 @@ def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | N
     trainer.engine.sync_master()  # sharded optimizer: every rank's fp32 weights brought up to date first
     sd = {}
     seen = {}
-    for k, v in trainer.model.state_dict().items():
+    for k, v in trainer.engine.model_state_dict().items():
         t = _gather_full(v.detach(), shards.get(k))
         key = (v.data_ptr(), tuple(v.shape))
         if key in seen:  # tied weights: safetensors refuses shared storage

@@ -30,7 +30,7 @@ def tiny_cfg(mtype="standard_moe", **kw):
 
 
 @pytest.mark.parametrize("mtype", ["standard_moe", "global_moe", "deepseek_standard_moe", "deepseek_global_moe",
-                                   "dense", "dense-hd64"])
+                                   "dense", "dense-hd64", "standard_moe-all-experts"])
 def test_forward_backward_matches_oracle(mtype):
     from moe_b200 import ops
     from moe_b200.models import build_model
@@ -38,8 +38,13 @@ def test_forward_backward_matches_oracle(mtype):
 
     torch.manual_seed(0)
     extra = {}
+    exact = False
     if mtype == "dense-hd64":  # a head size without an own attention kernel: library attention
         mtype, extra = "dense", dict(head_dim=64)
+    elif mtype == "standard_moe-all-experts":
+        # every token goes to every expert: no routing decision can differ between bf16 and fp32 scores, so
+        # each tensor's gradient has to agree closely (a wrong epilogue on a small tensor cannot hide)
+        mtype, extra, exact = "standard_moe", dict(num_experts=8, num_experts_per_tok=8), True
     model, _ = build_model(tiny_cfg(mtype, **extra), seed=1, device="cuda")
     with torch.no_grad():  # compare on bf16-representable weights
         for r in (model.routers() if mtype != "dense" else []):
@@ -67,10 +72,12 @@ def test_forward_backward_matches_oracle(mtype):
         cos = torch.nn.functional.cosine_similarity(p.grad.flatten().float(), q.grad.flatten().float(), dim=0).item()
         num += (p.grad.float() - q.grad.float()).pow(2).sum().item()
         den += q.grad.float().pow(2).sum().item()
-        if cos < 0.985:
+        if cos < (0.999 if exact or mtype == "dense" else 0.97):
             bad.append((n, cos))
+        if (exact or mtype == "dense") and relerr(p.grad, q.grad) > 4e-2:
+            bad.append((n, "relerr", relerr(p.grad, q.grad)))
     assert not bad, bad
-    assert (num / den) ** 0.5 < 0.10
+    assert (num / den) ** 0.5 < (0.04 if exact or mtype == "dense" else 0.15)
 
 
 def test_engine_training_steps_reduce_loss():
@@ -183,3 +190,43 @@ def test_graph_steps_enqueued_without_sync_use_their_own_hyper_parameters():
         finals.append(tr.engine.p32.clone())
     # a step run with a neighbour's values moves the weights by percents; run-to-run noise is far smaller
     assert relerr(finals[1], finals[0]) < 5e-3, relerr(finals[1], finals[0])
+
+
+@pytest.mark.parametrize("mtype,kw,accum,ckpt", [("standard_moe", {}, 1, False),
+                                                 ("global_moe", dict(tie_word_embeddings=True), 2, False),
+                                                 ("dense", {}, 1, True)])
+def test_sharded_parameter_engine_matches_replicated_engine(mtype, kw, accum, ckpt):
+    """The ZeRO-3 engine on one rank (every pull, gradient staging slot, reduce and shard update runs, the
+    peers are just absent) against the replicated engine: same losses, same weights after a few steps.
+    Covers the global bank in the root unit with tied embeddings, gradient accumulation and recomputation."""
+    import dataclasses
+
+    from moe_b200.models import build_model
+    from moe_b200.ops import gemm as G
+    from moe_b200.trainer import Trainer
+    from moe_b200.utils.training import TrainingConfig
+
+    tcfg = TrainingConfig(learning_rate=2e-3, warmup_steps=2, max_steps=20, batch_size=2, gradient_accumulation=accum,
+                          gradient_checkpointing=ckpt)
+    torch.manual_seed(0)
+    batches = [[torch.randint(0, 2048, (2, 128)) for _ in range(accum)] for _ in range(4)]
+    runs = []
+    for fsdp in (False, True):
+        model, _ = build_model(tiny_cfg(mtype, num_hidden_layers=3, **kw), seed=1, device="cuda")
+        tr = Trainer(model, tcfg, is_moe=mtype != "dense", shard_params=fsdp)
+        losses = []
+        for mbs in batches:
+            r = tr.train_step([{"input_ids": b, "labels": b} for b in mbs])
+            losses.append(r.loss.item())
+        torch.cuda.synchronize()
+        G.check_status()
+        runs.append((losses, tr.engine.full_master().clone(), float(r.grad_norm)))
+        if fsdp:
+            rep = tr.engine.memory_report()
+            assert rep["persistent_sharded_state"] > 0
+            sd = tr.engine.model_state_dict()
+            assert all(tuple(sd[n].shape) == tuple(p.shape) for n, p in model.named_parameters())
+    for a, b in zip(runs[0][0], runs[1][0]):
+        assert abs(a - b) < 5e-3 * abs(a), (runs[0][0], runs[1][0])
+    assert relerr(runs[1][1], runs[0][1]) < 5e-3
+    assert abs(runs[0][2] - runs[1][2]) < 2e-2 * runs[0][2]
