@@ -513,6 +513,33 @@ class TrainEngine:
             mask[lo:lo + (hi - lo) // 4 * 4] = True
         self.p32[:self.decay_end] = torch.where(mask, own, self.p32[:self.decay_end])
 
+    # ---- sharded checkpoints: which flat ranges this rank writes, and which it must read back
+    def export_state_ranges(self) -> list[tuple[str, int, int, torch.Tensor]]:
+        """(kind, flat_lo, flat_hi, tensor) with kind 'p' (fp32 master), 'm', 'v': every element of the training
+        state is named by exactly one rank (replicated parts by rank 0, sharded parts by their owner)."""
+        out = []
+        rank0 = self.rank == 0 if hasattr(self, "rank") else True
+        for p_lo, p_hi, m_lo, _, kind in self._segments:
+            n = p_hi - p_lo
+            if kind == 0 and not rank0:
+                continue
+            out.append(("p", p_lo, p_hi, self.p32[p_lo:p_hi]))
+            out.append(("m", p_lo, p_hi, self.m[m_lo:m_lo + n]))
+            out.append(("v", p_lo, p_hi, self.v[m_lo:m_lo + n]))
+        return out
+
+    def import_state_ranges(self) -> list[tuple[str, int, int, torch.Tensor]]:
+        """Destinations this rank fills when loading: all master values it holds, its part of the moments."""
+        out = [("p", 0, self.total, self.p32)]
+        for p_lo, p_hi, m_lo, _, _ in self._segments:
+            n = p_hi - p_lo
+            out.append(("m", p_lo, p_hi, self.m[m_lo:m_lo + n]))
+            out.append(("v", p_lo, p_hi, self.v[m_lo:m_lo + n]))
+        return out
+
+    def after_state_import(self) -> None:
+        self.refresh_compute_copy()
+
     def optimizer_state_dict(self) -> dict:
         st = {"step": self.step_count, "lr": self.lr, "state": {}}
         m, v = self.full_moments()

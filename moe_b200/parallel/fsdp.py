@@ -546,6 +546,30 @@ class FsdpEngine(TrainEngine):
         self._scatter_full(m, self.m)
         self._scatter_full(v, self.v)
 
+    def _state_ranges(self, everything_local: bool) -> list:
+        out = []
+        st = self.shard_total
+        for u in [self.root] + self.ring_units:
+            a = u.lo + u.per * self.rank
+            b = min(a + u.per, u.hi)
+            if b > a:
+                for kind, buf in (("p", self.p32), ("m", self.m), ("v", self.v)):
+                    out.append((kind, a, b, buf[u.soff:u.soff + (b - a)]))
+        n_ep = self.ep_end - self.decay_end
+        if n_ep:
+            for kind, buf in (("p", self.p32), ("m", self.m), ("v", self.v)):
+                out.append((kind, self.decay_end, self.ep_end, buf[st:st + n_ep]))
+        if self.total > self.ep_end and (everything_local or self.rank == 0):
+            for kind, buf in (("p", self.p32), ("m", self.m), ("v", self.v)):
+                out.append((kind, self.ep_end, self.total, buf[st + n_ep:]))
+        return out
+
+    def export_state_ranges(self) -> list:
+        return self._state_ranges(everything_local=False)
+
+    def import_state_ranges(self) -> list:
+        return self._state_ranges(everything_local=True)
+
     def memory_report(self) -> dict:
         """Bytes this rank holds per category (what the sharding buys is persistent state / world)."""
         return {"persistent_sharded_state": int(self.shard_total * (4 * 4 + 2)),

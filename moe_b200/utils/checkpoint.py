@@ -8,6 +8,12 @@ as `expert_bias` included), `optimizer.bin` (AdamW moments by parameter name + s
 A save goes to `checkpoint-{step}.tmp` and is renamed when complete, so an interrupted save never
 shadows the previous checkpoint.  State is stored by name, not by rank, so a run can resume on a
 different number of data-parallel ranks.
+
+Runs whose state is sharded (sharded optimizer, sharded parameters, expert parallelism) write the sharded
+payload of `sharded_state.py` instead of `model.safetensors` + `optimizer.bin`: every rank writes only the
+slices it owns (`state-{rank}.safetensors`), rank 0 adds `index.json` and `extra.bin` (buffers, step, lr), and
+nothing of the size of the model ever passes through one process.  `consolidate()` turns such a directory
+into a plain `model.safetensors` on the CPU.
 """
 from __future__ import annotations
 
@@ -78,9 +84,52 @@ def _set_rng_state(st: dict) -> None:
         torch.cuda.set_rng_state(st["cuda"])
 
 
+def _gather_objects(obj):
+    rank, world = _rank_world()
+    if world == 1:
+        return [obj]
+    out = [None] * world
+    dist.all_gather_object(out, obj)
+    return out
+
+
+def _save_sharded(trainer, tmp: str, rank: int, world: int) -> None:
+    from . import sharded_state as ss
+
+    eng = trainer.engine
+    metas = ss.metas_from_engine(eng)
+    part = ss.write_shard(tmp, rank, metas, eng.export_state_ranges())
+    # full shapes of expert banks are the same on every rank; rank 0's metas name every tensor
+    parts = _gather_objects(part)
+    if rank == 0:
+        ss.write_index(tmp, parts, metas, world)
+        params = {n for n, _ in trainer.model.named_parameters()}
+        buffers = {k: v.detach().cpu() for k, v in trainer.model.state_dict().items() if k not in params}
+        torch.save({"buffers": buffers, "step": eng.step_count, "lr": eng.lr}, os.path.join(tmp, "extra.bin"))
+
+
+def _load_sharded(trainer, resume_from: str, strict: bool) -> None:
+    from . import sharded_state as ss
+
+    eng = trainer.engine
+    rd = ss.ShardReader(resume_from)
+    rd.fill(ss.metas_from_engine(eng), eng.import_state_ranges(), strict=strict)
+    extra = torch.load(os.path.join(resume_from, "extra.bin"), map_location="cpu", weights_only=False)
+    own = dict(trainer.model.named_buffers())
+    for k, v in extra.get("buffers", {}).items():
+        if k in own:
+            own[k].copy_(v)
+    eng.step_count = int(extra.get("step", 0))
+    eng.lr = float(extra.get("lr", eng.lr))
+    eng.after_state_import()
+
+
 def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | None = None,
-                    wandb_run_id: str | None = None, scheduler_state: dict | None = None) -> str:
-    """All ranks call this.  Rank 0 writes the shared files; every rank writes its RNG and data state."""
+                    wandb_run_id: str | None = None, scheduler_state: dict | None = None,
+                    sharded: bool | None = None) -> str:
+    """All ranks call this.  Rank 0 writes the shared files; every rank writes its RNG and data state.
+    `sharded` (default: whenever the engine shards optimizer state, parameters or experts) selects the
+    per-rank payload described in the module docstring."""
     from safetensors.torch import save_file
 
     rank, world = _rank_world()
@@ -91,6 +140,15 @@ def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | N
             shutil.rmtree(tmp)
         os.makedirs(tmp, exist_ok=True)
     _barrier()
+    eng = trainer.engine
+    if sharded is None:
+        sharded = bool(getattr(eng, "sharded", False) or getattr(eng, "sharded_params", False)
+                       or getattr(eng, "has_ep", False))
+    if sharded:
+        _save_sharded(trainer, tmp, rank, world)
+        if rank == 0:
+            torch.save(scheduler_state or {"last_epoch": trainer.global_step}, os.path.join(tmp, "scheduler.bin"))
+        return _finish_save(tmp, final, rank, world, step, dataset_state, wandb_run_id)
     # expert-parallel shards are gathered into whole banks (all ranks take part), so the files do
     # not depend on the expert-parallel size of the run that wrote them
     shards = {n: getattr(p, "_ep_shard", None) for n, p in trainer.model.named_parameters()}
@@ -114,6 +172,11 @@ def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | N
         save_file(sd, os.path.join(tmp, "model.safetensors"), metadata={"format": "pt"})
         torch.save(opt, os.path.join(tmp, "optimizer.bin"))
         torch.save(scheduler_state or {"last_epoch": trainer.global_step}, os.path.join(tmp, "scheduler.bin"))
+    return _finish_save(tmp, final, rank, world, step, dataset_state, wandb_run_id)
+
+
+def _finish_save(tmp, final, rank, world, step, dataset_state, wandb_run_id) -> str:
+    """Per-rank RNG / data position, then `meta.json` and the atomic rename by rank 0."""
     with open(os.path.join(tmp, f"random_states_{rank}.pkl"), "wb") as f:
         pickle.dump(_rng_state(), f)
     if dataset_state is not None:
@@ -133,6 +196,13 @@ def save_checkpoint(trainer, step: int, output_dir: str, dataset_state: dict | N
         os.rename(tmp, final)
     _barrier()
     return final
+
+
+def consolidate(ckpt_dir: str, out_path: str | None = None) -> str:
+    """`model.safetensors` with whole tensors from a sharded checkpoint directory (CPU only)."""
+    from . import sharded_state as ss
+
+    return ss.consolidate(ckpt_dir, out_path)
 
 
 def _gather_full(t: torch.Tensor, shard) -> torch.Tensor:
@@ -165,7 +235,9 @@ def load_checkpoint(trainer, resume_from: str, strict: bool = True) -> tuple[int
 
     rank, world = _rank_world()
     mpath = os.path.join(resume_from, "model.safetensors")
-    if os.path.exists(mpath):
+    if os.path.exists(os.path.join(resume_from, "index.json")):
+        _load_sharded(trainer, resume_from, strict)
+    elif os.path.exists(mpath):
         sd = load_file(mpath)
         if getattr(trainer.model.config, "tie_word_embeddings", False) and "lm_head.weight" not in sd:
             sd["lm_head.weight"] = sd["model.embed_tokens.weight"]
@@ -173,7 +245,7 @@ def load_checkpoint(trainer, resume_from: str, strict: bool = True) -> tuple[int
         sd = {k: (_slice_for(params[k], v) if k in params else v) for k, v in sd.items()}
         trainer.engine.load_model_state_dict(sd, strict=strict)
     opath = os.path.join(resume_from, "optimizer.bin")
-    if os.path.exists(opath):
+    if os.path.exists(opath) and not os.path.exists(os.path.join(resume_from, "index.json")):
         opt = torch.load(opath, map_location="cpu", weights_only=False)
         params = dict(trainer.model.named_parameters())
         for name, st in opt["state"].items():
