@@ -34,7 +34,8 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
              int64_t ep_wait_n, const OptT& ep_epoch_base, int64_t ep_wait_epoch_off,
              const std::vector<int64_t>& ep_scatter_dst, const OptT& ep_scatter_meta,
              const std::vector<int64_t>& ep_post_flags, int64_t ep_post_index, int64_t ep_post_epoch_off,
-             int64_t ep_world, const OptT& ep_counter, int64_t cta2, const OptT& pair_tiles) {
+             int64_t ep_world, const OptT& ep_counter, int64_t cta2, const OptT& pair_tiles,
+             int64_t ep_limit_ns) {
   check_cuda(A, "A");
   check_cuda(B, "B");
   check_cuda(C, "C");
@@ -66,6 +67,7 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
   d.ep_post_epoch_off = (int)ep_post_epoch_off;
   d.ep_world = (int)ep_world;
   d.ep_counter = ptr_or_null<int>(ep_counter);
+  d.ep_limit_ns = (unsigned long long)ep_limit_ns;
   d.cta2 = (int)cta2;
   d.pair_tiles = ptr_or_null<const int>(pair_tiles);
   d.max_pair_tiles = pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0;
@@ -91,6 +93,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("ep_scatter_dst") = std::vector<int64_t>(), py::arg("ep_scatter_meta") = py::none(),
         py::arg("ep_post_flags") = std::vector<int64_t>(), py::arg("ep_post_index") = 0,
         py::arg("ep_post_epoch_off") = 0, py::arg("ep_world") = 0, py::arg("ep_counter") = py::none(),
-        py::arg("cta2") = 0, py::arg("pair_tiles") = py::none());
+        py::arg("cta2") = 0, py::arg("pair_tiles") = py::none(), py::arg("ep_limit_ns") = 0);
   bind_ops(m);
 }

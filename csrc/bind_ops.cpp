@@ -202,6 +202,13 @@ void moe_plan(const Tensor& idx, int64_t E, Tensor& scratch, Tensor& counts, Ten
                       pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0,
                       optp<int>(num_pair_tiles), stream()), "moe_plan");
 }
+void moe_slot_dot(const Tensor& dout, const Tensor& y, int64_t K, Tensor& dw) {
+  bf16c(dout, "dout"); bf16c(y, "y"); f32c(dw, "dw");
+  const int T = (int)dout.size(0), H = (int)dout.size(1);
+  need(y.numel() == (int64_t)T * K * H && dw.numel() == (int64_t)T * K, "moe_slot_dot: shapes");
+  c10::cuda::CUDAGuard g(dout.device());
+  rc_ok(b200_moe_slot_dot(dout.data_ptr(), y.data_ptr(), T, (int)K, H, dw.data_ptr<float>(), stream()), "moe_slot_dot");
+}
 void moe_gather(const Tensor& x, const Tensor& row_slot, const Tensor& seg_off, int64_t E, int64_t K, Tensor& xs) {
   bf16c(x, "x"); bf16c(xs, "xs"); i32c(row_slot, "row_slot"); i32c(seg_off, "seg_off");
   c10::cuda::CUDAGuard g(x.device());
@@ -440,6 +447,7 @@ void bind_ops(pybind11::module_& m) {
         pybind11::arg("pos"), pybind11::arg("row_slot"), pybind11::arg("pair_tiles") = pybind11::none(),
         pybind11::arg("num_pair_tiles") = pybind11::none());
   m.def("moe_gather", &moe_gather);
+  m.def("moe_slot_dot", &moe_slot_dot);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);
   m.def("lse_loss", &lse_loss);

@@ -82,6 +82,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return true;
 }
 
+// Bounded wait that also ends when `*abort` becomes non-zero (another warp role of the CTA has given up, e.g.
+// the producer whose peers never showed up): returns false in both cases.
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, const volatile int* abort) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (((++spins) & 0xffu) == 0u) {
+      if (*abort != 0) return false;
+      if (globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) return false;
+    }
+  }
+  return true;
+}
+
 // Same with an explicit limit (kernels that never wait on another GPU use a short one).
 __device__ __forceinline__ bool mbar_wait_ns(uint64_t* bar, uint32_t parity, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;

@@ -126,12 +126,14 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
   __shared__ uint64_t bar_tempty[2];
   __shared__ uint64_t bar_drain;
   __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;  // set by a warp role that gave up, so that the others stop waiting at once
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   if (threadIdx.x == 0) {
+    abort_flag = 0;
     tma_prefetch_desc(&mapA);
     tma_prefetch_desc(&mapB);
     for (int s = 0; s < STAGES; ++s) {
@@ -177,7 +179,10 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         // then order the (generic-proxy) acquire before the async-proxy TMA reads
         const int epoch = *args.ep.epoch_base + args.ep.wait_epoch_off;
         for (int r = 0; r < args.ep.wait_n && ok; ++r) ok = wait_flag_ge(args.ep.wait_flags + r, epoch, args.ep.limit_ns);
-        if (!ok) report(args.status, ST_TIMEOUT_PEER);
+        if (!ok) {
+          report(args.status, ST_TIMEOUT_PEER);
+          *reinterpret_cast<volatile int*>(&abort_flag) = 1;
+        }
         asm volatile("fence.proxy.async;" ::: "memory");
       }
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
@@ -247,7 +252,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
         TileInfo ti;
         decode_tile(args, t, m_tiles, n_tiles, ti);
-        if (!mbar_wait(&bar_tempty[acc], acc_phase ^ 1u)) {
+        if (!mbar_wait_abortable(&bar_tempty[acc], acc_phase ^ 1u, &abort_flag)) {
           report(args.status, ST_TIMEOUT_MMA);
           ok = false;
           break;
@@ -255,8 +260,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < ti.num_kb; ++kb) {
-          if (!mbar_wait(&bar_full[stage], phase)) {
+          if (!mbar_wait_abortable(&bar_full[stage], phase, &abort_flag)) {
             report(args.status, ST_TIMEOUT_MMA);
+            *reinterpret_cast<volatile int*>(&abort_flag) = 1;
             ok = false;
             break;
           }
@@ -298,7 +304,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
     for (int t = blockIdx.x; t < total; t += gridDim.x) {
       TileInfo ti;
       decode_tile(args, t, m_tiles, n_tiles, ti);
-      if (!mbar_wait(&bar_tfull[acc], acc_phase)) {
+      if (!mbar_wait_abortable(&bar_tfull[acc], acc_phase, &abort_flag)) {
         report(args.status, ST_TIMEOUT_EPILOGUE);
         break;
       }

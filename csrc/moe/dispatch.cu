@@ -285,9 +285,43 @@ __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, c
   }
 }
 
+// dw[t, k] = <dout[t], y[t * K + k]>: gradient of the routing weights when the expert outputs are laid out by
+// (token, slot), as the expert-parallel return buffer is.  One warp per (token, slot), fixed summation order.
+__global__ void moe_slot_dot_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y, int n,
+                                    int K, int H, float* __restrict__ dw) {
+  const int nch = H >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  for (int i = blockIdx.x * wpb + warp; i < n; i += gridDim.x * wpb) {
+    const uint4* g = reinterpret_cast<const uint4*>(dout + static_cast<size_t>(i / K) * H);
+    const uint4* r = reinterpret_cast<const uint4*>(y + static_cast<size_t>(i) * H);
+    float dot = 0.f;
+    for (int c = lane; c < nch; c += 32) {
+      const uint4 gq = g[c], yq = __ldcg(r + c);
+      const uint32_t gu[4] = {gq.x, gq.y, gq.z, gq.w}, yu[4] = {yq.x, yq.y, yq.z, yq.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 gf = unpack_bf16x2(gu[j]), yf = unpack_bf16x2(yu[j]);
+        dot += gf.x * yf.x + gf.y * yf.y;
+      }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) dw[i] = dot;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_moe_slot_dot(const void* dout, const void* y, int T, int K, int H, float* dw, cudaStream_t stream) {
+  if (H % 8 != 0) return -1;
+  if (T <= 0 || K <= 0) return 0;
+  int grid = (T * K + 7) / 8;
+  if (grid > 1184) grid = 1184;
+  moe_slot_dot_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
+                                                reinterpret_cast<const __nv_bfloat16*>(y), T * K, K, H, dw);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" int b200_moe_plan_blocks(int n) { return (n + PLAN_CHUNK - 1) / PLAN_CHUNK; }
 

@@ -185,7 +185,8 @@ class EPMoEFn(torch.autograd.Function):
         d2 = dout.reshape(T, H)
         d2 = (d2 if d2.dtype == BF16 else d2.to(BF16)).contiguous()
         # gradient of the routing weights: <dout[t], y[t, k]> with the unscaled expert outputs kept from forward
-        dw = torch.einsum("tkh,th->tk", b["yret"].t.view(T, K, H).float(), d2.float())
+        dw = torch.empty(T, K, dtype=torch.float32, device=dev)
+        e.moe_slot_dot(d2, b["yret"].t, K, dw)
         bb = ep.bwd_buffers(ctx.key & 1, T, K, H)
         e3 = ep.next_epoch()
         e.ep_dispatch(d2, tw.view(-1), idx32.view(-1), plan.pos, plan.seg_off, send_base, bb["dyrecv"].ptrs,
