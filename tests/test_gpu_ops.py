@@ -89,12 +89,13 @@ def test_rmsnorm_fwd_bwd(dev):
         assert relerr(w.grad, w2.grad) < 2e-2
 
 
-@pytest.mark.parametrize("hd", [32, 64, 128])
-def test_qknorm_rope(dev, hd):
+@pytest.mark.parametrize("hd,nh,nkv", [(32, 4, 2), (64, 4, 2), (128, 4, 2), (32, 6, 3), (64, 5, 5), (128, 3, 1)])
+def test_qknorm_rope(dev, hd, nh, nkv):
+    """Head counts that do not fill the last warp pass are included (several heads share a warp)."""
     from moe_b200.ops import functional as F, oracle
 
     torch.manual_seed(3)
-    B, S, nh, nkv = 2, 64, 4, 2
+    B, S = 2, 64
     qkv = _bf(B, S, (nh + 2 * nkv) * hd).requires_grad_()
     qw = (1 + 0.1 * torch.randn(hd, device=dev)).requires_grad_()
     kw = (1 + 0.1 * torch.randn(hd, device=dev)).requires_grad_()
