@@ -25,8 +25,10 @@ struct Gemm2Cfg {
   static constexpr int A_BYTES = 128 * GEMM_BK * 2;
   static constexpr int B_BYTES = (BN / 2) * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  // 4 KB staging buffers (32 rows x 128 B) per epilogue warp
-  static constexpr int RING = (EPI == EPI_SWIGLU) ? 3 : 2;
+  // 4 KB staging buffers (32 rows x 128 B) per epilogue warp.  The SwiGLU backward also stages its INPUT
+  // (the stored pre-activations) through shared memory: two double-buffered 4 KB tiles (gate, up) that TMA
+  // fetches one 64-column piece ahead, plus two output tiles.
+  static constexpr int RING = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD) ? 6 : 2;
   static constexpr int EPI_BYTES = 4 * RING * 4096;
   static constexpr int STAGES_FIT = (232448 - 1024 - 512 - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
@@ -94,6 +96,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
   __shared__ uint64_t bar_empty[STAGES];  // in each CTA: the pair's MMAs have consumed the stage
   __shared__ uint64_t bar_tfull[2];       // in each CTA: accumulator buffer complete
   __shared__ uint64_t bar_tempty[2];      // used in the even CTA: all 8 epilogue warps of the pair have drained it
+  __shared__ uint64_t bar_in[4][2];       // SwiGLU backward: per epilogue warp and buffer, pre-activation tile landed
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5;
@@ -115,6 +118,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
       mbar_init(&bar_tfull[s], 1);
       mbar_init(&bar_tempty[s], 8);
     }
+    for (int s = 0; s < 8; ++s) mbar_init(&bar_in[s >> 1][s & 1], 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -270,21 +274,32 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     int slot = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int in_buf = 0;            // SwiGLU backward: buffer the next pre-activation piece goes to
+    uint32_t in_phase = 0;     // bit b = parity of the next completion of bar_in[q][b]
     for (int t = first; t < total; t += step) {
       Tile2 ti;
       decode_tile2(args, t, m_tiles, n_tiles, ti);
-      if (!mbar_wait(&bar_tfull[acc], acc_phase)) {
-        report(args.status, ST_TIMEOUT_EPILOGUE);
-        break;
-      }
-      tc_fence_after();
-      const uint32_t t_acc = tmem_base + lane_base + static_cast<uint32_t>(acc * BN);
       const int row0 = ti.m0 + static_cast<int>(rank) * 128 + q * 32;  // first row of this warp's piece
       const long long row_g = static_cast<long long>(row0) + lane;
       // grouped by rows: the odd CTA's half of a pair tile may lie past the expert's segment
       const bool live = leader || ti.halves == 2;
       const bool row_ok = live && row_g < args.M;
       const int n0 = ti.n_idx * BN_OUT;
+      if constexpr (EPI == EPI_SWIGLU_BWD) {
+        // fetch the first 64-column piece of the stored pre-activations while the MMAs of the tile still run
+        if (live && n0 < args.N && lane == 0) {
+          uint64_t* b = &bar_in[q][in_buf];
+          mbar_expect_tx(b, 8192);
+          tma_load_3d(ring + in_buf * 8192, &mapC, b, n0, row0, 0);         // gate columns
+          tma_load_3d(ring + in_buf * 8192 + 4096, &mapC, b, n0, row0, 1);  // up columns
+        }
+      }
+      if (!mbar_wait(&bar_tfull[acc], acc_phase)) {
+        report(args.status, ST_TIMEOUT_EPILOGUE);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + lane_base + static_cast<uint32_t>(acc * BN);
 
       if constexpr (EPI == EPI_BF16 || EPI == EPI_LSE) {
         float run_max = -INFINITY, run_sum = 0.f;
@@ -460,14 +475,32 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
           }
         }
       } else if constexpr (EPI == EPI_SWIGLU_BWD) {
-        const __nv_bfloat16* gurow = reinterpret_cast<const __nv_bfloat16*>(args.aux0) + row_g * args.ld_aux0;
+        // ring layout of this warp: [buffer 0: gate, up][buffer 1: gate, up][out: d gate, d up]
+        uint8_t* outb = ring + 16384;
+        bool ok_in = true;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = 0; c < BN / 64 && ok_in; ++c) {
           const int cbase = n0 + c * 64;
           if (cbase >= args.N) break;
+          const uint8_t* inb = ring + in_buf * 8192;
           if (live) {
-            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();  // everybody is done reading the other buffer (piece c - 1)
+            if (lane == 0) {
+              if (c + 1 < BN / 64 && cbase + 64 < args.N) {  // next piece of this tile into the other buffer
+                uint64_t* b = &bar_in[q][in_buf ^ 1];
+                mbar_expect_tx(b, 8192);
+                tma_load_3d(ring + (in_buf ^ 1) * 8192, &mapC, b, cbase + 64, row0, 0);
+                tma_load_3d(ring + (in_buf ^ 1) * 8192 + 4096, &mapC, b, cbase + 64, row0, 1);
+              }
+              bulk_wait_read<0>();  // the output tiles of the previous piece have been read by their stores
+            }
+            ok_in = mbar_wait(&bar_in[q][in_buf], (in_phase >> in_buf) & 1u);
+            in_phase ^= 1u << in_buf;
             __syncwarp();
+            if (!ok_in) {
+              report(args.status, ST_TIMEOUT_EPILOGUE);
+              break;
+            }
           }
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -479,26 +512,25 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             if (live) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                uint32_t og[4] = {0u, 0u, 0u, 0u}, ou[4] = {0u, 0u, 0u, 0u};
-                if (row_ok && col0 + 8 * j < args.N) {  // N is a multiple of 8
-                  const uint4 gq = *reinterpret_cast<const uint4*>(gurow + col0 + 8 * j);
-                  const uint4 uq = *reinterpret_cast<const uint4*>(gurow + args.n_half + col0 + 8 * j);
-                  const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
-                  const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
+                const int pos = ((h * 4 + j) ^ (lane & 7)) << 4;
+                const uint4 gq = *reinterpret_cast<const uint4*>(inb + lane * 128 + pos);
+                const uint4 uq = *reinterpret_cast<const uint4*>(inb + 4096 + lane * 128 + pos);
+                const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+                const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
+                uint32_t og[4], ou[4];
 #pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    const float2 gf = unpack_bf16x2(gw[i]);
-                    const float2 uf = unpack_bf16x2(uw[i]);
-                    const float d0 = __uint_as_float(r[8 * j + 2 * i]);
-                    const float d1 = __uint_as_float(r[8 * j + 2 * i + 1]);
-                    const float s0 = sigmoidf_fast(gf.x), s1 = sigmoidf_fast(gf.y);
-                    og[i] = pack_bf16x2(d0 * uf.x * s0 * (1.f + gf.x * (1.f - s0)),
-                                        d1 * uf.y * s1 * (1.f + gf.y * (1.f - s1)));
-                    ou[i] = pack_bf16x2(d0 * gf.x * s0, d1 * gf.y * s1);
-                  }
+                for (int i = 0; i < 4; ++i) {
+                  const float2 gf = unpack_bf16x2(gw[i]);
+                  const float2 uf = unpack_bf16x2(uw[i]);
+                  const float d0 = __uint_as_float(r[8 * j + 2 * i]);
+                  const float d1 = __uint_as_float(r[8 * j + 2 * i + 1]);
+                  const float s0 = sigmoidf_fast(gf.x), s1 = sigmoidf_fast(gf.y);
+                  og[i] = pack_bf16x2(d0 * uf.x * s0 * (1.f + gf.x * (1.f - s0)),
+                                      d1 * uf.y * s1 * (1.f + gf.y * (1.f - s1)));
+                  ou[i] = pack_bf16x2(d0 * gf.x * s0, d1 * gf.y * s1);
                 }
-                stage_write(ring, lane, h * 4 + j, make_uint4(og[0], og[1], og[2], og[3]));
-                stage_write(ring + 4096, lane, h * 4 + j, make_uint4(ou[0], ou[1], ou[2], ou[3]));
+                stage_write(outb, lane, h * 4 + j, make_uint4(og[0], og[1], og[2], og[3]));
+                stage_write(outb + 4096, lane, h * 4 + j, make_uint4(ou[0], ou[1], ou[2], ou[3]));
               }
             }
           }
@@ -506,10 +538,11 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&mapX, ring, cbase, row0, 0);         // d(pre-activations) [2][rows][I]: gate
-              tma_store_3d(&mapX, ring + 4096, cbase, row0, 1);  // up
+              tma_store_3d(&mapX, outb, cbase, row0, 0);         // d(pre-activations) [2][rows][I]: gate
+              tma_store_3d(&mapX, outb + 4096, cbase, row0, 1);  // up
               bulk_commit();
             }
+            in_buf ^= 1;
           }
         }
       }

@@ -232,7 +232,11 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
     const int bn_out2 = d->epi == EPI_SWIGLU ? bn / 2 : bn;
     const uint64_t c_rows = d->mode == MODE_GROUPED_K ? static_cast<uint64_t>(d->M) : static_cast<uint64_t>(d->M);
     if (d->epi == EPI_SWIGLU_BWD) {
-      mc = ma;  // unused by this epilogue
+      // the epilogue reads the stored pre-activations through TMA: [2][rows][I] view of aux0 (gate, up planes)
+      if (d->aux0 == nullptr) return -22;
+      rc = make_store_map(&mc, 2, d->aux0, static_cast<uint64_t>(d->N), static_cast<uint64_t>(d->M), 2,
+                          static_cast<uint64_t>(d->ld_aux0) * 2, static_cast<uint64_t>(d->n_half) * 2, 64, 32);
+      if (rc) return rc - 6;
     } else {
       rc = make_store_map(&mc, f32 ? 4 : 2, d->C, static_cast<uint64_t>(d->N), c_rows,
                           d->mode == MODE_GROUPED_K ? static_cast<uint64_t>(d->num_experts) : 1,
