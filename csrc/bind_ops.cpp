@@ -118,7 +118,8 @@ void flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& 
 // ------------------------------------------------------------------- router
 void router_fwd(const Tensor& logits, const OptT& bias, Tensor& scores, Tensor& topk_w, Tensor& topk_idx, int64_t K,
                 int64_t mode, bool norm, double scale, int64_t num_groups, int64_t group_topk, const OptT& cnt_sel,
-                const OptT& cnt_unb, const OptT& tokens_acc, const OptT& rsum, const OptT& margin, int64_t S) {
+                const OptT& cnt_unb, const OptT& tokens_acc, const OptT& rsum, const OptT& margin, const OptT& part,
+                int64_t S) {
   f32c(logits, "logits"); f32c(scores, "scores"); f32c(topk_w, "topk_w"); i32c(topk_idx, "topk_idx");
   c10::cuda::CUDAGuard g(logits.device());
   const int T = (int)logits.size(0), E = (int)logits.size(1);
@@ -134,10 +135,16 @@ void router_fwd(const Tensor& logits, const OptT& bias, Tensor& scores, Tensor& 
   if (tokens_acc.has_value() && tokens_acc->defined()) { f32c(*tokens_acc, "tokens_acc"); need(tokens_acc->numel() == E, "tokens_acc size"); }
   if (rsum.has_value() && rsum->defined()) { f32c(*rsum, "rsum"); need(rsum->numel() >= T, "rsum size"); }
   if (margin.has_value() && margin->defined()) { f32c(*margin, "margin"); need(margin->numel() >= T, "margin size"); }
+  if (part.has_value() && part->defined()) {
+    f32c(*part, "part");
+    const int bt = b200_router_tokens_per_block(E);
+    need(part->numel() >= (int64_t)((T + bt - 1) / bt) * 2 * E, "part must hold [blocks, 2, E] floats");
+  }
   rc_ok(b200_router_fwd(logits.data_ptr<float>(), optp<const float>(bias), scores.data_ptr<float>(),
                         topk_w.data_ptr<float>(), topk_idx.data_ptr<int>(), T, E, (int)K, (int)mode, norm ? 1 : 0,
                         (float)scale, (int)num_groups, (int)group_topk, optp<int>(cnt_sel), optp<int>(cnt_unb),
-                        optp<float>(tokens_acc), optp<float>(rsum), optp<float>(margin), (int)S, stream()),
+                        optp<float>(tokens_acc), optp<float>(rsum), optp<float>(margin), optp<float>(part), (int)S,
+                        stream()),
         "router_fwd");
 }
 void router_colsum(const Tensor& scores, const OptT& rsum, int64_t S, Tensor& psum, const OptT& pn) {
@@ -150,6 +157,16 @@ void router_colsum(const Tensor& scores, const OptT& rsum, int64_t S, Tensor& ps
   if (pn.has_value() && pn->defined()) { f32c(*pn, "pn"); need(pn->numel() == psum.numel(), "pn size"); }
   rc_ok(b200_router_colsum(scores.data_ptr<float>(), optp<const float>(rsum), B, (int)S, E, psum.data_ptr<float>(),
                            optp<float>(pn), stream()), "router_colsum");
+}
+int64_t router_tokens_per_block(int64_t E) { return b200_router_tokens_per_block((int)E); }
+void router_part_reduce(const Tensor& part, int64_t blocks_per_seq, Tensor& psum, Tensor& pn) {
+  f32c(part, "part"); f32c(psum, "psum"); f32c(pn, "pn");
+  need(psum.dim() == 2 && pn.sizes() == psum.sizes(), "psum / pn must be [B, E]");
+  const int B = (int)psum.size(0), E = (int)psum.size(1);
+  need(part.numel() >= (int64_t)B * blocks_per_seq * 2 * E, "part too small");
+  c10::cuda::CUDAGuard g(part.device());
+  rc_ok(b200_router_part_reduce(part.data_ptr<float>(), B, (int)blocks_per_seq, E, psum.data_ptr<float>(),
+                                pn.data_ptr<float>(), stream()), "router_part_reduce");
 }
 void moe_aux(const Tensor& cnt_unb, const OptT& cnt_sel, const Tensor& psum, const OptT& pn, int64_t K, int64_t S,
              const OptT& gvec, Tensor& out) {
@@ -314,6 +331,14 @@ void embed_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
         "embed_fwd");
 }
 int64_t embed_sort_capacity() { return b200_embed_sort_capacity(); }
+void embed_sort(const Tensor& ids, int64_t V, Tensor& keys) {
+  need(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids must be int64");
+  need(keys.is_cuda() && keys.scalar_type() == at::kLong && keys.is_contiguous() && keys.numel() >= ids.numel(),
+       "keys must be an int64 scratch of at least ids.numel() elements");
+  c10::cuda::CUDAGuard g(ids.device());
+  rc_ok(b200_embed_sort(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), (int)ids.numel(), (int)V,
+                        reinterpret_cast<unsigned long long*>(keys.data_ptr<int64_t>()), stream()), "embed_sort");
+}
 void embed_bwd(const Tensor& ids, const Tensor& dout, Tensor& grad, Tensor& keys, bool presorted, bool accumulate) {
   bf16c(dout, "dout"); f32c(grad, "grad");
   need(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids must be int64");
@@ -430,7 +455,9 @@ void bind_ops(pybind11::module_& m) {
           py::arg("topk_idx"), py::arg("K"), py::arg("mode"), py::arg("norm"), py::arg("scale"),
           py::arg("num_groups"), py::arg("group_topk"), py::arg("cnt_sel") = py::none(),
           py::arg("cnt_unb") = py::none(), py::arg("tokens_acc") = py::none(), py::arg("rsum") = py::none(),
-          py::arg("margin") = py::none(), py::arg("S") = 0);
+          py::arg("margin") = py::none(), py::arg("part") = py::none(), py::arg("S") = 0);
+    m.def("router_tokens_per_block", &router_tokens_per_block);
+    m.def("router_part_reduce", &router_part_reduce);
     m.def("router_colsum", &router_colsum);
     m.def("moe_aux", &moe_aux);
   }
@@ -456,6 +483,7 @@ void bind_ops(pybind11::module_& m) {
   m.def("embed_fwd", &embed_fwd);
   m.def("embed_bwd", &embed_bwd);
   m.def("embed_sort_capacity", &embed_sort_capacity);
+  m.def("embed_sort", &embed_sort);
   m.def("sumsq_blocks", &sumsq_blocks);
   m.def("sumsq", &sumsq);
   m.def("clip_coef", &clip_coef);

@@ -70,57 +70,39 @@ __global__ void lce_reduce_kernel(const float* __restrict__ row_loss, const long
   }
 }
 
-// In place over [T, V] bf16.  V must be a multiple of 8.  Blocks of 1024 threads with four 16-byte loads
-// in flight per thread: one such block per SM already saturates HBM, so the pass can run beside a GEMM
-// whose CTAs leave room for little else.
-constexpr int DL_UNROLL = 4;
-__global__ void __launch_bounds__(1024, 1)
-dlogits_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const float* __restrict__ lse,
-               const long long* __restrict__ labels, int ignore_index, int T, int V,
-               const float* __restrict__ loss_acc, float upstream) {
+// In place over [T, V] bf16; 8 elements per thread step.  V must be a multiple of 8.
+__global__ void dlogits_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const float* __restrict__ lse,
+                               const long long* __restrict__ labels, int ignore_index, int T, int V,
+                               const float* __restrict__ loss_acc, float upstream) {
   const int vch = V >> 3;
   const long long total = static_cast<long long>(T) * vch;
   const float nvalid = loss_acc[1];
   const float sc = nvalid > 0.f ? upstream / nvalid : 0.f;
   constexpr float kLog2e = 1.4426950408889634f;
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; base < total;
-       base += stride * DL_UNROLL) {
-    uint4 q[DL_UNROLL];
-    uint4* ptr[DL_UNROLL];
-    int row[DL_UNROLL], col0[DL_UNROLL];
-#pragma unroll
-    for (int u = 0; u < DL_UNROLL; ++u) {
-      const long long i = base + u * stride;
-      ptr[u] = nullptr;
-      if (i < total) {
-        row[u] = static_cast<int>(i / vch);
-        col0[u] = static_cast<int>(i - static_cast<long long>(row[u]) * vch) * 8;
-        ptr[u] = reinterpret_cast<uint4*>(logits + static_cast<size_t>(row[u]) * ld + col0[u]);
-        q[u] = *ptr[u];
-      }
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / vch);
+    const int c = static_cast<int>(i - static_cast<long long>(row) * vch);
+    uint4* p = reinterpret_cast<uint4*>(logits + static_cast<size_t>(row) * ld + c * 8);
+    const long long lab = labels[row];
+    if (lab == ignore_index || lab < 0 || lab >= V) {
+      *p = make_uint4(0, 0, 0, 0);
+      continue;
     }
+    const float nl = -lse[row] * kLog2e;
+    const uint4 q = *p;
+    const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[4];
+    const int col0 = c * 8;
 #pragma unroll
-    for (int u = 0; u < DL_UNROLL; ++u) {
-      if (ptr[u] == nullptr) continue;
-      const long long lab = labels[row[u]];
-      if (lab == ignore_index || lab < 0 || lab >= V) {
-        *ptr[u] = make_uint4(0, 0, 0, 0);
-        continue;
-      }
-      const float nl = -lse[row[u]] * kLog2e;
-      const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(w[j]);
-        float g0 = ex2_approx(fmaf(f.x, kLog2e, nl)), g1 = ex2_approx(fmaf(f.y, kLog2e, nl));
-        if (col0[u] + 2 * j == lab) g0 -= 1.f;
-        if (col0[u] + 2 * j + 1 == lab) g1 -= 1.f;
-        o[j] = pack_bf16x2(g0 * sc, g1 * sc);
-      }
-      *ptr[u] = make_uint4(o[0], o[1], o[2], o[3]);
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(u[j]);
+      float g0 = ex2_approx(fmaf(f.x, kLog2e, nl)), g1 = ex2_approx(fmaf(f.y, kLog2e, nl));
+      if (col0 + 2 * j == lab) g0 -= 1.f;
+      if (col0 + 2 * j + 1 == lab) g1 -= 1.f;
+      o[j] = pack_bf16x2(g0 * sc, g1 * sc);
     }
+    *p = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -238,7 +220,7 @@ extern "C" int b200_dlogits(void* logits, long long ld, const float* lse, const 
                             int T, int V, const float* loss_acc, float upstream, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (V % 8 != 0) return -1;
-  dlogits_kernel<<<148 * 2, 1024, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(logits), ld, lse, labels,
+  dlogits_kernel<<<148 * 16, 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(logits), ld, lse, labels,
                                                ignore_index, T, V, loss_acc, upstream);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -257,6 +239,27 @@ extern "C" int b200_embed_fwd(const long long* ids, const void* table, int T, in
 // Largest token count the single-block sort handles (64-bit keys in shared memory).
 extern "C" int b200_embed_sort_capacity() { return 16384; }
 
+// Sort the (id, position) keys of `ids` into keys[T] (at most b200_embed_sort_capacity() tokens).  The ids are
+// known when the forward pass starts, so a caller can run this early, beside other work.
+extern "C" int b200_embed_sort(const long long* ids, int T, int V, unsigned long long* keys, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (T > b200_embed_sort_capacity() || keys == nullptr) return -3;
+  int cap = 1;
+  while (cap < T) cap <<= 1;
+  const size_t smem = static_cast<size_t>(cap) * sizeof(unsigned long long);
+  if (smem > 48 * 1024) {
+    static bool raised = false;
+    if (!raised) {
+      if (cudaFuncSetAttribute(embed_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) !=
+          cudaSuccess)
+        return -4;
+      raised = true;
+    }
+  }
+  embed_sort_kernel<<<1, 1024, smem, stream>>>(ids, T, V, cap, keys);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 // keys: uint64[T] scratch.  The caller zeroes `grad` first unless `accumulate`; rows of ids that do not
 // occur are left as they are.
 extern "C" int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, float* grad,
@@ -264,20 +267,8 @@ extern "C" int b200_embed_bwd(const long long* ids, const void* dout, int T, int
   if (T <= 0) return 0;
   if (H % 8 != 0 || keys == nullptr) return -1;
   if (!presorted) {
-    if (T > b200_embed_sort_capacity()) return -3;
-    int cap = 1;
-    while (cap < T) cap <<= 1;
-    const size_t smem = static_cast<size_t>(cap) * sizeof(unsigned long long);
-    if (smem > 48 * 1024) {
-      static bool raised = false;
-      if (!raised) {
-        if (cudaFuncSetAttribute(embed_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) !=
-            cudaSuccess)
-          return -4;
-        raised = true;
-      }
-    }
-    embed_sort_kernel<<<1, 1024, smem, stream>>>(ids, T, V, cap, keys);
+    const int rc = b200_embed_sort(ids, T, V, keys, stream);
+    if (rc) return rc;
   }
   int grid = (T + 7) / 8;
   if (grid > 2368) grid = 2368;

@@ -49,12 +49,12 @@ struct RouterStats {
   float* tokens_acc;  // [E] running token counter of the router (selection counts are added)
   float* rsum;        // [T] sum of the token's scores over the experts
   float* margin;      // [T] k-th minus (k+1)-th unbiased score
+  float* part;        // [blocks, 2, E] per-block sums of the scores and of the row-normalised scores (needs rsum,
+                      // and S a multiple of the block's token count)
   int S;              // tokens per sequence
   int separate_unb;   // the unbiased top-k can differ from the selection (bias or group-limited routing)
+  int tpw;            // consecutive tokens per warp (a block covers ROUTER_WARPS * tpw consecutive tokens)
 };
-
-constexpr int ROUTER_TPW = 8;                              // consecutive tokens per warp
-constexpr int ROUTER_BLOCK_TOKENS = ROUTER_WARPS * ROUTER_TPW;  // consecutive tokens per block
 
 // mode 0: softmax, mode 1: sigmoid.  bias (may be null) only steers selection.
 __global__ void router_fwd_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
@@ -68,14 +68,21 @@ __global__ void router_fwd_kernel(const float* __restrict__ logits, const float*
   // block-level histograms (one sequence per block when S is a multiple of the block's token count)
   int* hsel = reinterpret_cast<int*>(sm + static_cast<size_t>(ROUTER_WARPS) * (E + 32));
   int* hunb = hsel + E;
+  // per-warp running sums over this warp's tokens (fixed order): [warp][raw | normalised][E]
+  float* psw = reinterpret_cast<float*>(hunb + E) + static_cast<size_t>(warp) * 2 * E;
+  const int block_tokens = ROUTER_WARPS * st.tpw;
   const bool want_cnt = st.cnt_sel != nullptr;
-  const bool block_hist = want_cnt && (st.S % ROUTER_BLOCK_TOKENS == 0);
+  const bool block_hist = want_cnt && (st.S % block_tokens == 0);
+  const bool want_part = st.part != nullptr;
   if (block_hist) {
     for (int e = threadIdx.x; e < 2 * E; e += blockDim.x) hsel[e] = 0;
-    __syncthreads();
   }
-  const int t_begin = blockIdx.x * ROUTER_BLOCK_TOKENS + warp * ROUTER_TPW;
-  for (int t = t_begin; t < t_begin + ROUTER_TPW && t < T; ++t) {
+  if (want_part) {
+    for (int e = lane; e < 2 * E; e += 32) psw[e] = 0.f;
+  }
+  __syncthreads();
+  const int t_begin = blockIdx.x * block_tokens + warp * st.tpw;
+  for (int t = t_begin; t < t_begin + st.tpw && t < T; ++t) {
     const float* lr = logits + static_cast<size_t>(t) * E;
     float* sr = scores + static_cast<size_t>(t) * E;
     if (mode == 0) {
@@ -180,6 +187,14 @@ __global__ void router_fwd_kernel(const float* __restrict__ logits, const float*
       for (int e = lane; e < E; e += 32) rs += sr[e];
       rs = warp_sum(rs);
       if (lane == 0) st.rsum[t] = rs;
+      if (want_part) {
+        const float inv = 1.f / (rs + 1e-20f);
+        for (int e = lane; e < E; e += 32) {
+          const float v = sr[e];
+          psw[e] += v;
+          psw[E + e] += v * inv;
+        }
+      }
     }
     if (st.separate_unb && (st.cnt_unb != nullptr || st.margin != nullptr)) {
       // top-(k+1) of the unbiased scores: counts for the Switch loss / report, margin between k and k+1
@@ -212,9 +227,19 @@ __global__ void router_fwd_kernel(const float* __restrict__ logits, const float*
     }
     __syncwarp();
   }
+  if (want_part) {
+    __syncthreads();
+    const float* all = reinterpret_cast<const float*>(hunb + E);
+    for (int e = threadIdx.x; e < 2 * E; e += blockDim.x) {
+      float a = 0.f;
+#pragma unroll
+      for (int w = 0; w < ROUTER_WARPS; ++w) a += all[static_cast<size_t>(w) * 2 * E + e];  // warp order: fixed
+      st.part[static_cast<size_t>(blockIdx.x) * 2 * E + e] = a;
+    }
+  }
   if (block_hist) {
     __syncthreads();
-    const int t0 = blockIdx.x * ROUTER_BLOCK_TOKENS;
+    const int t0 = blockIdx.x * block_tokens;
     if (t0 < T) {
       const int seq = t0 / st.S;
       for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -260,6 +285,38 @@ __global__ void router_colsum_kernel(const float* __restrict__ scores, const flo
     }
     psum[static_cast<size_t>(b) * E + e] = x;
     if (pn != nullptr) pn[static_cast<size_t>(b) * E + e] = y;
+  }
+}
+
+// Per-sequence sums from the per-block partials router_fwd_kernel wrote: psum[b, e] (and pn[b, e]) = sum over the
+// `bps` blocks of sequence b, in a fixed order (32 warps stride over the blocks, then warp order).
+__global__ void __launch_bounds__(1024)
+router_part_reduce_kernel(const float* __restrict__ part, int bps, int E, float* __restrict__ psum,
+                          float* __restrict__ pn) {
+  __shared__ float sh[2][32][33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.x * 32 + lane;
+  const int b = blockIdx.y;
+  float a = 0.f, n = 0.f;
+  if (e < E) {
+    for (int k = warp; k < bps; k += 32) {
+      const float* p = part + (static_cast<size_t>(b) * bps + k) * 2 * E;
+      a += p[e];
+      n += p[E + e];
+    }
+  }
+  sh[0][warp][lane] = a;
+  sh[1][warp][lane] = n;
+  __syncthreads();
+  if (warp == 0 && e < E) {
+    float x = 0.f, y = 0.f;
+#pragma unroll
+    for (int w = 0; w < 32; ++w) {
+      x += sh[0][w][lane];
+      y += sh[1][w][lane];
+    }
+    psum[static_cast<size_t>(b) * E + e] = x;
+    pn[static_cast<size_t>(b) * E + e] = y;
   }
 }
 
@@ -381,7 +438,8 @@ __global__ void router_bwd_kernel(const float* __restrict__ dscores, const float
 
 using namespace b200;
 
-static int router_fwd_grid(int T) { return (T + ROUTER_BLOCK_TOKENS - 1) / ROUTER_BLOCK_TOKENS; }
+// tokens per warp: few for small expert counts (many blocks in flight), more when a token's row is long
+extern "C" int b200_router_tokens_per_block(int E) { return ROUTER_WARPS * (E <= 256 ? 2 : 8); }
 
 static int router_grid(int T) {
   int g = (T + ROUTER_WARPS - 1) / ROUTER_WARPS;
@@ -390,8 +448,8 @@ static int router_grid(int T) {
 
 extern "C" int b200_router_fwd(const float* logits, const float* bias, float* scores, float* topk_w, int* topk_idx,
                                int T, int E, int K, int mode, int norm, float scale, int num_groups, int group_topk,
-                               int* cnt_sel, int* cnt_unb, float* tokens_acc, float* rsum, float* margin, int S,
-                               cudaStream_t stream) {
+                               int* cnt_sel, int* cnt_unb, float* tokens_acc, float* rsum, float* margin, float* part,
+                               int S, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (K > 32 || K > E || num_groups > 32) return -1;
   if (num_groups > 1 && (E % num_groups != 0 || group_topk <= 0 || K % group_topk != 0 || K / group_topk > 8))
@@ -403,15 +461,20 @@ extern "C" int b200_router_fwd(const float* logits, const float* bias, float* sc
   st.tokens_acc = tokens_acc;
   st.rsum = rsum;
   st.margin = margin;
+  st.part = part;
   st.S = S > 0 ? S : T;
   st.separate_unb = (bias != nullptr || num_groups > 1) ? 1 : 0;
+  st.tpw = b200_router_tokens_per_block(E) / ROUTER_WARPS;
   if (!st.separate_unb && cnt_unb != nullptr && cnt_unb != cnt_sel) return -1;  // identical by construction
-  const size_t smem = (static_cast<size_t>(ROUTER_WARPS) * (E + 32) + 2 * static_cast<size_t>(E)) * sizeof(float);
+  const int block_tokens = ROUTER_WARPS * st.tpw;
+  if (part != nullptr && (rsum == nullptr || st.S % block_tokens != 0)) return -1;
+  const size_t smem = (static_cast<size_t>(ROUTER_WARPS) * (E + 32) + 2 * static_cast<size_t>(E) +
+                       (part != nullptr ? static_cast<size_t>(ROUTER_WARPS) * 2 * E : 0)) * sizeof(float);
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return -1;
     cudaFuncSetAttribute(router_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   }
-  router_fwd_kernel<<<router_fwd_grid(T), ROUTER_WARPS * 32, smem, stream>>>(
+  router_fwd_kernel<<<(T + block_tokens - 1) / block_tokens, ROUTER_WARPS * 32, smem, stream>>>(
       logits, bias, scores, topk_w, topk_idx, T, E, K, mode, norm, scale, num_groups, group_topk, st);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -421,6 +484,13 @@ extern "C" int b200_router_colsum(const float* scores, const float* rsum, int B,
   if (B <= 0 || S <= 0 || E <= 0) return 0;
   if (pn != nullptr && rsum == nullptr) return -1;
   router_colsum_kernel<<<dim3((E + 31) / 32, B), 256, 0, stream>>>(scores, rsum, S, E, psum, pn);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_router_part_reduce(const float* part, int B, int blocks_per_seq, int E, float* psum, float* pn,
+                                       cudaStream_t stream) {
+  if (B <= 0 || blocks_per_seq <= 0 || E <= 0) return -1;
+  router_part_reduce_kernel<<<dim3((E + 31) / 32, B), 1024, 0, stream>>>(part, blocks_per_seq, E, psum, pn);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

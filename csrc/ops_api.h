@@ -30,7 +30,13 @@ int b200_qknorm_rope_bwd(const void* dq, const void* dk, const void* dv, const v
 // for both when there is neither bias nor group-limited routing), tokens_acc float [E], rsum / margin float [T].
 int b200_router_fwd(const float* logits, const float* bias, float* scores, float* topk_w, int* topk_idx, int T, int E,
                     int K, int mode, int norm, float scale, int num_groups, int group_topk, int* cnt_sel,
-                    int* cnt_unb, float* tokens_acc, float* rsum, float* margin, int S, cudaStream_t stream);
+                    int* cnt_unb, float* tokens_acc, float* rsum, float* margin, float* part, int S,
+                    cudaStream_t stream);
+// consecutive tokens one block of b200_router_fwd covers (its `part` output has one [2, E] row per block)
+int b200_router_tokens_per_block(int E);
+// per-sequence sums of the per-block partials: psum / pn [B, E]
+int b200_router_part_reduce(const float* part, int B, int blocks_per_seq, int E, float* psum, float* pn,
+                            cudaStream_t stream);
 // per-sequence column sums of the scores (psum) and of the row-normalised scores (pn, optional), [B, E]
 int b200_router_colsum(const float* scores, const float* rsum, int B, int S, int E, float* psum, float* pn,
                        cudaStream_t stream);
@@ -70,6 +76,7 @@ int b200_dlogits(void* logits, long long ld, const float* lse, const long long* 
                  const float* loss_acc, float upstream, cudaStream_t stream);
 int b200_embed_fwd(const long long* ids, const void* table, int T, int H, int V, void* out, cudaStream_t stream);
 int b200_embed_sort_capacity();  // tokens the built-in key sort handles
+int b200_embed_sort(const long long* ids, int T, int V, unsigned long long* keys, cudaStream_t stream);
 // deterministic: (id, position) keys are sorted (here, or by the caller: presorted) and every id's rows are
 // added in position order by one warp; keys = uint64[T] scratch
 int b200_embed_bwd(const long long* ids, const void* dout, int T, int H, int V, float* grad,

@@ -76,7 +76,24 @@ class EmbeddingFn(torch.autograd.Function):
         table = w16(weight)
         flat = ids.reshape(-1).contiguous()
         out = torch.empty(flat.numel(), table.shape[1], dtype=BF16, device=table.device)
-        ext().embed_fwd(flat, table, out)
+        e = ext()
+        e.embed_fwd(flat, table, out)
+        ctx.sorted = None
+        n = flat.numel()
+        if ctx.needs_input_grad[1] and n <= e.embed_sort_capacity():
+            # the backward pass needs the (id, position) keys sorted; the ids are known now, so the one-block
+            # sort runs on a side stream under the forward pass instead of in the tail of backward
+            dev = flat.device
+            main, side = torch.cuda.current_stream(dev), _side_stream(dev)
+            keys = torch.empty(n, dtype=torch.int64, device=dev)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            done = torch.cuda.Event()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                e.embed_sort(flat, table.shape[0], keys)
+                done.record(side)
+            ctx.sorted = (keys, done)  # kept alive until backward has waited for `done` on the main stream
         ctx.save_for_backward(flat)
         ctx.weight = weight
         ctx.shape = tuple(ids.shape)
@@ -92,7 +109,11 @@ class EmbeddingFn(torch.autograd.Function):
             tgt.zero_()
         n = flat.numel()
         # deterministic: (id, position) keys are sorted and each id's rows are added in position order
-        if n <= e.embed_sort_capacity():
+        if ctx.sorted is not None:
+            keys, done = ctx.sorted
+            torch.cuda.current_stream(flat.device).wait_event(done)
+            presorted = True
+        elif n <= e.embed_sort_capacity():
             keys = _scratch("embed_keys", n, torch.int64, flat.device)
             presorted = False
         else:  # beyond the single-block sort: library radix sort of the same keys
@@ -479,10 +500,19 @@ class RouterFn(torch.autograd.Function):
         b = bias.detach().float().contiguous() if bias is not None else None
         e = ext()
         if site is not None and collect:
-            e.router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
-                         int(group_topk or 0), site.cnt_sel, site.cnt_unb, tokens_acc, site.rsum, site.margin,
-                         site.S)
-            e.router_colsum(scores, site.rsum, site.S, site.psum, site.pn)
+            bt = e.router_tokens_per_block(E)
+            if site.S % bt == 0:  # a block never straddles two sequences: per-block partial sums, reduced below
+                nblk = T // bt
+                part = _scratch("router_part", nblk * 2 * E, torch.float32, x2.device)
+                e.router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
+                             int(group_topk or 0), site.cnt_sel, site.cnt_unb, tokens_acc, site.rsum, site.margin,
+                             part, site.S)
+                e.router_part_reduce(part, site.S // bt, site.psum, site.pn)
+            else:
+                e.router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
+                             int(group_topk or 0), site.cnt_sel, site.cnt_unb, tokens_acc, site.rsum, site.margin,
+                             None, site.S)
+                e.router_colsum(scores, site.rsum, site.S, site.psum, site.pn)
         else:
             e.router_fwd(logits, b, scores, tw, ti, K, mode, bool(norm), float(scale), int(num_groups or 0),
                          int(group_topk or 0))
@@ -682,7 +712,10 @@ def moe_experts(x, topk_idx, topk_w, gate_up, down):
 
 # --------------------------------------------------- fused linear + cross entropy
 LCE_CHUNK_ROWS = int(os.environ.get("MOE_B200_LCE_CHUNK", "4096"))
-LCE_OVERLAP = os.environ.get("MOE_B200_LCE_OVERLAP", "1") != "0"
+# Measured on a B200 under the power cap: running the memory-bound softmax-gradient pass of chunk c beside the
+# vocabulary GEMM of chunk c + 1 does not shorten the sequence (both draw on the same power budget), so the
+# second logits buffer it needs is not spent by default.
+LCE_OVERLAP = os.environ.get("MOE_B200_LCE_OVERLAP", "0") != "0"
 _SIDE_STREAMS: dict = {}
 
 

@@ -271,7 +271,7 @@ def test_embedding(dev, n_tok):
 
 
 @pytest.mark.parametrize("mtype,E,K,groups,B,S", [("softmax", 16, 4, None, 4, 128), ("sigmoid", 64, 4, (8, 4), 2, 256),
-                                                   ("sigmoid", 32, 2, None, 3, 96)])
+                                                   ("sigmoid", 32, 2, None, 3, 96), ("softmax", 16, 4, None, 2, 100)])
 def test_router_statistics_and_balance_losses(dev, mtype, E, K, groups, B, S):
     """The router kernels' statistics against the plain-PyTorch losses: counts, Switch loss, sequence-level
     loss, margins, and the gradient both losses send into the router weight."""
