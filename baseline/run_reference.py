@@ -50,12 +50,22 @@ def _build(cfg: dict, ref_dir: str):
         model = GlobalMoEForCausalLM(config)
     else:
         raise ValueError(f"reference arm: model type {m['type']} not wired")
+    # the reference's own selection (`train.py:241-245`): grouped_mm, and `eager` when that raises; what ran and
+    # why is recorded, together with the class that actually computes the experts (Liger replaces HF's)
     impl = "grouped_mm"
     try:
         model.set_experts_implementation("grouped_mm")
-    except Exception:
-        model.set_experts_implementation("eager")
-        impl = "eager"
+    except Exception as e:
+        impl = f"eager (grouped_mm raised {e!r})"
+        try:
+            model.set_experts_implementation("eager")
+        except Exception as e2:
+            impl += f"; eager raised {e2!r}"
+    inner = getattr(model, "model", model)
+    bank = getattr(inner, "global_experts", None)
+    if bank is None:
+        bank = inner.layers[0].mlp.experts
+    impl += f", experts module {type(bank).__module__}.{type(bank).__name__}"
     t = cfg["training"]
     tcfg = TrainingConfig(
         learning_rate=t["learning_rate"], weight_decay=t["weight_decay"], beta1=t.get("beta1", 0.9),
@@ -124,7 +134,8 @@ def run(args, root, dist_setup, timed_region, make_batches, load_bench_config) -
                             f"(accelerate is not in this image) + reference AdamW/LR/clip, bf16 autocast"},
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tok/s", "ms_per_step": ms_e2e / K,
                 "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
-        "gpu_launches": 0, "clocks": clocks, "loss_last": float(last["loss"].item()), "loss_e2e_last": losses[-1],
+        "gpu_launches": None,  # kernels of this repository: none run in this arm (not counted, not zero by measurement)
+        "clocks": clocks, "loss_last": float(last["loss"].item()), "loss_e2e_last": losses[-1],
         # rank 0's loss of every end-to-end step (same synthetic token stream in both arms)
         "losses_e2e": [round(x, 4) for x in losses[:256]],
     }
