@@ -44,6 +44,12 @@ def parse_args():
                     help="replicate Adam moments and the update on every rank (default for N > 1: sharded, ZeRO-1)")
     ap.add_argument("--fsdp", action="store_true",
                     help="shard parameters, gradients and optimizer state (ZeRO-3) instead of ZeRO-1")
+    ap.add_argument("--stub-comm", action="store_true",
+                    help="measurement aid: every rank talks to its own buffers (no NVLink traffic, no waits); "
+                         "step time minus this run's step time is the exposed communication")
+    ap.add_argument("--timeline", action="store_true",
+                    help="after the timed regions: one more eager step with CUDA-event marks around the bucket "
+                         "reduces, AdamW and the parameter barrier on every rank (printed under `timeline`)")
     ap.add_argument("--layers", type=int, default=None, help="override num_hidden_layers (shape debugging only)")
     ap.add_argument("--checkpoint", action="store_true", help="recompute each decoder layer in backward")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly (no whole-step CUDA graph)")
@@ -178,6 +184,8 @@ def run_ours(args) -> dict:
     from moe_b200.trainer import Trainer
     from moe_b200.utils.training import TrainingConfig
 
+    if args.stub_comm:
+        os.environ["MOE_B200_COMM_STUB"] = "1"
     rank, local, world = dist_setup(args.gpus)
     cfg = load_bench_config(args.config, args.batch, args.seq)
     if args.checkpoint:
@@ -226,6 +234,25 @@ def run_ours(args) -> dict:
 
     ms_e2e, clocks_e2e = timed_region(step_e2e, K, world, local)
     G.check_status()
+    timeline = None
+    if args.timeline:
+        import torch.distributed as dist
+
+        trainer.use_graph = False
+        b = host[W]
+        trainer.train_step({"input_ids": b, "labels": b})  # eager path warm
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        trainer.engine.start_timeline()
+        trainer.train_step({"input_ids": b, "labels": b})
+        mine = trainer.engine.timeline_report()
+        gathered = [None] * world
+        if world > 1:
+            dist.all_gather_object(gathered, mine)
+        else:
+            gathered = [mine]
+        timeline = {f"rank{r}": t for r, t in enumerate(gathered)}
     tokens = B * S * world * K
     value = tokens / (ms / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
@@ -249,6 +276,7 @@ def run_ours(args) -> dict:
         "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / K, "h2d_bytes_per_step": B * S * 8,
                 "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
         "gpu_launches": launches, "clocks": clocks, "loss_last": loss_dev, "loss_e2e_last": losses[-1],
+        **({"comm_stubbed": True} if args.stub_comm else {}), **({"timeline": timeline} if timeline else {}),
         # rank 0's loss of every end-to-end step (same synthetic token stream in both arms)
         "losses_e2e": [round(x, 4) for x in losses[:256]],
     }

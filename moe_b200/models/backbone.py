@@ -18,6 +18,7 @@ import torch.nn as nn
 from torch.utils.checkpoint import checkpoint
 
 from .. import ops
+from ..utils.profiling import phase
 from .config import Qwen3Config, Qwen3MoeConfig
 from .router import DeepSeekRouter, TopKRouter, recompute_guard
 
@@ -157,11 +158,14 @@ class DecoderLayer(nn.Module):
 
     def forward(self, h, y, next_norm: RMSNorm, global_experts=None):
         """`h`: residual stream, `y = input_layernorm(h)`.  Returns (h', next_norm(h'), router scores)."""
-        a = self.self_attn(y)
-        h, y = ops.add_rmsnorm(a, h, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon)
-        ops.set_moe_site(self.mlp, global_experts, self.layer_idx)
-        m, scores = self.mlp(y, global_experts)
-        h, y = ops.add_rmsnorm(m, h, next_norm.weight, next_norm.variance_epsilon)
+        with phase("attn"):
+            a = self.self_attn(y)
+            h, y = ops.add_rmsnorm(a, h, self.post_attention_layernorm.weight,
+                                   self.post_attention_layernorm.variance_epsilon)
+        with phase("moe"):
+            ops.set_moe_site(self.mlp, global_experts, self.layer_idx)
+            m, scores = self.mlp(y, global_experts)
+            h, y = ops.add_rmsnorm(m, h, next_norm.weight, next_norm.variance_epsilon)
         return h, y, scores
 
 

@@ -13,6 +13,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..ops.oracle import shift_labels
+from ..utils.profiling import phase
 from .backbone import DecoderModel, Linear, init_weights_
 from .config import GlobalMoEConfig, Qwen3Config, Qwen3MoeConfig
 from .load_balancing import load_balancing_loss_func, seq_load_balancing_loss_func
@@ -113,8 +114,9 @@ class _CausalLM(nn.Module):
             out.hidden_states = hidden
         if labels is not None:
             tgt = shift_labels(labels)
-            ce = ops.linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), self.lm_head.weight, tgt.reshape(-1),
-                                          -100, loss_scale)
+            with phase("lce"):
+                ce = ops.linear_cross_entropy(hidden.reshape(-1, hidden.shape[-1]), self.lm_head.weight,
+                                              tgt.reshape(-1), -100, loss_scale)
             out.ce_loss = ce
             out.loss = ce
         if labels is None or kwargs.get("return_logits"):

@@ -25,6 +25,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..ops import oracle
+from ..utils.profiling import phase
 
 ALIGN = 64  # elements; keeps every slice 16-byte aligned in bf16 and 256-byte aligned in fp32
 
@@ -185,6 +186,7 @@ class TrainEngine:
         # accumulate locally, the buckets are reduced during the last micro-batch's backward
         # (what `accelerator.accumulate` / DDP `no_sync` do in the reference, `train.py:546`)
         self.accumulating = False
+        self._timeline = None  # list of (label, event) while a device timeline is being recorded
 
     # ------------------------------------------------------------------ set-up helpers
     def _fuse_adjacent(self) -> None:
@@ -308,6 +310,27 @@ class TrainEngine:
             self._launch_reduce(first_offset, hi)
             self._reduced_upto = first_offset
 
+    # ---- device timeline of one step (CUDA events on the streams the work runs on; eager mode only)
+    def start_timeline(self) -> None:
+        self._timeline = []
+        self.mark("step_start")
+
+    def mark(self, label: str, stream=None) -> None:
+        if self._timeline is None or not self.cuda:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(stream if stream is not None else torch.cuda.current_stream(self.device))
+        self._timeline.append((label, ev))
+
+    def timeline_report(self) -> list[tuple[str, float]]:
+        """(label, milliseconds since `step_start`) for every mark, after synchronising the device."""
+        tl, self._timeline = self._timeline or [], None
+        if not tl:
+            return []
+        torch.cuda.synchronize(self.device)
+        t0 = tl[0][1]
+        return [(label, round(t0.elapsed_time(ev), 4)) for label, ev in tl]
+
     def _launch_reduce(self, lo: int, hi: int, final: bool = False) -> None:
         if self.world == 1 or hi <= lo:
             return
@@ -320,7 +343,10 @@ class TrainEngine:
             ev.record()
             with torch.cuda.stream(self._comm_stream):
                 self._comm_stream.wait_event(ev)
-                self._fused_ar.reduce(lo, hi - lo, final, publish=not (self.sharded and hi <= self.decay_end))
+                self.mark(f"reduce[{lo}:{hi}]_start", self._comm_stream)
+                with phase("comm"):
+                    self._fused_ar.reduce(lo, hi - lo, final, publish=not (self.sharded and hi <= self.decay_end))
+                self.mark(f"reduce[{lo}:{hi}]_end", self._comm_stream)
         elif self.cuda:
             ev = torch.cuda.Event()
             ev.record()
@@ -438,7 +464,10 @@ class TrainEngine:
             self.set_hyper(lr)
         elif lr is not None:
             self.lr = lr
-        self.reduce_gradients()
+        self.mark("backward_end")
+        with phase("comm"):
+            self.reduce_gradients()
+        self.mark("reduces_joined")
         if count:
             self.step_count += 1
         b1, b2 = self.betas
@@ -457,8 +486,10 @@ class TrainEngine:
                         None if kind == 2 else self.p16[p_lo:p_hi], self._hyper, b1, b2, self.eps, wd,
                         self._coef_ep if kind == 1 else self._coef,
                         [q + 2 * p_lo for q in self._peers.p16_ptrs] if kind == 2 else [])
+            self.mark("adamw_end")
             if self.sharded:  # every rank's stores into this rank's bf16 copy have landed after this
                 self._fused_ar.param_barrier()
+                self.mark("param_barrier_end")
             self._grad_norm = self._coef[1]
         else:
             norm = self.g32.norm()

@@ -51,6 +51,18 @@ class PeerBuffers:
         self.p16 = None
         self.p16_ptrs: list[int] = []
         dist.barrier(group)
+        # Measurement aid: MOE_B200_COMM_STUB=1 points every "peer" at this rank's own buffers and pre-sets the
+        # flag words, so the same kernels run with the same local work but nothing crosses NVLink and nobody
+        # waits for anybody.  Step time minus the stubbed step time is the exposed communication.  Results of a
+        # stubbed run are not a data-parallel average and must not be trained on.
+        self.stubbed = os.environ.get("MOE_B200_COMM_STUB", "0") == "1"
+        if self.stubbed:
+            self.grad_ptrs = [self.grad_ptrs[self.rank]] * self.world
+            self.flag_ptrs = [self.flag_ptrs[self.rank]] * self.world
+            self.norm_ptrs = [self.norm_ptrs[self.rank]] * self.world
+            self.multicast_ptr = 0
+            self.flags.fill_(1 << 30)
+            torch.cuda.synchronize(device)
 
     def add_param_copy(self, numel: int) -> None:
         """A symmetric bf16 parameter copy: with a sharded optimizer the owner of a slice stores the updated
@@ -63,6 +75,8 @@ class PeerBuffers:
         h = sm.rendezvous(self.p16, self.group)
         self._handles = self._handles + (h,)
         self.p16_ptrs = [int(p) for p in h.buffer_ptrs]
+        if getattr(self, "stubbed", False):
+            self.p16_ptrs = [self.p16_ptrs[self.rank]] * self.world
         dist.barrier(self.group)
 
 

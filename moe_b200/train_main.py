@@ -47,7 +47,8 @@ def parse_args(argv=None):
     p.add_argument("--max_checkpoints", type=int, default=0, help="Checkpoints to keep (0 = all)")
     p.add_argument("--device", default=None, choices=["cpu", "cuda"], help="default: cuda when available")
     p.add_argument("--max_steps", type=int, default=None, help="Override training.max_steps")
-    p.add_argument("--profile", action="store_true", help="NVTX ranges per step phase")
+    p.add_argument("--profile", action="store_true",
+                   help="NVTX ranges per step and per phase (attn, moe, lce, comm); runs eagerly, without the CUDA graph")
     return p.parse_args(argv)
 
 
@@ -187,6 +188,10 @@ def main(argv=None) -> None:
               f"  Precision : {'bf16 compute, fp32 master' if device == 'cuda' else 'fp32'}\n  GPUs      : {world}\n"
               f"{'=' * 60}\n", flush=True)
 
+    if args.profile:
+        from .utils import profiling
+
+        profiling.enable()
     trainer = Trainer(model, tcfg, is_moe=not is_dense, overlap_grad_reduce=pcfg.get("overlap", True),
                       shard_optimizer=shard_opt, shard_params=shard_par, cuda_graph=use_graph)
     trainer.engine.broadcast_parameters(0)
