@@ -230,3 +230,35 @@ def test_sharded_parameter_engine_matches_replicated_engine(mtype, kw, accum, ck
         assert abs(a - b) < 5e-3 * abs(a), (runs[0][0], runs[1][0])
     assert relerr(runs[1][1], runs[0][1]) < 5e-3
     assert abs(runs[0][2] - runs[1][2]) < 2e-2 * runs[0][2]
+
+
+@pytest.mark.parametrize("mtype", ["standard_moe", "deepseek_global_moe"])
+def test_two_runs_are_bitwise_identical(mtype):
+    """Race detector of last resort: nothing on the training path adds floating-point numbers in an order that
+    depends on scheduling (sorted embedding gradient, fixed-order loss / statistics / norm reductions, one
+    writer per gradient tile), so two runs from the same seed on the same data agree bit for bit - weights,
+    loss and gradient norm.  A data race or a float atomic would show up here as a difference."""
+    from moe_b200.models import build_model
+    from moe_b200.ops import gemm as G
+    from moe_b200.trainer import Trainer
+    from moe_b200.utils.training import TrainingConfig
+
+    tcfg = TrainingConfig(learning_rate=2e-3, warmup_steps=2, max_steps=20, batch_size=2, gradient_accumulation=1)
+    torch.manual_seed(0)
+    batches = [torch.randint(0, 2048, (2, 256)) for _ in range(4)]
+    runs = []
+    for _ in range(2):
+        model, _ = build_model(tiny_cfg(mtype, num_hidden_layers=3), seed=1, device="cuda")
+        tr = Trainer(model, tcfg)
+        outs = []
+        for b in batches:
+            r = tr.train_step({"input_ids": b, "labels": b})
+            outs.append((r.loss.clone(), r.grad_norm.clone()))
+        torch.cuda.synchronize()
+        G.check_status()
+        runs.append((tr.engine.p32.clone(), outs, [r.local_tokens_per_expert.clone() for r in model.routers()]))
+    assert torch.equal(runs[0][0], runs[1][0])
+    for (l0, g0), (l1, g1) in zip(runs[0][1], runs[1][1]):
+        assert torch.equal(l0, l1) and torch.equal(g0, g1)
+    for a, b in zip(runs[0][2], runs[1][2]):
+        assert torch.equal(a, b)
