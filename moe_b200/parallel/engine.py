@@ -491,6 +491,8 @@ class TrainEngine:
                 self._fused_ar.param_barrier()
                 self.mark("param_barrier_end")
             self._grad_norm = self._coef[1]
+            if self._peers is not None and getattr(self._peers, "_guard", 0):
+                self._peers.check_canaries()
         else:
             norm = self.g32.norm()
             coef = 1.0

@@ -14,6 +14,7 @@ import torch
 import torch.distributed as dist
 
 MAX_RANKS = 8
+CANARY = 1.2345678e30  # guard-word value of the debug mode
 
 
 class PeerBuffers:
@@ -26,17 +27,24 @@ class PeerBuffers:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if self.world > MAX_RANKS:
             raise ValueError(f"the peer-memory kernels support at most {MAX_RANKS} ranks (one NVLink domain)")
-        self.grad = sm.empty(numel, dtype=torch.float32, device=device)
+        # Debug aid (MOE_B200_DEBUG_CANARY=1): guard words on both sides of the gradient buffer, which peers write
+        # into; `check_canaries()` (called by the engine after every step in that mode) reports an overrun.
+        self._guard = 64 if os.environ.get("MOE_B200_DEBUG_CANARY", "0") == "1" else 0
+        self._grad_full = sm.empty(numel + 2 * self._guard, dtype=torch.float32, device=device)
+        self.grad = self._grad_full[self._guard:self._guard + numel]
         self.flags = sm.empty(4 * MAX_RANKS, dtype=torch.int32, device=device)
         self.norm = sm.empty(MAX_RANKS, dtype=torch.float32, device=device)
-        for t in (self.grad, self.flags, self.norm):
+        for t in (self._grad_full, self.flags, self.norm):
             t.zero_()
+        if self._guard:
+            self._grad_full[:self._guard] = CANARY
+            self._grad_full[-self._guard:] = CANARY
         torch.cuda.synchronize(device)
-        hg = sm.rendezvous(self.grad, group)
+        hg = sm.rendezvous(self._grad_full, group)
         hf = sm.rendezvous(self.flags, group)
         hn = sm.rendezvous(self.norm, group)
         self._handles = (hg, hf, hn)
-        self.grad_ptrs = [int(p) for p in hg.buffer_ptrs]
+        self.grad_ptrs = [int(p) + 4 * self._guard for p in hg.buffer_ptrs]
         self.flag_ptrs = [int(p) for p in hf.buffer_ptrs]
         self.norm_ptrs = [int(p) for p in hn.buffer_ptrs]
         mc = 0
@@ -45,6 +53,8 @@ class PeerBuffers:
                 mc = int(hg.multicast_ptr)
         except Exception:
             mc = int(getattr(hg, "multicast_ptr", 0) or 0)
+        if mc:
+            mc += 4 * self._guard
         # NVLS only on request to opt out: MOE_B200_MULTIMEM=0 forces plain peer loads / stores
         self.multicast_ptr = mc if os.environ.get("MOE_B200_MULTIMEM", "1") != "0" else 0
         self.group = group
@@ -63,6 +73,16 @@ class PeerBuffers:
             self.multicast_ptr = 0
             self.flags.fill_(1 << 30)
             torch.cuda.synchronize(device)
+
+    def check_canaries(self) -> None:
+        """Raises if anything wrote outside the gradient buffer (debug mode only; synchronises)."""
+        if not self._guard:
+            return
+        g = self._guard
+        lo, hi = self._grad_full[:g], self._grad_full[-g:]
+        if not (bool((lo == CANARY).all()) and bool((hi == CANARY).all())):
+            raise RuntimeError("guard words around the symmetric gradient buffer were overwritten "
+                               f"(rank {self.rank}: below {int((lo != CANARY).sum())}, above {int((hi != CANARY).sum())})")
 
     def add_param_copy(self, numel: int) -> None:
         """A symmetric bf16 parameter copy: with a sharded optimizer the owner of a slice stores the updated
