@@ -252,7 +252,8 @@ std::vector<void*> ptrs8(const std::vector<int64_t>& v) {
 void ep_exchange(const Tensor& counts, const std::vector<int64_t>& cmat, const std::vector<int64_t>& flags,
                  const Tensor& epoch_base, int64_t epoch_off, int64_t rank, int64_t world, int64_t E, int64_t H,
                  Tensor& send_base, Tensor& recv_seg_off, Tensor& recv_tile_expert, Tensor& recv_num_m_tiles,
-                 Tensor& recv_buf, Tensor& recv_meta, Tensor& status) {
+                 Tensor& recv_buf, Tensor& recv_meta, Tensor& status, const OptT& recv_pair_tiles,
+                 const OptT& recv_num_pair_tiles) {
   i32c(counts, "counts"); i32c(send_base, "send_base"); i32c(recv_seg_off, "recv_seg_off");
   i32c(recv_tile_expert, "recv_tile_expert"); i32c(recv_num_m_tiles, "recv_num_m_tiles"); bf16c(recv_buf, "recv_buf");
   i32c(recv_meta, "recv_meta"); i32c(epoch_base, "epoch_base");
@@ -262,7 +263,9 @@ void ep_exchange(const Tensor& counts, const std::vector<int64_t>& cmat, const s
                          (int)epoch_off, (int)rank, (int)world, (int)E, (int)H, (int)recv_buf.size(0),
                          send_base.data_ptr<int>(), recv_seg_off.data_ptr<int>(), recv_tile_expert.data_ptr<int>(),
                          recv_num_m_tiles.data_ptr<int>(), recv_buf.data_ptr(), recv_meta.data_ptr<int>(),
-                         status.data_ptr<int>(), 0, stream()), "ep_exchange");
+                         status.data_ptr<int>(), 0, optp<int>(recv_pair_tiles),
+                         recv_pair_tiles.has_value() && recv_pair_tiles->defined() ? (int)(recv_pair_tiles->numel() / 2) : 0,
+                         optp<int>(recv_num_pair_tiles), stream()), "ep_exchange");
 }
 
 void ep_dispatch(const Tensor& rows, const OptT& scale, const Tensor& idx, const Tensor& pos,
@@ -438,7 +441,12 @@ void bind_ops(pybind11::module_& m) {
   m.def("allreduce", &allreduce);
   m.def("peer_barrier", &peer_barrier);
   m.def("allgather_bf16", &allgather_bf16);
-  m.def("ep_exchange", &ep_exchange);
+  m.def("ep_exchange", &ep_exchange, pybind11::arg("counts"), pybind11::arg("cmat"), pybind11::arg("flags"),
+        pybind11::arg("epoch_base"), pybind11::arg("epoch_off"), pybind11::arg("rank"), pybind11::arg("world"),
+        pybind11::arg("E"), pybind11::arg("H"), pybind11::arg("send_base"), pybind11::arg("recv_seg_off"),
+        pybind11::arg("recv_tile_expert"), pybind11::arg("recv_num_m_tiles"), pybind11::arg("recv_buf"),
+        pybind11::arg("recv_meta"), pybind11::arg("status"), pybind11::arg("recv_pair_tiles") = pybind11::none(),
+        pybind11::arg("recv_num_pair_tiles") = pybind11::none());
   m.def("ep_dispatch", &ep_dispatch);
   m.def("clip_coef_multi", &clip_coef_multi);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

@@ -35,7 +35,8 @@ ep_exchange_kernel(const int* __restrict__ counts, EpPeers cmat /* int [W][E] pe
                    int* __restrict__ send_base /* [E] */, int* __restrict__ recv_seg_off /* [El+1] */,
                    int* __restrict__ recv_tile_expert, int* __restrict__ recv_num_m_tiles,
                    __nv_bfloat16* __restrict__ recv_buf, int* __restrict__ recv_meta, int* status,
-                   unsigned long long limit_ns) {
+                   unsigned long long limit_ns, int* __restrict__ recv_pair_tiles, int max_pairs,
+                   int* __restrict__ recv_num_pair_tiles) {
   extern __shared__ int sm[];  // [E] segment offsets of every expert inside its owner's buffer, then [E] totals
   int* seg = sm;
   int* tot = sm + E;
@@ -56,7 +57,10 @@ ep_exchange_kernel(const int* __restrict__ counts, EpPeers cmat /* int [W][E] pe
   }
   __syncthreads();
   if (!ok_s) {
-    if (threadIdx.x == 0) *recv_num_m_tiles = 0;
+    if (threadIdx.x == 0) {
+      *recv_num_m_tiles = 0;
+      if (recv_num_pair_tiles != nullptr) *recv_num_pair_tiles = 0;
+    }
     return;
   }
   const int* cm = reinterpret_cast<const int*>(cmat.p[rank]);
@@ -96,6 +100,19 @@ ep_exchange_kernel(const int* __restrict__ counts, EpPeers cmat /* int [W][E] pe
     recv_seg_off[el] = seg[e];
     const int t0 = seg[e] / 128, t1 = (seg[e] + (tot[e] + 127) / 128 * 128) / 128;
     for (int t = t0; t < t1 && t * 128 < total_rows; ++t) recv_tile_expert[t] = el;
+  }
+  // the same rows as pair tiles for the pair-tile GEMM kernel: two 128-row tiles of one expert, or its last one
+  if (recv_pair_tiles != nullptr && threadIdx.x == 0) {
+    int np = 0;
+    for (int el = 0; el < El && total_rows > 0; ++el) {
+      const int e = rank * El + el;
+      const int t0 = seg[e] / 128, n128 = (tot[e] + 127) / 128;
+      for (int i = 0; 2 * i < n128 && np < max_pairs; ++i, ++np) {
+        recv_pair_tiles[2 * np] = (t0 + 2 * i) * 128;
+        recv_pair_tiles[2 * np + 1] = el | ((2 * i + 2 <= n128 ? 2 : 1) << 16);
+      }
+    }
+    *recv_num_pair_tiles = np;
   }
   // zero the padding rows (they enter the weight-gradient contraction) and mark them as sourceless
   const int nch = H >> 3;
@@ -175,7 +192,8 @@ static EpPeers to_peers(void* const* p) {
 extern "C" int b200_ep_exchange(const int* counts, void* const* cmat, void* const* flags, int chan, const int* epoch_base,
                                 int epoch_off, int rank, int world, int E, int H, int capacity, int* send_base,
                                 int* recv_seg_off, int* recv_tile_expert, int* recv_num_m_tiles, void* recv_buf,
-                                int* recv_meta, int* status, unsigned long long limit_ns, cudaStream_t stream) {
+                                int* recv_meta, int* status, unsigned long long limit_ns, int* recv_pair_tiles,
+                                int max_pairs, int* recv_num_pair_tiles, cudaStream_t stream) {
   if (world < 1 || world > B200_MAX_RANKS || E % world != 0 || H % 8 != 0 || capacity % 128 != 0) return -1;
   const size_t smem = 2 * static_cast<size_t>(E) * sizeof(int);
   if (smem > 200 * 1024) return -1;
@@ -185,7 +203,7 @@ extern "C" int b200_ep_exchange(const int* counts, void* const* cmat, void* cons
   ep_exchange_kernel<<<1, 1024, smem, stream>>>(counts, to_peers(cmat), to_peers(flags), chan, epoch_base, epoch_off,
                                                 rank, world, E, H, capacity, send_base, recv_seg_off, recv_tile_expert,
                                                 recv_num_m_tiles, reinterpret_cast<__nv_bfloat16*>(recv_buf), recv_meta,
-                                                status, limit_ns);
+                                                status, limit_ns, recv_pair_tiles, max_pairs, recv_num_pair_tiles);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

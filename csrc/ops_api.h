@@ -125,7 +125,8 @@ int b200_allgather_bf16(const void* const* shards, int world, long long per, lon
 int b200_ep_exchange(const int* counts, void* const* cmat, void* const* flags, int chan, const int* epoch_base,
                      int epoch_off, int rank, int world, int E, int H, int capacity, int* send_base, int* recv_seg_off,
                      int* recv_tile_expert, int* recv_num_m_tiles, void* recv_buf, int* recv_meta, int* status,
-                     unsigned long long limit_ns, cudaStream_t stream);
+                     unsigned long long limit_ns, int* recv_pair_tiles, int max_pairs,
+                     int* recv_num_pair_tiles, cudaStream_t stream);
 int b200_ep_dispatch(const void* rows, const float* scale, const int* idx, const int* pos, const int* local_seg_off,
                      const int* send_base, void* const* recv_buf, void* const* recv_meta, void* const* flags, int chan,
                      const int* epoch_base, int epoch_off, int rank, int world, int E, int n, int K, int H,

@@ -149,21 +149,25 @@ class EPMoEFn(torch.autograd.Function):
         rseg = torch.empty(El + 1, dtype=torch.int32, device=dev)
         rtile = torch.empty(cap // 128, dtype=torch.int32, device=dev)
         rnt = torch.empty(1, dtype=torch.int32, device=dev)
+        # the received rows as pair tiles, for the pair-tile GEMM kernels
+        rpair = torch.empty((cap // 128 + El + 1) // 2, 2, dtype=torch.int32, device=dev)
+        rnp = torch.empty(1, dtype=torch.int32, device=dev)
+        pair = (rpair, rnp)
         e0 = ep.next_epoch()
         e.ep_exchange(plan.counts, ep.cmat.ptrs, ep.flags.ptrs, ep.epoch_base, e0, ep.rank, ep.world, ep.E, H,
-                      send_base, rseg, rtile, rnt, b["xrecv"].t, b["meta"].t, ep.status)
+                      send_base, rseg, rtile, rnt, b["xrecv"].t, b["meta"].t, ep.status, rpair, rnp)
         e1 = ep.next_epoch()
         e.ep_dispatch(x2, None, idx32.view(-1), plan.pos, plan.seg_off, send_base, b["xrecv"].ptrs, b["meta"].ptrs,
                       ep.flags.ptrs, ep.epoch_base, e1, ep.rank, ep.world, ep.E, K, cap, ep.counter)
         act = torch.empty(cap, I, dtype=BF16, device=dev)
         gu = torch.empty(cap, I2, dtype=BF16, device=dev)
-        G.grouped_up_swiglu(b["xrecv"].t, w1, rtile, rnt, act, gu, ep=ep.wait_kw(CH_DISPATCH, e1))
+        G.grouped_up_swiglu(b["xrecv"].t, w1, rtile, rnt, act, gu, ep=ep.wait_kw(CH_DISPATCH, e1), pair=pair)
         e2 = ep.next_epoch()
         G.grouped_nt(act, w2, rtile, rnt, b["yret"].t, scatter=True, ep=ep.scatter_kw(b["yret"].ptrs, b["meta"].t, e2))
         out = torch.empty(T, H, dtype=BF16, device=dev)
         e.moe_combine(b["yret"].t, None, tw, None, out, K, ep.local_flags(CH_RETURN), ep.world, ep.epoch_base, e2,
                       ep.status)
-        ctx.save_for_backward(gu, act, tw, idx32, send_base, rseg, rtile, rnt)
+        ctx.save_for_backward(gu, act, tw, idx32, send_base, rseg, rtile, rnt, rpair, rnp)
         ctx.plan, ctx.ep, ctx.bufs, ctx.key = plan, ep, b, key
         ctx.params, ctx.w = (gate_up, down), (w1, w2)
         ctx.in_shape = tuple(x.shape)
@@ -173,7 +177,7 @@ class EPMoEFn(torch.autograd.Function):
     def backward(ctx, dout):
         from ..ops.functional import BF16, GradSink
 
-        gu, act, tw, idx32, send_base, rseg, rtile, rnt = ctx.saved_tensors
+        gu, act, tw, idx32, send_base, rseg, rtile, rnt, rpair, rnp = ctx.saved_tensors
         ep, b, plan = ctx.ep, ctx.bufs, ctx.plan
         e = ep.ext
         w1, w2 = ctx.w
@@ -192,7 +196,8 @@ class EPMoEFn(torch.autograd.Function):
         e.ep_dispatch(d2, tw.view(-1), idx32.view(-1), plan.pos, plan.seg_off, send_base, bb["dyrecv"].ptrs,
                       b["meta"].ptrs, ep.flags.ptrs, ep.epoch_base, e3, ep.rank, ep.world, ep.E, K, cap, ep.counter)
         dgu = torch.empty_like(gu)
-        G.grouped_nn_swiglu_bwd(bb["dyrecv"].t, w2, rtile, rnt, gu, dgu, ep=ep.wait_kw(CH_DISPATCH, e3))
+        G.grouped_nn_swiglu_bwd(bb["dyrecv"].t, w2, rtile, rnt, gu, dgu, ep=ep.wait_kw(CH_DISPATCH, e3),
+                                pair=(rpair, rnp))
         s2 = GradSink(down)
         t2, b2 = s2.target()
         G.grouped_tn(bb["dyrecv"].t, act, rseg, t2, beta=b2)

@@ -23,8 +23,9 @@ def relerr(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
+@pytest.mark.parametrize("use_pair", [True, False])
 @pytest.mark.parametrize("W,T,H,I,E,K", [(2, 300, 256, 128, 8, 2), (4, 512, 128, 256, 16, 4), (8, 64, 128, 64, 32, 2)])
-def test_emulated_ranks_forward_matches_whole_bank(W, T, H, I, E, K):
+def test_emulated_ranks_forward_matches_whole_bank(W, T, H, I, E, K, use_pair):
     from moe_b200 import ops
     from moe_b200.ops import _ext
     from moe_b200.ops import gemm as G
@@ -57,10 +58,12 @@ def test_emulated_ranks_forward_matches_whole_bank(W, T, H, I, E, K):
     rseg = [torch.empty(El + 1, dtype=torch.int32, device=dev) for _ in range(W)]
     rtile = [torch.zeros(cap // 128, dtype=torch.int32, device=dev) for _ in range(W)]
     rnt = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(W)]
+    rpair = [torch.zeros((cap // 128 + El + 1) // 2, 2, dtype=torch.int32, device=dev) for _ in range(W)]
+    rnp = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(W)]
     for _ in range(2):  # second round: every count matrix is complete
         for r in range(W):
             e.ep_exchange(plans[r].counts, ptr(cmat), ptr(flags), epoch, 0, r, W, E, H, send_base[r], rseg[r], rtile[r],
-                          rnt[r], xrecv[r], meta[r], status)
+                          rnt[r], xrecv[r], meta[r], status, rpair[r], rnp[r])
     for r in range(W):
         e.ep_dispatch(xs[r], None, idx[r].view(-1), plans[r].pos, plans[r].seg_off, send_base[r], ptr(xrecv), ptr(meta),
                       ptr(flags), epoch, 1, r, W, E, K, cap, counter)
@@ -70,7 +73,8 @@ def test_emulated_ranks_forward_matches_whole_bank(W, T, H, I, E, K):
         w1, w2 = gu16[r * El:(r + 1) * El].contiguous(), dn16[r * El:(r + 1) * El].contiguous()
         G.grouped_up_swiglu(xrecv[r], w1, rtile[r], rnt[r], act, pre,
                             ep=dict(ep_wait_flags=flags[r][CH_DISPATCH * MAXR:(CH_DISPATCH + 1) * MAXR], ep_wait_n=W,
-                                    ep_epoch_base=epoch, ep_wait_epoch_off=1))
+                                    ep_epoch_base=epoch, ep_wait_epoch_off=1),
+                            pair=(rpair[r], rnp[r]) if use_pair else None)
         G.grouped_nt(act, w2, rtile[r], rnt[r], yret[r], scatter=True,
                      ep=dict(ep_scatter_dst=ptr(yret), ep_scatter_meta=meta[r], ep_post_flags=ptr(flags),
                              ep_post_index=CH_RETURN * MAXR + r, ep_post_epoch_off=2, ep_world=W, ep_counter=gcounter,
