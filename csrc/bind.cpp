@@ -35,7 +35,7 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
              const std::vector<int64_t>& ep_scatter_dst, const OptT& ep_scatter_meta,
              const std::vector<int64_t>& ep_post_flags, int64_t ep_post_index, int64_t ep_post_epoch_off,
              int64_t ep_world, const OptT& ep_counter, int64_t cta2, const OptT& pair_tiles,
-             int64_t ep_limit_ns) {
+             int64_t ep_limit_ns, const OptT& a_gather, const OptT& b_gather) {
   check_cuda(A, "A");
   check_cuda(B, "B");
   check_cuda(C, "C");
@@ -68,6 +68,11 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
   d.ep_world = (int)ep_world;
   d.ep_counter = ptr_or_null<int>(ep_counter);
   d.ep_limit_ns = (unsigned long long)ep_limit_ns;
+  d.a_gather = ptr_or_null<const int>(a_gather);
+  d.b_gather = ptr_or_null<const int>(b_gather);
+  if (d.a_gather != nullptr)
+    TORCH_CHECK(a_gather->scalar_type() == at::kInt && a_gather->numel() >= M, "a_gather: int32, one entry per A row");
+  if (d.b_gather != nullptr) TORCH_CHECK(b_gather->scalar_type() == at::kInt, "b_gather must be int32");
   d.cta2 = (int)cta2;
   d.pair_tiles = ptr_or_null<const int>(pair_tiles);
   d.max_pair_tiles = pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0;
@@ -93,6 +98,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("ep_scatter_dst") = std::vector<int64_t>(), py::arg("ep_scatter_meta") = py::none(),
         py::arg("ep_post_flags") = std::vector<int64_t>(), py::arg("ep_post_index") = 0,
         py::arg("ep_post_epoch_off") = 0, py::arg("ep_world") = 0, py::arg("ep_counter") = py::none(),
-        py::arg("cta2") = 0, py::arg("pair_tiles") = py::none(), py::arg("ep_limit_ns") = 0);
+        py::arg("cta2") = 0, py::arg("pair_tiles") = py::none(), py::arg("ep_limit_ns") = 0,
+        py::arg("a_gather") = py::none(), py::arg("b_gather") = py::none());
   bind_ops(m);
 }

@@ -204,7 +204,7 @@ void router_bwd(const OptT& dscores, const Tensor& dtopk_w, const Tensor& scores
 int64_t moe_plan_blocks(int64_t n) { return b200_moe_plan_blocks((int)n); }
 void moe_plan(const Tensor& idx, int64_t E, Tensor& scratch, Tensor& counts, Tensor& seg_off, Tensor& tile_expert,
               Tensor& num_m_tiles, Tensor& pos, Tensor& row_slot, const OptT& pair_tiles,
-              const OptT& num_pair_tiles) {
+              const OptT& num_pair_tiles, const OptT& row_tok, int64_t K) {
   i32c(idx, "idx"); i32c(scratch, "scratch"); i32c(counts, "counts"); i32c(seg_off, "seg_off");
   i32c(tile_expert, "tile_expert"); i32c(num_m_tiles, "num_m_tiles"); i32c(pos, "pos"); i32c(row_slot, "row_slot");
   c10::cuda::CUDAGuard g(idx.device());
@@ -217,7 +217,7 @@ void moe_plan(const Tensor& idx, int64_t E, Tensor& scratch, Tensor& counts, Ten
                       seg_off.data_ptr<int>(), tile_expert.data_ptr<int>(), num_m_tiles.data_ptr<int>(),
                       pos.data_ptr<int>(), row_slot.data_ptr<int>(), cap, optp<int>(pair_tiles),
                       pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0,
-                      optp<int>(num_pair_tiles), stream()), "moe_plan");
+                      optp<int>(num_pair_tiles), optp<int>(row_tok), (int)K, stream()), "moe_plan");
 }
 void moe_slot_dot(const Tensor& dout, const Tensor& y, int64_t K, Tensor& dw) {
   bf16c(dout, "dout"); bf16c(y, "y"); f32c(dw, "dw");
@@ -480,7 +480,8 @@ void bind_ops(pybind11::module_& m) {
   m.def("moe_plan", &moe_plan, pybind11::arg("idx"), pybind11::arg("E"), pybind11::arg("scratch"),
         pybind11::arg("counts"), pybind11::arg("seg_off"), pybind11::arg("tile_expert"), pybind11::arg("num_m_tiles"),
         pybind11::arg("pos"), pybind11::arg("row_slot"), pybind11::arg("pair_tiles") = pybind11::none(),
-        pybind11::arg("num_pair_tiles") = pybind11::none());
+        pybind11::arg("num_pair_tiles") = pybind11::none(), pybind11::arg("row_tok") = pybind11::none(),
+        pybind11::arg("K") = 1);
   m.def("moe_gather", &moe_gather);
   m.def("moe_slot_dot", &moe_slot_dot);
   m.def("moe_combine", &moe_combine);

@@ -279,6 +279,16 @@ __device__ __forceinline__ void tma2_load_3d(void* dst, const CUtensorMap* map, 
       "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Four rows of a 2-D tensor (row indices r0..r3, `box` columns starting at column x) into four consecutive
+// 128-byte-pitch rows of shared memory; rows outside the tensor read as zeros.  The map has a {box, 1} box.
+__device__ __forceinline__ void tma2_gather4(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x,
+                                             int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], "
+      "[%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t* smem_result, uint32_t ncols) {  // one full warp in each CTA
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
                "r"(ncols)

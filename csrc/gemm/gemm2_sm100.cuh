@@ -146,7 +146,91 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
   const int first = blockIdx.x >> 1;
   const int step = gridDim.x >> 1;
 
-  if (warp == 0) {
+  if (warp == 0 && (args.a_gather != nullptr || args.b_gather != nullptr)) {
+    // ------------------------------------------------ producer with gathered operand rows (both CTAs)
+    // All 32 lanes issue: a 128-row operand tile is 32 gather4 copies of four rows each, one per lane.
+    const uint32_t full0 = mapa_shared(smem_u32(&bar_full[0]), 0);
+    constexpr int OOB = 0x7f7f7f7f;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    if (args.ep.wait_flags != nullptr && first < total) {
+      if (lane == 0) {
+        const int epoch = *args.ep.epoch_base + args.ep.wait_epoch_off;
+        for (int r = 0; r < args.ep.wait_n && ok; ++r) ok = wait_flag_ge(args.ep.wait_flags + r, epoch, args.ep.limit_ns);
+        if (!ok) report(args.status, ST_TIMEOUT_PEER);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    for (int t = first; t < total && ok; t += step) {
+      Tile2 ti;
+      decode_tile2(args, t, m_tiles, n_tiles, ti);
+      const int eb = (args.mode == MODE_GROUPED_K) ? 0 : ti.e;
+      const int n0 = ti.n_idx * BN_OUT;
+      const int am0 = ti.m0 + static_cast<int>(rank) * 128;
+      int4 aidx = make_int4(OOB, OOB, OOB, OOB);
+      if (args.a_gather != nullptr && am0 + lane * 4 + 3 < args.M)
+        aidx = *reinterpret_cast<const int4*>(args.a_gather + am0 + lane * 4);
+      for (int kb = 0; kb < ti.num_kb; ++kb) {
+        if (!mbar_wait(&bar_empty[stage], phase ^ 1u)) {
+          if (lane == 0) report(args.status, ST_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        if (leader && lane == 0) mbar_expect_tx(&bar_full[stage], 2 * Cfg::STAGE_BYTES);
+        const uint32_t fb = full0 + static_cast<uint32_t>(stage) * 8u;
+        uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
+        uint8_t* sb = sa + Cfg::A_BYTES;
+        const int kk = ti.k0 + kb * GEMM_BK;
+        if (args.a_gather != nullptr) {  // K-major A: 128 rows of 64 contraction elements
+          tma2_gather4(sa + lane * 512, &mapA, fb, kk, aidx.x, aidx.y, aidx.z, aidx.w);
+        } else if (lane == 0) {
+          if constexpr (!A_MN) {
+            tma2_load_2d(sa, &mapA, fb, kk, am0);
+          } else {
+            tma2_load_2d(sa, &mapA, fb, am0, kk);
+            tma2_load_2d(sa + 8192, &mapA, fb, am0 + 64, kk);
+          }
+        }
+        if (args.b_gather != nullptr) {
+          // MN-major B: BH / 64 sub-tiles of 64 contraction rows x 64 columns; 16 lanes per sub-tile
+          if constexpr (B_MN && BH == 128) {
+            const int j = lane >> 4, l16 = lane & 15;
+            const int4 bidx = *reinterpret_cast<const int4*>(args.b_gather + kk + l16 * 4);
+            tma2_gather4(sb + j * 8192 + l16 * 512, &mapB, fb, n0 + static_cast<int>(rank) * BH + 64 * j, bidx.x,
+                         bidx.y, bidx.z, bidx.w);
+          }
+        } else if (lane == 0) {
+          if constexpr (!B_MN) {
+            int brow;
+            if constexpr (EPI == EPI_SWIGLU) {
+              brow = leader ? n0 : args.n_half + n0;
+            } else {
+              brow = n0 + static_cast<int>(rank) * BH;
+            }
+            tma2_load_3d(sb, &mapB, fb, kk, brow, eb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BH / 64; ++j)
+              tma2_load_3d(sb + j * 8192, &mapB, fb, n0 + static_cast<int>(rank) * BH + 64 * j, kk, eb);
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    for (int i = 0; i < STAGES; ++i) {
+      (void)mbar_wait(&bar_empty[stage], phase ^ 1u);
+      if (++stage == STAGES) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)
     if (lane == 0) {
       const uint32_t full0 = mapa_shared(smem_u32(&bar_full[0]), 0);  // the even CTA's bar_full[0]

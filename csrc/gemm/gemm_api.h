@@ -35,6 +35,12 @@ typedef struct B200GemmDesc {
   // num_m_tiles then holds the number of pair tiles
   const int* pair_tiles;
   int max_pair_tiles;
+  // pair-tile kernel: fetch operand rows by index with TMA gather.  a_gather: A (K-major) is then the SOURCE
+  // tensor [a_rows, a_inner] and a_gather[r] names the source row of output row r; b_gather: B (MN-major,
+  // grouped by contraction) is the source tensor [b_rows, b_inner] and b_gather[k] the source row of contraction
+  // row k.  Indices outside the source give zero rows.
+  const int* a_gather;
+  const int* b_gather;
   void* C;
   long long ldc, c_expert_stride;
   void* aux0;

@@ -190,6 +190,9 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   a.seg_off = d->seg_off;
   a.pair_tiles = d->pair_tiles;
   a.max_pair_tiles = d->max_pair_tiles;
+  a.a_gather = d->a_gather;
+  a.b_gather = d->b_gather;
+  if ((a.a_gather || a.b_gather) && !d->cta2) return -23;
   a.C = d->C; a.ldc = d->ldc; a.c_expert_stride = d->c_expert_stride;
   a.aux0 = d->aux0; a.ld_aux0 = d->ld_aux0;
   a.aux1 = d->aux1; a.ld_aux1 = d->ld_aux1;
@@ -214,7 +217,12 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   CUtensorMap ma, mb;
   int rc;
   // A: 2-D. K-major: dims {K, rows}; MN-major: dims {M extent, contraction rows}.
-  rc = make_map(&ma, d->A, d->a_inner, d->a_rows, 0, static_cast<uint64_t>(d->lda) * 2, 0, 64, d->a_mn ? 64 : 128);
+  if (d->a_gather != nullptr) {
+    if (d->a_mn) return -23;
+    rc = make_map(&ma, d->A, d->a_inner, d->a_rows, 0, static_cast<uint64_t>(d->lda) * 2, 0, 64, 1);  // gather box
+  } else {
+    rc = make_map(&ma, d->A, d->a_inner, d->a_rows, 0, static_cast<uint64_t>(d->lda) * 2, 0, 64, d->a_mn ? 64 : 128);
+  }
   if (rc) return rc;
   if (d->cta2) {
     // ---- pair-tile kernel: each CTA loads bn/2 rows (or columns) of B; C and the SwiGLU side tensors
@@ -222,10 +230,15 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
     if (bn != 256 && bn != 128) return -20;
     if (d->epi == EPI_BF16_SCATTER) return -21;
     if (d->mode == MODE_GROUPED_M && (d->pair_tiles == nullptr || d->max_pair_tiles <= 0)) return -22;
-    rc = make_map(&mb, d->B, d->b_inner, d->b_rows, d->b_experts > 0 ? d->b_experts : 1,
-                  static_cast<uint64_t>(d->ldb) * 2,
-                  static_cast<uint64_t>(d->b_expert_stride > 0 ? d->b_expert_stride : d->ldb * (long long)d->b_rows) * 2,
-                  64, d->b_mn ? 64u : static_cast<uint32_t>(bn / 2));
+    if (d->b_gather != nullptr) {
+      if (!d->b_mn || bn != 256 || d->mode != MODE_GROUPED_K) return -23;
+      rc = make_map(&mb, d->B, d->b_inner, d->b_rows, 0, static_cast<uint64_t>(d->ldb) * 2, 0, 64, 1);  // gather box
+    } else {
+      rc = make_map(&mb, d->B, d->b_inner, d->b_rows, d->b_experts > 0 ? d->b_experts : 1,
+                    static_cast<uint64_t>(d->ldb) * 2,
+                    static_cast<uint64_t>(d->b_expert_stride > 0 ? d->b_expert_stride : d->ldb * (long long)d->b_rows) * 2,
+                    64, d->b_mn ? 64u : static_cast<uint32_t>(bn / 2));
+    }
     if (rc) return rc - 3;
     CUtensorMap mc, mx;
     const bool f32 = d->epi == EPI_F32;

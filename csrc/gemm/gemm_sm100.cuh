@@ -55,6 +55,11 @@ struct GemmArgs {
   const int* seg_off;      // grouped_k: [E+1] padded row offsets (multiples of 128)
   const int* pair_tiles;   // grouped_m, pair-tile kernel: per tile (first row, expert | live halves << 16)
   int max_pair_tiles;      // capacity of pair_tiles; num_m_tiles then counts pair tiles
+  // pair-tile kernel: operand rows fetched by index (TMA gather) instead of from a materialised sorted copy.
+  // a_gather[r] = source row of A row r (K-major A); b_gather[k] = source row of contraction row k (MN-major B,
+  // grouped by contraction).  An index outside the source tensor gives a zero row.
+  const int* a_gather;
+  const int* b_gather;
   void* C;
   long long ldc;
   long long c_expert_stride;  // grouped_k: elements between experts in C

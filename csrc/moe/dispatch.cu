@@ -136,7 +136,7 @@ __global__ void plan_scan_kernel(int* __restrict__ block_hist, int nblocks, int 
 // One warp per chunk walks its entries in order; rank within (chunk, expert) from match/popc.
 __global__ void plan_scatter_kernel(const int* __restrict__ idx, int n, int E, const int* __restrict__ block_off,
                                     const int* __restrict__ seg_off, int* __restrict__ pos,
-                                    int* __restrict__ row_slot, int capacity) {
+                                    int* __restrict__ row_slot, int capacity, int* __restrict__ row_tok, int K) {
   extern __shared__ int cnt[];  // [E] running count inside this chunk
   const int lane = threadIdx.x;
   for (int e = lane; e < E; e += 32) cnt[e] = 0;
@@ -161,6 +161,7 @@ __global__ void plan_scatter_kernel(const int* __restrict__ idx, int n, int E, c
       if (p < capacity) {
         pos[g] = p;
         row_slot[p] = g;
+        if (row_tok != nullptr) row_tok[p] = g / K;
       } else {
         pos[g] = -1;
       }
@@ -328,7 +329,7 @@ extern "C" int b200_moe_plan_blocks(int n) { return (n + PLAN_CHUNK - 1) / PLAN_
 // scratch: int32[plan_blocks(n) * E].  row_slot must hold `capacity` ints; it is reset to -1 here.
 extern "C" int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* seg_off, int* tile_expert,
                              int* num_m_tiles, int* pos, int* row_slot, int capacity, int* pair_tiles, int max_pairs,
-                             int* num_pair_tiles, cudaStream_t stream) {
+                             int* num_pair_tiles, int* row_tok, int K, cudaStream_t stream) {
   if (n <= 0 || E <= 0 || E > 65535 || capacity % 128 != 0) return -1;
   const size_t scan_sm = (3 * static_cast<size_t>(E) + 2) * sizeof(int);
   if (static_cast<size_t>(E) * sizeof(int) > 48 * 1024 || scan_sm > 200 * 1024) return -1;
@@ -343,11 +344,14 @@ extern "C" int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* co
   const int nb = b200_moe_plan_blocks(n);
   const size_t sm = static_cast<size_t>(E) * sizeof(int);
   cudaMemsetAsync(row_slot, 0xff, static_cast<size_t>(capacity) * sizeof(int), stream);
+  // source token of every sorted row, for operand gathers; padding rows keep an index outside any tensor
+  if (row_tok != nullptr) cudaMemsetAsync(row_tok, 0x7f, static_cast<size_t>(capacity) * sizeof(int), stream);
   plan_hist_kernel<<<nb, 256, sm, stream>>>(idx, n, E, scratch);
   plan_scan_kernel<<<1, 1024, scan_sm, stream>>>(
       scratch, nb, E, counts, seg_off, tile_expert, capacity / 128, num_m_tiles, pair_tiles, max_pairs,
       num_pair_tiles);
-  plan_scatter_kernel<<<nb, 32, sm, stream>>>(idx, n, E, scratch, seg_off, pos, row_slot, capacity);
+  plan_scatter_kernel<<<nb, 32, sm, stream>>>(idx, n, E, scratch, seg_off, pos, row_slot, capacity, row_tok,
+                                              K > 0 ? K : 1);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

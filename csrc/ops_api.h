@@ -51,10 +51,11 @@ int b200_router_bwd(const float* dscores, const float* dtopk_w, const float* sco
 
 // ---- moe/dispatch.cu
 int b200_moe_plan_blocks(int n);  // plan scratch: int[blocks * E]
-// pair_tiles (optional): int2 per pair tile for the pair-tile GEMM kernel, capacity max_pairs
+// pair_tiles (optional): int2 per pair tile for the pair-tile GEMM kernel, capacity max_pairs;
+// row_tok (optional): int[capacity], source token (assignment / K) of every sorted row, 0x7f7f7f7f for padding
 int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* seg_off, int* tile_expert,
                   int* num_m_tiles, int* pos, int* row_slot, int capacity, int* pair_tiles, int max_pairs,
-                  int* num_pair_tiles, cudaStream_t stream);
+                  int* num_pair_tiles, int* row_tok, int K, cudaStream_t stream);
 // dw[t * K + k] = <dout[t], y[t * K + k]> (bf16 rows of H elements)
 int b200_moe_slot_dot(const void* dout, const void* y, int T, int K, int H, float* dw, cudaStream_t stream);
 int b200_moe_gather(const void* x, const int* row_slot, const int* seg_off, int E, int K, int H, void* xs,

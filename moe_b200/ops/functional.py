@@ -636,9 +636,11 @@ class MoEPlan:
         self.pair_tiles = torch.empty((self.cap // 128 + E + 1) // 2, 2, dtype=torch.int32, device=dev)
         self.num_pair_tiles = torch.empty(1, dtype=torch.int32, device=dev)
         self.pair = (self.pair_tiles, self.num_pair_tiles)
+        # source token of every sorted row (an index outside any tensor for padding rows): operand gathers
+        self.row_tok = torch.empty(self.cap, dtype=torch.int32, device=dev)
         scratch = _scratch("moe_plan", e.moe_plan_blocks(n) * E, torch.int32, dev)
         e.moe_plan(idx32.reshape(-1), E, scratch, self.counts, self.seg_off, self.tile_expert, self.num_m_tiles,
-                   self.pos, self.row_slot, self.pair_tiles, self.num_pair_tiles)
+                   self.pos, self.row_slot, self.pair_tiles, self.num_pair_tiles, self.row_tok, K)
 
 
 class MoEExpertsFn(torch.autograd.Function):
@@ -657,16 +659,23 @@ class MoEExpertsFn(torch.autograd.Function):
         tw = topk_w.reshape(T, K).float().contiguous()
         plan = MoEPlan(idx32, E)
         cap, dev = plan.cap, x2.device
-        xs = torch.empty(cap, H, dtype=BF16, device=dev)
-        e.moe_gather(x2, plan.row_slot, plan.seg_off, E, K, xs)
         act = torch.empty(cap, I, dtype=BF16, device=dev)
         gu = torch.empty(cap, I2, dtype=BF16, device=dev)
-        G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair)
+        gathered = G.gather_supported(H, I2)
+        if gathered:  # dispatch = the A-operand load: the kernel fetches token rows by index, no sorted copy
+            xs = x2
+            G.grouped_up_swiglu(x2, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair,
+                                gather=plan.row_tok)
+        else:
+            xs = torch.empty(cap, H, dtype=BF16, device=dev)
+            e.moe_gather(x2, plan.row_slot, plan.seg_off, E, K, xs)
+            G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair)
         ys = torch.empty(cap, H, dtype=BF16, device=dev)
         G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys, pair=plan.pair)
         out = torch.empty(T, H, dtype=BF16, device=dev)
         e.moe_combine(ys, plan.pos, tw, None, out, K, None, 0, None, 0, None)
         ctx.save_for_backward(xs, gu, act, ys, tw)
+        ctx.gathered = gathered
         ctx.plan = plan
         ctx.params = (gate_up, down)
         ctx.w = (w1, w2)
@@ -682,7 +691,7 @@ class MoEExpertsFn(torch.autograd.Function):
         w1, w2 = ctx.w
         gate_up, down = ctx.params
         T, K, E, cap = plan.T, plan.K, plan.E, plan.cap
-        H = xs.shape[1]
+        H = xs.shape[1]  # `xs` is the unsorted [T, H] activation when the operand rows are gathered by index
         dev = xs.device
         d2 = dout.reshape(T, H)
         if d2.dtype != BF16:
@@ -700,7 +709,7 @@ class MoEExpertsFn(torch.autograd.Function):
         G.grouped_nn(dgu, w1, plan.tile_expert, plan.num_m_tiles, dxs, pair=plan.pair)
         s1 = GradSink(gate_up)
         t1, b1 = s1.target()
-        G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1)
+        G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1, b_gather=plan.row_tok if ctx.gathered else None)
         dx = torch.empty(T, H, dtype=BF16, device=dev)
         e.moe_combine(dxs, plan.pos, None, None, dx, K, None, 0, None, 0, None)
         return dx.view(ctx.in_shape), dw.view(T, K), None, s1.done(t1), s2.done(t2)
