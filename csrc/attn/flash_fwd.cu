@@ -32,10 +32,6 @@ namespace b200 {
 constexpr int FA_THREADS = 320;
 constexpr int FA_TILE = 32768;   // 128 x 128 bf16
 constexpr int FA_RING = 5;       // K/V slots
-#ifndef FA_POLY_PAIRS
-#define FA_POLY_PAIRS 0           // of every four pairs of exponentials, how many run on the FMA pipe (measured
-                                  // at B=8, S=2048, 16/8 heads: 0 -> 0.148 ms, 1 -> 0.151, 2 -> 0.158, 3 -> 0.171)
-#endif
 constexpr int FA_EXTRA = 256;    // barriers
 constexpr int FA_SMEM = 232448;  // everything a CTA may have; the seven tiles alone take 224 KB
 constexpr unsigned long long FA_LIMIT_NS = 2000000000ull;  // nothing here waits on another GPU
@@ -45,7 +41,7 @@ struct FaFwdArgs {
   float* lse;
   int B, S, nh, nkv;
   int items;
-  float scale_log2, inv_scale_log2;
+  float scale_log2;
   int* status;
 };
 
@@ -352,7 +348,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         // pass 2: exponentials -> P as bf16 pairs over the first 64 columns of this row's scores.  Columns
         // [32 hh, 32 hh + 32) are written after score columns [64 hh, 64 hh + 64) have been read.
         const float mb = m_ref * sl2;
-        const float s_min = m_ref - 126.0f * args.inv_scale_log2;  // scores below it would underflow 2^-126
         float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
         uint64_t acc2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
@@ -389,25 +384,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
               for (int i = 0; i < 4; ++i) pk[c8 * 4 + i] = pack_bf16x2(p[2 * i], p[2 * i + 1]);
             }
           } else {
-            // two values per issue slot (f32x2) for the scale and the sums: this loop is bound by issue
-            // slots (0.158 -> 0.148 ms).  FA_POLY_PAIRS of every four pairs could take a polynomial exp2 on
-            // the FMA pipe instead of the XU pipe; every share measured slower than none
+            // two values per issue slot (f32x2) for the scale and the sums: this loop is bound by issue slots
             const uint64_t sl2_2 = pack2(sl2, sl2), nmb2 = pack2(-mb, -mb);
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                float lo = __uint_as_float(r[c8 * 8 + 2 * k]), hi = __uint_as_float(r[c8 * 8 + 2 * k + 1]);
-                uint64_t p2;
-                if (k >= 4 - FA_POLY_PAIRS) {
-                  lo = fmaxf(lo, s_min);
-                  hi = fmaxf(hi, s_min);
-                  p2 = ex2_poly2(fma2(pack2(lo, hi), sl2_2, nmb2));
-                } else {
-                  float xl, xh;
-                  unpack2(fma2(pack2(lo, hi), sl2_2, nmb2), xl, xh);
-                  p2 = pack2(ex2_approx(xl), ex2_approx(xh));
-                }
+                const float lo = __uint_as_float(r[c8 * 8 + 2 * k]), hi = __uint_as_float(r[c8 * 8 + 2 * k + 1]);
+                float xl, xh;
+                unpack2(fma2(pack2(lo, hi), sl2_2, nmb2), xl, xh);
+                const uint64_t p2 = pack2(ex2_approx(xl), ex2_approx(xh));
                 acc2[k] = add2(acc2[k], p2);
                 float pl, ph;
                 unpack2(p2, pl, ph);
@@ -497,7 +483,6 @@ extern "C" int b200_flash_fwd(const void* q, const void* k, const void* v, void*
   a.B = B; a.S = S; a.nh = nh; a.nkv = nkv;
   a.items = B * (nh / 2) * (S / 128);
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
-  a.inv_scale_log2 = 1.0f / a.scale_log2;
   a.status = status;
   const int grid = a.items < sms ? a.items : sms;
   flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(mq, mk, mv, a);

@@ -35,7 +35,8 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
              const std::vector<int64_t>& ep_scatter_dst, const OptT& ep_scatter_meta,
              const std::vector<int64_t>& ep_post_flags, int64_t ep_post_index, int64_t ep_post_epoch_off,
              int64_t ep_world, const OptT& ep_counter, int64_t cta2, const OptT& pair_tiles,
-             int64_t ep_limit_ns, const OptT& a_gather, const OptT& b_gather) {
+             int64_t ep_limit_ns, const OptT& a_gather, const OptT& b_gather, const OptT& row_slot,
+             const OptT& row_w, const OptT& row_dot) {
   check_cuda(A, "A");
   check_cuda(B, "B");
   check_cuda(C, "C");
@@ -71,8 +72,16 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
   d.a_gather = ptr_or_null<const int>(a_gather);
   d.b_gather = ptr_or_null<const int>(b_gather);
   if (d.a_gather != nullptr)
-    TORCH_CHECK(a_gather->scalar_type() == at::kInt && a_gather->numel() >= M, "a_gather: int32, one entry per A row");
+    TORCH_CHECK(a_gather->scalar_type() == at::kInt && (mode == 2 || a_gather->numel() >= M),
+                "a_gather: int32, one entry per A row");
   if (d.b_gather != nullptr) TORCH_CHECK(b_gather->scalar_type() == at::kInt, "b_gather must be int32");
+  d.row_slot = ptr_or_null<const int>(row_slot);
+  d.row_w = ptr_or_null<const float>(row_w);
+  d.row_dot = ptr_or_null<float>(row_dot);
+  if (d.row_slot != nullptr)
+    TORCH_CHECK(row_slot->scalar_type() == at::kInt && row_slot->numel() >= M, "row_slot: int32, one entry per row");
+  if (d.row_w != nullptr) TORCH_CHECK(row_w->scalar_type() == at::kFloat, "row_w must be fp32");
+  if (d.row_dot != nullptr) TORCH_CHECK(row_dot->scalar_type() == at::kFloat, "row_dot must be fp32");
   d.cta2 = (int)cta2;
   d.pair_tiles = ptr_or_null<const int>(pair_tiles);
   d.max_pair_tiles = pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0;
@@ -99,6 +108,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("ep_post_flags") = std::vector<int64_t>(), py::arg("ep_post_index") = 0,
         py::arg("ep_post_epoch_off") = 0, py::arg("ep_world") = 0, py::arg("ep_counter") = py::none(),
         py::arg("cta2") = 0, py::arg("pair_tiles") = py::none(), py::arg("ep_limit_ns") = 0,
-        py::arg("a_gather") = py::none(), py::arg("b_gather") = py::none());
+        py::arg("a_gather") = py::none(), py::arg("b_gather") = py::none(), py::arg("row_slot") = py::none(),
+        py::arg("row_w") = py::none(), py::arg("row_dot") = py::none());
   bind_ops(m);
 }

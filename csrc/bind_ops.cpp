@@ -219,6 +219,15 @@ void moe_plan(const Tensor& idx, int64_t E, Tensor& scratch, Tensor& counts, Ten
                       pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0,
                       optp<int>(num_pair_tiles), optp<int>(row_tok), (int)K, stream()), "moe_plan");
 }
+void moe_row_dot_reduce(const Tensor& row_dot, const Tensor& row_slot, const Tensor& seg_off, int64_t E, Tensor& dw) {
+  f32c(row_dot, "row_dot"); i32c(row_slot, "row_slot"); i32c(seg_off, "seg_off"); f32c(dw, "dw");
+  const int cap = (int)row_slot.numel();
+  need(row_dot.numel() % cap == 0 && row_dot.numel() >= cap, "row_dot must be [capacity, n_tiles]");
+  c10::cuda::CUDAGuard g(row_dot.device());
+  rc_ok(b200_moe_row_dot_reduce(row_dot.data_ptr<float>(), row_slot.data_ptr<int>(), seg_off.data_ptr<int>(), (int)E,
+                                (int)(row_dot.numel() / cap), cap, dw.data_ptr<float>(), stream()),
+        "moe_row_dot_reduce");
+}
 void moe_slot_dot(const Tensor& dout, const Tensor& y, int64_t K, Tensor& dw) {
   bf16c(dout, "dout"); bf16c(y, "y"); f32c(dw, "dw");
   const int T = (int)dout.size(0), H = (int)dout.size(1);
@@ -484,6 +493,7 @@ void bind_ops(pybind11::module_& m) {
         pybind11::arg("K") = 1);
   m.def("moe_gather", &moe_gather);
   m.def("moe_slot_dot", &moe_slot_dot);
+  m.def("moe_row_dot_reduce", &moe_row_dot_reduce);
   m.def("moe_combine", &moe_combine);
   m.def("moe_combine_bwd", &moe_combine_bwd);
   m.def("lse_loss", &lse_loss);

@@ -407,21 +407,6 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-// ex2_poly for two values at once (inputs must be >= -126)
-__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x) {
-  const uint64_t magic = pack2(12582912.0f, 12582912.0f), nmagic = pack2(-12582912.0f, -12582912.0f);
-  const uint64_t t = add2(x, magic);
-  const uint64_t n = add2(t, nmagic);
-  const uint64_t f = fma2(n, pack2(-1.0f, -1.0f), x);
-  uint64_t p = fma2(pack2(0.05500893f, 0.05500893f), f, pack2(0.24221096f, 0.24221096f));
-  p = fma2(p, f, pack2(0.69328293f, 0.69328293f));
-  p = fma2(p, f, pack2(1.0f, 1.0f));
-  float plo, phi, tlo, thi;
-  unpack2(p, plo, phi);
-  unpack2(t, tlo, thi);
-  return pack2(__int_as_float(__float_as_int(plo) + (__float_as_int(tlo) << 23)),
-               __int_as_float(__float_as_int(phi) + (__float_as_int(thi) << 23)));
-}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

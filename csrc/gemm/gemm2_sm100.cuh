@@ -170,8 +170,10 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
       const int n0 = ti.n_idx * BN_OUT;
       const int am0 = ti.m0 + static_cast<int>(rank) * 128;
       int4 aidx = make_int4(OOB, OOB, OOB, OOB);
-      if (args.a_gather != nullptr && am0 + lane * 4 + 3 < args.M)
-        aidx = *reinterpret_cast<const int4*>(args.a_gather + am0 + lane * 4);
+      if constexpr (!A_MN) {
+        if (args.a_gather != nullptr && am0 + lane * 4 + 3 < args.M)
+          aidx = *reinterpret_cast<const int4*>(args.a_gather + am0 + lane * 4);
+      }
       for (int kb = 0; kb < ti.num_kb; ++kb) {
         if (!mbar_wait(&bar_empty[stage], phase ^ 1u)) {
           if (lane == 0) report(args.status, ST_TIMEOUT_PRODUCER);
@@ -183,8 +185,14 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
         uint8_t* sb = sa + Cfg::A_BYTES;
         const int kk = ti.k0 + kb * GEMM_BK;
-        if (args.a_gather != nullptr) {  // K-major A: 128 rows of 64 contraction elements
-          tma2_gather4(sa + lane * 512, &mapA, fb, kk, aidx.x, aidx.y, aidx.z, aidx.w);
+        if (args.a_gather != nullptr) {
+          if constexpr (!A_MN) {  // K-major A: 128 rows of 64 contraction elements, rows named by output row
+            tma2_gather4(sa + lane * 512, &mapA, fb, kk, aidx.x, aidx.y, aidx.z, aidx.w);
+          } else {  // MN-major A: two sub-tiles of 64 contraction rows x 64 columns, rows named by contraction row
+            const int j = lane >> 4, l16 = lane & 15;
+            const int4 kidx = *reinterpret_cast<const int4*>(args.a_gather + kk + l16 * 4);
+            tma2_gather4(sa + j * 8192 + l16 * 512, &mapA, fb, am0 + 64 * j, kidx.x, kidx.y, kidx.z, kidx.w);
+          }
         } else if (lane == 0) {
           if constexpr (!A_MN) {
             tma2_load_2d(sa, &mapA, fb, kk, am0);
@@ -512,6 +520,14 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
       } else if constexpr (EPI == EPI_SWIGLU) {
         // accumulator columns [0, BN/2) = gate, [BN/2, BN) = up, for output columns n0 .. n0+BN/2.
         // Three staging buffers (activation, gate, up) are filled over two 32-column halves.
+        float wr = 1.f;  // routing weight of this lane's row, folded into the stored activation when given
+        if (args.row_w != nullptr) {
+          wr = 0.f;
+          if (row_ok) {
+            const int sl = args.row_slot[row_g];
+            if (sl >= 0) wr = args.row_w[sl];
+          }
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / 128; ++c) {
           const int cbase = n0 + c * 64;
@@ -538,7 +554,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                 // activation from the bf16-rounded pre-activations, so that backward sees the same values
                 const float2 gf = unpack_bf16x2(pg[i]);
                 const float2 uf = unpack_bf16x2(pu[i]);
-                pa[i] = pack_bf16x2(gf.x * sigmoidf_fast(gf.x) * uf.x, gf.y * sigmoidf_fast(gf.y) * uf.y);
+                pa[i] = pack_bf16x2(wr * gf.x * sigmoidf_fast(gf.x) * uf.x, wr * gf.y * sigmoidf_fast(gf.y) * uf.y);
               }
               if (live) {
                 stage_write(ring, lane, h * 4 + j, make_uint4(pa[0], pa[1], pa[2], pa[3]));
@@ -562,6 +578,14 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         // ring layout of this warp: [buffer 0: gate, up][buffer 1: gate, up][out: d gate, d up]
         uint8_t* outb = ring + 16384;
         bool ok_in = true;
+        float wr = 1.f, rdot = 0.f;
+        if (args.row_w != nullptr) {
+          wr = 0.f;
+          if (row_ok) {
+            const int sl = args.row_slot[row_g];
+            if (sl >= 0) wr = args.row_w[sl];
+          }
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / 64 && ok_in; ++c) {
           const int cbase = n0 + c * 64;
@@ -606,9 +630,13 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                 for (int i = 0; i < 4; ++i) {
                   const float2 gf = unpack_bf16x2(gw[i]);
                   const float2 uf = unpack_bf16x2(uw[i]);
-                  const float d0 = __uint_as_float(r[8 * j + 2 * i]);
-                  const float d1 = __uint_as_float(r[8 * j + 2 * i + 1]);
+                  float d0 = __uint_as_float(r[8 * j + 2 * i]);
+                  float d1 = __uint_as_float(r[8 * j + 2 * i + 1]);
                   const float s0 = sigmoidf_fast(gf.x), s1 = sigmoidf_fast(gf.y);
+                  // gradient of the routing weight: <d(weighted activation), activation> (columns < N only)
+                  if (col0 + 8 * j + 2 * i < args.N) rdot += d0 * gf.x * s0 * uf.x + d1 * gf.y * s1 * uf.y;
+                  d0 *= wr;
+                  d1 *= wr;
                   og[i] = pack_bf16x2(d0 * uf.x * s0 * (1.f + gf.x * (1.f - s0)),
                                       d1 * uf.y * s1 * (1.f + gf.y * (1.f - s1)));
                   ou[i] = pack_bf16x2(d0 * gf.x * s0, d1 * gf.y * s1);
@@ -629,6 +657,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             in_buf ^= 1;
           }
         }
+        if (args.row_dot != nullptr && row_ok) args.row_dot[row_g * n_tiles + ti.n_idx] = rdot;
       }
       tc_fence_before();
       __syncwarp();

@@ -41,6 +41,11 @@ typedef struct B200GemmDesc {
   // row k.  Indices outside the source give zero rows.
   const int* a_gather;
   const int* b_gather;
+  // pair-tile SwiGLU epilogues: fold the routing weight row_w[row_slot[r]] of sorted row r into the stored
+  // activation (forward) / the incoming gradient (backward, which also writes row_dot[r * n_tiles + n])
+  const int* row_slot;
+  const float* row_w;
+  float* row_dot;
   void* C;
   long long ldc, c_expert_stride;
   void* aux0;

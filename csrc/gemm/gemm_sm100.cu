@@ -192,7 +192,11 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   a.max_pair_tiles = d->max_pair_tiles;
   a.a_gather = d->a_gather;
   a.b_gather = d->b_gather;
-  if ((a.a_gather || a.b_gather) && !d->cta2) return -23;
+  a.row_slot = d->row_slot;
+  a.row_w = d->row_w;
+  a.row_dot = d->row_dot;
+  if ((a.a_gather || a.b_gather || a.row_w || a.row_dot) && !d->cta2) return -23;
+  if ((a.row_w != nullptr) != (a.row_slot != nullptr)) return -23;
   a.C = d->C; a.ldc = d->ldc; a.c_expert_stride = d->c_expert_stride;
   a.aux0 = d->aux0; a.ld_aux0 = d->ld_aux0;
   a.aux1 = d->aux1; a.ld_aux1 = d->ld_aux1;
@@ -218,7 +222,7 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   int rc;
   // A: 2-D. K-major: dims {K, rows}; MN-major: dims {M extent, contraction rows}.
   if (d->a_gather != nullptr) {
-    if (d->a_mn) return -23;
+    if (d->a_mn && d->mode != MODE_GROUPED_K) return -23;
     rc = make_map(&ma, d->A, d->a_inner, d->a_rows, 0, static_cast<uint64_t>(d->lda) * 2, 0, 64, 1);  // gather box
   } else {
     rc = make_map(&ma, d->A, d->a_inner, d->a_rows, 0, static_cast<uint64_t>(d->lda) * 2, 0, 64, d->a_mn ? 64 : 128);

@@ -60,6 +60,14 @@ struct GemmArgs {
   // grouped by contraction).  An index outside the source tensor gives a zero row.
   const int* a_gather;
   const int* b_gather;
+  // pair-tile SwiGLU epilogues, optional routing-weight folding: the weight of sorted row r is
+  // row_w[row_slot[r]] (0 for padding rows, row_slot < 0).  Forward: the stored activation is multiplied by it
+  // (so the down projection yields weighted expert outputs and the combine is a plain sum).  Backward: the
+  // incoming d(weighted activation) is multiplied by it, and row_dot[r * n_tiles + n] receives this tile's part
+  // of <d(weighted activation)[r], activation[r]> = the gradient of the routing weight.
+  const int* row_slot;
+  const float* row_w;
+  float* row_dot;
   void* C;
   long long ldc;
   long long c_expert_stride;  // grouped_k: elements between experts in C

@@ -310,9 +310,31 @@ __global__ void moe_slot_dot_kernel(const __nv_bfloat16* __restrict__ dout, cons
   }
 }
 
+// dw[slot(r)] = sum over the n_tiles partial dot products the SwiGLU-backward epilogue left for sorted row r.
+__global__ void moe_row_dot_reduce_kernel(const float* __restrict__ row_dot, const int* __restrict__ row_slot,
+                                          const int* __restrict__ seg_off, int E, int n_tiles, int capacity,
+                                          float* __restrict__ dw) {
+  int live = seg_off[E];
+  if (live > capacity) live = capacity;
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < live; r += gridDim.x * blockDim.x) {
+    const int s = row_slot[r];
+    if (s < 0) continue;
+    float a = 0.f;
+    for (int n = 0; n < n_tiles; ++n) a += row_dot[static_cast<size_t>(r) * n_tiles + n];
+    dw[s] = a;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_moe_row_dot_reduce(const float* row_dot, const int* row_slot, const int* seg_off, int E,
+                                       int n_tiles, int capacity, float* dw, cudaStream_t stream) {
+  if (n_tiles <= 0 || capacity <= 0) return -1;
+  moe_row_dot_reduce_kernel<<<296, 256, 0, stream>>>(row_dot, row_slot, seg_off, E, n_tiles, capacity, dw);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 extern "C" int b200_moe_slot_dot(const void* dout, const void* y, int T, int K, int H, float* dw, cudaStream_t stream) {
   if (H % 8 != 0) return -1;

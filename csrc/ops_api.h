@@ -56,6 +56,9 @@ int b200_moe_plan_blocks(int n);  // plan scratch: int[blocks * E]
 int b200_moe_plan(const int* idx, int n, int E, int* scratch, int* counts, int* seg_off, int* tile_expert,
                   int* num_m_tiles, int* pos, int* row_slot, int capacity, int* pair_tiles, int max_pairs,
                   int* num_pair_tiles, int* row_tok, int K, cudaStream_t stream);
+// dw[row_slot[r]] = sum_n row_dot[r * n_tiles + n] for the live sorted rows (routing-weight gradient)
+int b200_moe_row_dot_reduce(const float* row_dot, const int* row_slot, const int* seg_off, int E, int n_tiles,
+                            int capacity, float* dw, cudaStream_t stream);
 // dw[t * K + k] = <dout[t], y[t * K + k]> (bf16 rows of H elements)
 int b200_moe_slot_dot(const void* dout, const void* y, int T, int K, int H, float* dw, cudaStream_t stream);
 int b200_moe_gather(const void* x, const int* row_slot, const int* seg_off, int E, int K, int H, void* xs,

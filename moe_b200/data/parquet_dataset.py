@@ -77,7 +77,9 @@ class StatefulParquetDataset(IterableDataset):
         return pd.read_parquet(path, columns=[self.config.text_column])
 
     def _windows(self) -> Iterator[tuple[dict, dict]]:
-        """Yields (sample, state-after-sample)."""
+        """Yields (sample, state-after-sample); at the end of a file (None, state at the start of the next file).
+        `_cur` is only ever assigned by the consumer, so a read-ahead worker cannot move it past what was
+        handed out."""
         seq_len = self.config.seq_len
         eos = self.tokenizer.eos_token_id or 0
         start = self._start
@@ -111,13 +113,14 @@ class StatefulParquetDataset(IterableDataset):
                     del buf[:pos]
             carry = buf
             start = {"file_idx": file_idx + 1, "seq_idx": 0, "buffer": list(carry)}
-            self._cur = dict(start)
+            yield None, dict(start)
 
     def __iter__(self) -> Iterator[dict]:
         if self.config.prefetch <= 0:
             for sample, state in self._windows():
                 self._cur = state
-                yield sample
+                if sample is not None:
+                    yield sample
             return
         q: queue.Queue = queue.Queue(maxsize=self.config.prefetch)
         stop = threading.Event()
@@ -148,6 +151,7 @@ class StatefulParquetDataset(IterableDataset):
                     raise item
                 sample, state = item
                 self._cur = state  # state of the sample handed out, not of what the worker has read ahead
-                yield sample
+                if sample is not None:
+                    yield sample
         finally:
             stop.set()

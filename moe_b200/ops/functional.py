@@ -661,20 +661,28 @@ class MoEExpertsFn(torch.autograd.Function):
         cap, dev = plan.cap, x2.device
         act = torch.empty(cap, I, dtype=BF16, device=dev)
         gu = torch.empty(cap, I2, dtype=BF16, device=dev)
-        gathered = G.gather_supported(H, I2)
-        if gathered:  # dispatch = the A-operand load: the kernel fetches token rows by index, no sorted copy
-            xs = x2
-            G.grouped_up_swiglu(x2, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair,
-                                gather=plan.row_tok)
-        else:
-            xs = torch.empty(cap, H, dtype=BF16, device=dev)
-            e.moe_gather(x2, plan.row_slot, plan.seg_off, E, K, xs)
-            G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair)
+        folded, gathered = G.fold_supported(H, I2), G.gather_supported(H, I2)
         ys = torch.empty(cap, H, dtype=BF16, device=dev)
-        G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys, pair=plan.pair)
         out = torch.empty(T, H, dtype=BF16, device=dev)
-        e.moe_combine(ys, plan.pos, tw, None, out, K, None, 0, None, 0, None)
-        ctx.save_for_backward(xs, gu, act, ys, tw)
+        if gathered:  # dispatch = the A-operand load: the kernel fetches token rows by index, no sorted copy
+            xs, rows = x2, plan.row_tok
+        else:
+            xs, rows = torch.empty(cap, H, dtype=BF16, device=dev), None
+            e.moe_gather(x2, plan.row_slot, plan.seg_off, E, K, xs)
+        if folded:
+            # The routing weight is applied where the activation is stored, so the combine is a plain sum of K
+            # rows and the backward needs neither the expert outputs nor a weighted scatter of the gradient.
+            G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair,
+                                gather=rows, row_slot=plan.row_slot, row_w=tw.view(-1))
+            G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys, pair=plan.pair)
+            e.moe_combine(ys, plan.pos, None, None, out, K, None, 0, None, 0, None)
+            ctx.save_for_backward(xs, gu, act, tw)
+        else:
+            G.grouped_up_swiglu(xs, w1, plan.tile_expert, plan.num_m_tiles, act, gu, pair=plan.pair)
+            G.grouped_nt(act, w2, plan.tile_expert, plan.num_m_tiles, ys, pair=plan.pair)
+            e.moe_combine(ys, plan.pos, tw, None, out, K, None, 0, None, 0, None)
+            ctx.save_for_backward(xs, gu, act, ys, tw)
+        ctx.folded = folded
         ctx.gathered = gathered
         ctx.plan = plan
         ctx.params = (gate_up, down)
@@ -686,31 +694,56 @@ class MoEExpertsFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         e = ext()
-        xs, gu, act, ys, tw = ctx.saved_tensors
         plan = ctx.plan
         w1, w2 = ctx.w
         gate_up, down = ctx.params
         T, K, E, cap = plan.T, plan.K, plan.E, plan.cap
-        H = xs.shape[1]  # `xs` is the unsorted [T, H] activation when the operand rows are gathered by index
-        dev = xs.device
+        H = ctx.in_shape[-1]
         d2 = dout.reshape(T, H)
         if d2.dtype != BF16:
             d2 = d2.to(BF16)
         d2 = d2.contiguous()
-        dys = torch.empty(cap, H, dtype=BF16, device=dev)
-        dw = torch.zeros(T * K, dtype=torch.float32, device=dev)
-        e.moe_combine_bwd(d2, ys, plan.row_slot, plan.seg_off, tw.view(-1), E, K, dys, dw)
-        dgu = torch.empty_like(gu)
-        G.grouped_nn_swiglu_bwd(dys, w2, plan.tile_expert, plan.num_m_tiles, gu, dgu, pair=plan.pair)
+        dev = d2.device
         s2 = GradSink(down)
         t2, b2 = s2.target()
-        G.grouped_tn(dys, act, plan.seg_off, t2, beta=b2)
-        dxs = dys  # reuse: dys is dead after the two GEMMs above
-        G.grouped_nn(dgu, w1, plan.tile_expert, plan.num_m_tiles, dxs, pair=plan.pair)
         s1 = GradSink(gate_up)
         t1, b1 = s1.target()
-        G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1, b_gather=plan.row_tok if ctx.gathered else None)
         dx = torch.empty(T, H, dtype=BF16, device=dev)
+        if ctx.folded:
+            # `act` holds w * silu(g) * u.  d(act) = w * (dout[tok] @ W2) with the SwiGLU backward in the epilogue,
+            # which also leaves <dout[tok] @ W2, silu(g) * u> per row and column tile: the routing-weight gradient.
+            # With gathered operands the output gradient is read in place by token index; otherwise one unweighted
+            # row gather puts it into expert order.
+            xs, gu, act, tw = ctx.saved_tensors
+            I = act.shape[1]
+            rows = plan.row_tok if ctx.gathered else None
+            if ctx.gathered:
+                dys = d2
+                dxs = torch.empty(cap, H, dtype=BF16, device=dev)
+            else:
+                dys = torch.empty(cap, H, dtype=BF16, device=dev)
+                e.moe_gather(d2, plan.row_slot, plan.seg_off, E, K, dys)
+                dxs = dys  # reused once the two GEMMs that read it are done
+            dgu = torch.empty_like(gu)
+            row_dot = torch.empty(cap, (I + 255) // 256, dtype=torch.float32, device=dev)
+            G.grouped_nn_swiglu_bwd(dys, w2, plan.tile_expert, plan.num_m_tiles, gu, dgu, pair=plan.pair,
+                                    gather=rows, row_slot=plan.row_slot, row_w=tw.view(-1), row_dot=row_dot)
+            dw = torch.zeros(T * K, dtype=torch.float32, device=dev)  # slots of dropped rows keep 0
+            e.moe_row_dot_reduce(row_dot, plan.row_slot, plan.seg_off, E, dw)
+            G.grouped_tn(dys, act, plan.seg_off, t2, beta=b2, a_gather=rows)
+            G.grouped_nn(dgu, w1, plan.tile_expert, plan.num_m_tiles, dxs, pair=plan.pair)
+            G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1, b_gather=rows)
+        else:
+            xs, gu, act, ys, tw = ctx.saved_tensors
+            dys = torch.empty(cap, H, dtype=BF16, device=dev)
+            dw = torch.zeros(T * K, dtype=torch.float32, device=dev)
+            e.moe_combine_bwd(d2, ys, plan.row_slot, plan.seg_off, tw.view(-1), E, K, dys, dw)
+            dgu = torch.empty_like(gu)
+            G.grouped_nn_swiglu_bwd(dys, w2, plan.tile_expert, plan.num_m_tiles, gu, dgu, pair=plan.pair)
+            G.grouped_tn(dys, act, plan.seg_off, t2, beta=b2)
+            dxs = dys  # reuse: dys is dead after the two GEMMs above
+            G.grouped_nn(dgu, w1, plan.tile_expert, plan.num_m_tiles, dxs, pair=plan.pair)
+            G.grouped_tn(dgu, xs, plan.seg_off, t1, beta=b1)
         e.moe_combine(dxs, plan.pos, None, None, dx, K, None, 0, None, 0, None)
         return dx.view(ctx.in_shape), dw.view(T, K), None, s1.done(t1), s2.done(t2)
 

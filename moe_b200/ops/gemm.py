@@ -66,12 +66,12 @@ def _pick_bn(n: int) -> int:
 def _launch(*, mode, epi, bn, a_mn, b_mn, M, N, K, A, lda, a_inner, a_rows, B, ldb, b_expert_stride, b_inner,
             b_rows, b_experts, C, ldc, num_experts=1, m_fast=1, beta=0, n_half=0, tile_expert=None,
             num_m_tiles=None, seg_off=None, c_expert_stride=0, aux0=None, ld_aux0=0, aux1=None, ld_aux1=0, ep=None,
-            cta2=0, pair_tiles=None, a_gather=None, b_gather=None):
+            cta2=0, pair_tiles=None, a_gather=None, b_gather=None, row_slot=None, row_w=None, row_dot=None):
     ext = _ext.load()
     ext.gemm(mode, epi, bn, a_mn, b_mn, M, N, K, num_experts, m_fast, beta, n_half, A, lda, a_inner, a_rows, B, ldb,
              b_expert_stride, b_inner, b_rows, b_experts, tile_expert, num_m_tiles, seg_off, C, ldc,
              c_expert_stride, aux0, ld_aux0, aux1, ld_aux1, status_word(A.device), cta2=cta2, pair_tiles=pair_tiles,
-             a_gather=a_gather, b_gather=b_gather, **(ep or {}))
+             a_gather=a_gather, b_gather=b_gather, row_slot=row_slot, row_w=row_w, row_dot=row_dot, **(ep or {}))
 
 
 def _check2d(t: torch.Tensor, name: str) -> None:
@@ -182,15 +182,23 @@ def _pair_kw(pair, N: int) -> dict:
     return dict(cta2=1, pair_tiles=pair[0], num_m_tiles=pair[1], bn=256)
 
 
+def fold_supported(H: int, I2: int) -> bool:
+    """Whether the routing weight can be applied inside the expert GEMMs' epilogues (pair-tile kernels)."""
+    return (pair_tiles_enabled() and I2 > 256 and H > 128 and H % 8 == 0
+            and os.environ.get("MOE_B200_MOE_FOLD", "1") != "0")
+
+
 def gather_supported(H: int, I2: int) -> bool:
-    """Whether the expert GEMMs can fetch token rows by index (TMA gather in the pair-tile kernels) instead of
-    reading a materialised expert-sorted copy of the activations."""
-    return pair_tiles_enabled() and I2 >= 256 and H > 128 and H % 8 == 0 and os.environ.get("MOE_B200_MOE_GATHER", "1") != "0"
+    """Whether the expert GEMMs fetch token rows by index (TMA gather in the pair-tile kernels) instead of
+    reading a materialised expert-sorted copy.  Off unless MOE_B200_MOE_GATHER=1: a `tile::gather4` copy moves
+    four 128-byte rows, and at 32 of them per 16 KB operand tile the copy engine, not the tensor pipe, bounds the
+    main loop (the gathered GEMMs measured 3 to 4 times slower than the same GEMMs on a sorted copy)."""
+    return fold_supported(H, I2) and os.environ.get("MOE_B200_MOE_GATHER", "0") == "1"
 
 
 def grouped_up_swiglu(xs: torch.Tensor, w_gate_up: torch.Tensor, tile_expert: torch.Tensor,
                       num_m_tiles: torch.Tensor, act: torch.Tensor, gu: torch.Tensor, bn: int = 256, ep=None,
-                      pair=None, gather: torch.Tensor | None = None) -> None:
+                      pair=None, gather: torch.Tensor | None = None, row_slot=None, row_w=None) -> None:
     """`xs[R,H]` (expert-sorted, 128-row padded) x `w_gate_up[E,2I,H]` -> `act[R,I]`, pre-activations `gu[R,2I]`.
     With `gather` (int32, one source row per sorted row; pair-tile kernel only) `xs` is the UNSORTED `[T,H]`
     activation and the kernel's producer fetches row `gather[r]` for sorted row r: dispatch is the A-operand load."""
@@ -204,6 +212,8 @@ def grouped_up_swiglu(xs: torch.Tensor, w_gate_up: torch.Tensor, tile_expert: to
         if not kw.get("cta2"):
             raise ValueError("row gather needs the pair-tile kernel")
         kw["a_gather"] = gather
+    if row_w is not None:  # routing weight folded into the stored activation
+        kw.update(row_slot=row_slot, row_w=row_w)
     _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU, a_mn=0, b_mn=0, M=R, N=I, K=H, A=xs, lda=xs.stride(0),
             a_inner=H, a_rows=xs.shape[0], B=w_gate_up, ldb=w_gate_up.stride(1), b_expert_stride=w_gate_up.stride(0),
             b_inner=H, b_rows=I2, b_experts=E, C=act, ldc=act.stride(0), n_half=I, tile_expert=tile_expert,
@@ -241,31 +251,41 @@ def grouped_nn(xs: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, num
 
 def grouped_nn_swiglu_bwd(dy: torch.Tensor, w_down: torch.Tensor, tile_expert: torch.Tensor,
                           num_m_tiles: torch.Tensor, gu: torch.Tensor, dgu: torch.Tensor,
-                          bn: int | None = None, ep=None, pair=None) -> None:
-    """`d(act) = dy[R,H] @ w_down[e][H,I]`, fused with the SwiGLU backward: writes `dgu[R,2I]`."""
-    R, H = dy.shape
+                          bn: int | None = None, ep=None, pair=None, gather: torch.Tensor | None = None,
+                          row_slot=None, row_w=None, row_dot=None) -> None:
+    """`d(act) = dy[R,H] @ w_down[e][H,I]`, fused with the SwiGLU backward: writes `dgu[R,2I]`.  With `gather`
+    `dy` is the unsorted `[T,H]` output gradient and sorted row r reads `dy[gather[r]]`; `row_w` / `row_slot`
+    multiply the incoming gradient by the routing weight and `row_dot [R, ceil(I/256)]` receives the partial
+    dot products that make up the routing-weight gradient."""
+    H = dy.shape[1]
+    R = dgu.shape[0]
     E, _, I = w_down.shape
     kw = dict(bn=bn or (128 if I <= 128 else 256), num_m_tiles=num_m_tiles)
     kw.update(_pair_kw(pair, I if I > 128 else 0))
+    if gather is not None or row_w is not None:
+        if not kw.get("cta2"):
+            raise ValueError("row gather / weight folding need the pair-tile kernel")
+        kw.update(a_gather=gather, row_slot=row_slot, row_w=row_w, row_dot=row_dot)
     _launch(mode=MODE_GROUPED_M, epi=EPI_SWIGLU_BWD, a_mn=0, b_mn=1, M=R, N=I,
-            K=H, A=dy, lda=dy.stride(0), a_inner=H, a_rows=R, B=w_down, ldb=w_down.stride(1),
+            K=H, A=dy, lda=dy.stride(0), a_inner=H, a_rows=dy.shape[0], B=w_down, ldb=w_down.stride(1),
             b_expert_stride=w_down.stride(0), b_inner=I, b_rows=H, b_experts=E, C=dgu, ldc=dgu.stride(0),
             n_half=I, tile_expert=tile_expert, aux0=gu, ld_aux0=gu.stride(0), aux1=dgu,
             ld_aux1=dgu.stride(0), m_fast=0, ep=ep, **kw)
 
 
 def grouped_tn(a: torch.Tensor, b: torch.Tensor, seg_off: torch.Tensor, out: torch.Tensor, beta: int = 0,
-               bn: int | None = None, b_gather: torch.Tensor | None = None) -> None:
+               bn: int | None = None, b_gather: torch.Tensor | None = None,
+               a_gather: torch.Tensor | None = None) -> None:
     """Per-expert weight gradient: `out[e][M,N] (+)= a[seg_e, M]^T @ b[seg_e, N]`, fp32.  With `b_gather` (int32
     per sorted row) `b` is the unsorted `[T,N]` tensor and contraction row k reads `b[b_gather[k]]`."""
     R, M = a.shape
     N = b.shape[1]
     E = out.shape[0]
     pair = _use_pair(M, N, bn) and out.stride(1) % 4 == 0 and out.stride(0) % 4 == 0
-    if b_gather is not None and not (pair and N > 128):
+    if (b_gather is not None and not (pair and N > 128)) or (a_gather is not None and not pair):
         raise ValueError("row gather needs the 256-wide pair-tile kernel")
     _launch(mode=MODE_GROUPED_K, epi=EPI_F32, bn=(128 if N <= 128 else 256) if pair else (bn or (128 if N <= 128 else 256)),
             a_mn=1, b_mn=1, M=M, N=N, K=0,
-            A=a, lda=a.stride(0), a_inner=M, a_rows=R, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N,
+            A=a, lda=a.stride(0), a_inner=M, a_rows=a.shape[0], B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N,
             b_rows=b.shape[0], b_experts=1, C=out, ldc=out.stride(1), c_expert_stride=out.stride(0), num_experts=E,
-            seg_off=seg_off, beta=beta, m_fast=0, cta2=int(pair), b_gather=b_gather)
+            seg_off=seg_off, beta=beta, m_fast=0, cta2=int(pair), b_gather=b_gather, a_gather=a_gather)

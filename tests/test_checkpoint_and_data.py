@@ -229,6 +229,26 @@ def test_parquet_prefetch_thread_same_stream_and_state(parquet_dir):
     assert all(torch.equal(a, b) for a, b in zip(got + rest, base)) and len(got) + len(rest) == len(base)
 
 
+def test_parquet_prefetch_state_at_every_position_including_file_ends(parquet_dir):
+    """With a read-ahead worker the saved position is that of the sample handed out, at every cut: the worker
+    reaching the end of a file (or of all files) while earlier samples still sit in the queue must not move it."""
+    import time
+
+    base = [x["input_ids"] for x in StatefulParquetDataset(DataConfig(data_dir=parquet_dir, seq_len=32), Tok())]
+    for cut in range(1, len(base) + 1):
+        ds = StatefulParquetDataset(DataConfig(data_dir=parquet_dir, seq_len=32, prefetch=2), Tok())
+        it = iter(ds)
+        got = [next(it)["input_ids"] for _ in range(cut)]
+        time.sleep(0.002)  # let the worker run ahead (across a file boundary where one is near)
+        st = json.loads(json.dumps(ds.get_state()))
+        it.close()
+        ds2 = StatefulParquetDataset(DataConfig(data_dir=parquet_dir, seq_len=32), Tok())
+        ds2.set_state(st)
+        rest = [x["input_ids"] for x in ds2]
+        assert len(got) + len(rest) == len(base), cut
+        assert all(torch.equal(a, b) for a, b in zip(got + rest, base)), cut
+
+
 def test_synthetic_stream_is_reproducible_and_rank_dependent():
     a = SyntheticTokenDataset(SyntheticConfig(1000, 8, 3), rank=0)
     b = SyntheticTokenDataset(SyntheticConfig(1000, 8, 3), rank=1)

@@ -155,9 +155,14 @@ def test_router(dev, mode, E, K, groups):
 
 @pytest.mark.parametrize("T,H,I,E,K", [(300, 256, 192, 8, 2), (1024, 512, 256, 16, 4), (64, 128, 64, 32, 8),
                                        (2000, 256, 320, 4, 2)])
-def test_moe_experts(dev, tile_kind, T, H, I, E, K):
+@pytest.mark.parametrize("mode", ["plain", "fold", "gather"])
+def test_moe_experts(dev, tile_kind, monkeypatch, mode, T, H, I, E, K):
+    """plain: weighted combine kernel; fold: routing weight applied in the GEMM epilogues (default where the
+    pair-tile kernels apply); gather: token rows fetched by index inside the GEMMs on top of that."""
     from moe_b200 import ops
 
+    monkeypatch.setenv("MOE_B200_MOE_FOLD", "0" if mode == "plain" else "1")
+    monkeypatch.setenv("MOE_B200_MOE_GATHER", "1" if mode == "gather" else "0")
     torch.manual_seed(5)
     x = _bf(T, H)
     gu = torch.randn(E, 2 * I, H, device=dev) * 0.05
