@@ -64,17 +64,19 @@ __device__ __forceinline__ int fb_sched(int round, int cta, int ctas) {
 }
 
 // ----------------------------------------------------------------------------------------- delta
+template <int HD>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                   float* __restrict__ dsc, int B, int S, int nh, float scale) {
-  // half a warp per (b, s, h): 128 elements, 8 per lane (one 16-byte load from each tensor)
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-  const int l16 = threadIdx.x & 15;
+  // HD / 8 lanes per (b, s, h): 8 elements per lane (one 16-byte load from each tensor)
+  constexpr int LPR = HD / 8;
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / LPR;
+  const int l16 = threadIdx.x & (LPR - 1);
   const long long total = static_cast<long long>(B) * S * nh;
   const bool live = w < total;
   float s = 0.f;
   if (live) {
-    const uint4 a = reinterpret_cast<const uint4*>(o + w * 128)[l16];
-    const uint4 b = reinterpret_cast<const uint4*>(d_o + w * 128)[l16];
+    const uint4 a = reinterpret_cast<const uint4*>(o + w * HD)[l16];
+    const uint4 b = reinterpret_cast<const uint4*>(d_o + w * HD)[l16];
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -84,7 +86,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
     }
   }
 #pragma unroll
-  for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
   if (live && l16 == 0) {
     const long long bs = w / nh;
     const int h = static_cast<int>(w - bs * nh);
@@ -97,6 +99,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 // -------------------------------------------------------------------------------------------- dQ
 constexpr int DQ_RING = 5;
 
+template <int HD>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
@@ -156,6 +159,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   // TMEM columns: S[0] 0, S[1] 128, dP 256, dQ 384
+  constexpr int KC = HD / 64;               // 64-column chunks of a head
+  constexpr int TILE_BYTES = 128 * HD * 2;  // bytes of one Q / dO / K / V tile
   const int group = args.nh / args.nkv;
   const int per_qt = args.B * args.nh;
   const int n_qt = args.S >> 7;
@@ -172,11 +177,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
           ok = false;
           break;
         }
-        mbar_expect_tx(&bar_q_full, 2 * FB_TILE);
-        tma_load_3d(sQ, &mapQ, &bar_q_full, h * 128, qt * 128, b);
-        tma_load_3d(sQ + 16384, &mapQ, &bar_q_full, h * 128 + 64, qt * 128, b);
-        tma_load_3d(sDO, &mapDO, &bar_q_full, h * 128, qt * 128, b);
-        tma_load_3d(sDO + 16384, &mapDO, &bar_q_full, h * 128 + 64, qt * 128, b);
+        mbar_expect_tx(&bar_q_full, 2 * TILE_BYTES);
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc) {
+          tma_load_3d(sQ + kc * 16384, &mapQ, &bar_q_full, h * HD + kc * 64, qt * 128, b);
+          tma_load_3d(sDO + kc * 16384, &mapDO, &bar_q_full, h * HD + kc * 64, qt * 128, b);
+        }
         for (int j = 0; j <= qt && ok; ++j) {
           for (int kv = 0; kv < 2; ++kv) {
             const int slot = load % DQ_RING;
@@ -184,11 +190,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
               ok = false;
               break;
             }
-            mbar_expect_tx(&bar_r_full[slot], FB_TILE);
+            mbar_expect_tx(&bar_r_full[slot], TILE_BYTES);
             uint8_t* dst = sR + slot * FB_TILE;
             const CUtensorMap* m = kv ? &mapV : &mapK;
-            tma_load_3d(dst, m, &bar_r_full[slot], hk * 128, j * 128, b);
-            tma_load_3d(dst + 16384, m, &bar_r_full[slot], hk * 128 + 64, j * 128, b);
+#pragma unroll
+            for (int kc = 0; kc < KC; ++kc)
+              tma_load_3d(dst + kc * 16384, m, &bar_r_full[slot], hk * HD + kc * 64, j * 128, b);
             ++load;
           }
         }
@@ -201,7 +208,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both operands K-major
-      constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);  // B MN-major
+      constexpr uint32_t idesc_mn = make_idesc_bf16(128, HD, 0, 1);  // B MN-major
       bool ok = true;
       uint32_t load = 0, g = 0;
       int it_count = 0;
@@ -213,7 +220,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       };
       auto issue_kk = [&](uint32_t d_col, uint32_t a_addr, uint32_t b_addr) {
 #pragma unroll
-        for (int kc = 0; kc < 2; ++kc)
+        for (int kc = 0; kc < KC; ++kc)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16(tmem + d_col, make_smem_desc(a_addr + kc * 16384 + k * 32, 16, 1024),
@@ -328,11 +335,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       }
       tc_fence_after();
       const long long row_g = static_cast<long long>(b) * args.S + qt * 128 + row_l;
-      uint4* dst = reinterpret_cast<uint4*>(args.dq + (row_g * args.nh + h) * 128 + half * 64);
+      uint4* dst = reinterpret_cast<uint4*>(args.dq + (row_g * args.nh + h) * HD + half * (HD / 2));
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
+      for (int hh = 0; hh < HD / 64; ++hh) {
         uint32_t rr[32];
-        tmem_ld_32x32(t_row + 384 + half * 64 + hh * 32, rr);
+        tmem_ld_32x32(t_row + 384 + half * (HD / 2) + hh * 32, rr);
         tmem_ld_wait();
 #pragma unroll
         for (int c8 = 0; c8 < 4; ++c8)
@@ -362,6 +369,7 @@ constexpr int FB_HALF = 16384;    // 64 rows x 128 columns bf16: [hd chunk 0: 64
 __device__ __forceinline__ uint32_t fb_a_col(int ks) { return ks < 2 ? ks * 8 : 32 + (ks - 2) * 8; }
 
 // ----------------------------------------------------------------------------------------- dK, dV
+template <int HD>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO64,
@@ -421,6 +429,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_co
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   // TMEM columns: S^T[2] at 0 / 64, dP^T[2] at 128 / 192, dV at 256, dK at 384
+  constexpr int KC = HD / 64;
+  constexpr int TILE_BYTES = 128 * HD * 2;
   const int group = args.nh / args.nkv;
   const int per_j = args.B * args.nkv;
   const int n_qt = args.S >> 7;
@@ -438,11 +448,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_co
           ok = false;
           break;
         }
-        mbar_expect_tx(&bar_kv_full, 2 * FB_TILE);
-        tma_load_3d(sK, &mapK, &bar_kv_full, hk * 128, j * 128, b);
-        tma_load_3d(sK + 16384, &mapK, &bar_kv_full, hk * 128 + 64, j * 128, b);
-        tma_load_3d(sV, &mapV, &bar_kv_full, hk * 128, j * 128, b);
-        tma_load_3d(sV + 16384, &mapV, &bar_kv_full, hk * 128 + 64, j * 128, b);
+        mbar_expect_tx(&bar_kv_full, 2 * TILE_BYTES);
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc) {
+          tma_load_3d(sK + kc * 16384, &mapK, &bar_kv_full, hk * HD + kc * 64, j * 128, b);
+          tma_load_3d(sV + kc * 16384, &mapV, &bar_kv_full, hk * HD + kc * 64, j * 128, b);
+        }
         for (int gi = 0; gi < group && ok; ++gi) {
           const int h = hk * group + gi;
           for (int row0 = j * 128; row0 < args.S; row0 += 64, ++u) {  // query rows of this sub-tile
@@ -451,12 +462,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_co
               ok = false;
               break;
             }
-            mbar_expect_tx(&bar_r_full[slot], FB_SLOT + 512);
+            mbar_expect_tx(&bar_r_full[slot], TILE_BYTES + 512);  // 64 rows of Q and of dO, two statistics rows
             uint8_t* dst = sR + slot * FB_SLOT;
 #pragma unroll
-            for (int kc = 0; kc < 2; ++kc) {
-              tma_load_3d(dst + kc * 8192, &mapQ64, &bar_r_full[slot], h * 128 + kc * 64, row0, b);
-              tma_load_3d(dst + FB_HALF + kc * 8192, &mapDO64, &bar_r_full[slot], h * 128 + kc * 64, row0, b);
+            for (int kc = 0; kc < KC; ++kc) {
+              tma_load_3d(dst + kc * 8192, &mapQ64, &bar_r_full[slot], h * HD + kc * 64, row0, b);
+              tma_load_3d(dst + FB_HALF + kc * 8192, &mapDO64, &bar_r_full[slot], h * HD + kc * 64, row0, b);
             }
             const long long so = (static_cast<long long>(b) * args.nh + h) * args.S + row0;
             bulk_load_1d(sStat + slot * 128, args.lse2 + so, 256, &bar_r_full[slot]);
@@ -472,7 +483,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_co
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 1);
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, HD, 0, 1);
       bool ok = true;
       uint32_t u0 = 0;
       int it_count = 0;
@@ -486,7 +497,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_co
       auto mma1 = [&](uint32_t u) {  // S^T = K_j Q_sub^T, dP^T = V_j dO_sub^T
         const uint32_t buf = u & 1, qq = slot_addr(u), dd = qq + FB_HALF;
 #pragma unroll
-        for (int kc = 0; kc < 2; ++kc)
+        for (int kc = 0; kc < KC; ++kc)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             umma_bf16(tmem + buf * 64, make_smem_desc(k_addr + kc * 16384 + k * 32, 16, 1024),
@@ -596,14 +607,14 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_co
       }
       tc_fence_after();
       const long long row_g = static_cast<long long>(b) * args.S + j * 128 + row_l;
-      const long long off = (row_g * args.nkv + hk) * 128 + half * 64;
+      const long long off = (row_g * args.nkv + hk) * HD + half * (HD / 2);
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         uint4* dst = reinterpret_cast<uint4*>((which ? args.dk : args.dv) + off);
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
+        for (int hh = 0; hh < HD / 64; ++hh) {
           uint32_t rr[32];
-          tmem_ld_32x32(t_row + 256 + which * 128 + half * 64 + hh * 32, rr);
+          tmem_ld_32x32(t_row + 256 + which * 128 + half * (HD / 2) + hh * 32, rr);
           tmem_ld_wait();
 #pragma unroll
           for (int c8 = 0; c8 < 4; ++c8)
@@ -630,12 +641,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap mapQ64, const __grid_co
 
 using namespace b200;
 
-extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int nh,
-                              int nkv, float softmax_scale, int* status, cudaStream_t stream) {
-  if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
+template <int HD>
+static int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                            const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int nh,
+                            int nkv, float softmax_scale, int* status, cudaStream_t stream) {
   CUtensorMap mq, mk, mv, mdo, mq64, mdo64;
-  const uint64_t qrow = static_cast<uint64_t>(nh) * 128, krow = static_cast<uint64_t>(nkv) * 128;
+  const uint64_t qrow = static_cast<uint64_t>(nh) * HD, krow = static_cast<uint64_t>(nkv) * HD;
   int rc = make_map(&mq, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
   if (rc == 0) rc = make_map(&mdo, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
   if (rc == 0) rc = make_map(&mk, k, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
@@ -646,8 +657,10 @@ extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) !=
+            cudaSuccess)
       return -10;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -655,7 +668,7 @@ extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const
     configured = true;
   }
   const long long rows = static_cast<long long>(B) * S * nh;
-  attn_delta_kernel<<<static_cast<unsigned>((rows * 16 + 255) / 256), 256, 0, stream>>>(
+  attn_delta_kernel<HD><<<static_cast<unsigned>((rows * (HD / 8) + 255) / 256), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, B, S, nh,
       softmax_scale);
   FbArgs a;
@@ -669,8 +682,19 @@ extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   a.status = status;
   a.items = B * nh * (S / 128);
-  flash_bwd_dq_kernel<<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq, mk, mv, mdo, a);
+  flash_bwd_dq_kernel<HD><<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq, mk, mv, mdo, a);
   a.items = B * nkv * (S / 128);
-  flash_bwd_dkv_kernel<<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq64, mk, mv, mdo64, a);
+  flash_bwd_dkv_kernel<HD><<<a.items < sms ? a.items : sms, FB_THREADS, FB_SMEM, stream>>>(mq64, mk, mv, mdo64, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int nh,
+                              int nkv, int head_dim, float softmax_scale, int* status, cudaStream_t stream) {
+  if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
+  if (head_dim == 128)
+    return launch_flash_bwd<128>(q, k, v, o, d_o, lse, delta, dq, dk, dv, B, S, nh, nkv, softmax_scale, status, stream);
+  if (head_dim == 64)
+    return launch_flash_bwd<64>(q, k, v, o, d_o, lse, delta, dq, dk, dv, B, S, nh, nkv, softmax_scale, status, stream);
+  return -3;
 }

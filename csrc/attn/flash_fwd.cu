@@ -1,4 +1,4 @@
-// Causal grouped-query flash attention, forward, for sm_100a (head_dim 128).
+// Causal grouped-query flash attention, forward, for sm_100a (head_dim 128 or 64: template parameter HD).
 //
 // Persistent CTAs (one per SM).  A work item is (batch, pair of query heads that share one key/value head,
 // 128 query rows); key/value tiles of 128 rows stream through a 5-slot TMA ring (K0, V0, K1, V1, ...) and
@@ -30,7 +30,7 @@
 namespace b200 {
 
 constexpr int FA_THREADS = 320;
-constexpr int FA_TILE = 32768;   // 128 x 128 bf16
+constexpr int FA_TILE = 32768;   // slot size: 128 x 128 bf16 (head_dim 64 fills half of a slot)
 constexpr int FA_RING = 5;       // K/V slots
 constexpr int FA_EXTRA = 256;    // barriers
 constexpr int FA_SMEM = 232448;  // everything a CTA may have; the seven tiles alone take 224 KB
@@ -67,6 +67,7 @@ __device__ __forceinline__ int fa_sched(int round, int cta, int ctas) {
   return round * ctas + ((round & 1) ? ctas - 1 - cta : cta);
 }
 
+template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                  const __grid_constant__ CUtensorMap mapV, const FaFwdArgs args) {
@@ -123,6 +124,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
   const int group = args.nh / args.nkv;
+  constexpr int KC = HD / 64;              // 64-column chunks of a head
+  constexpr int TILE_BYTES = 128 * HD * 2;  // bytes that one Q, K or V tile brings in
 
   if (warp == 0) {
     if (lane == 0) {
@@ -139,10 +142,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
             ok = false;
             break;
           }
-          mbar_expect_tx(&bar_q_full[x], FA_TILE);
-          tma_load_3d(sQ + x * FA_TILE, &mapQ, &bar_q_full[x], (2 * it.pair + x) * 128, it.qt * 128, it.b);
-          tma_load_3d(sQ + x * FA_TILE + 16384, &mapQ, &bar_q_full[x], (2 * it.pair + x) * 128 + 64, it.qt * 128,
-                      it.b);
+          mbar_expect_tx(&bar_q_full[x], TILE_BYTES);
+#pragma unroll
+          for (int kc = 0; kc < KC; ++kc)
+            tma_load_3d(sQ + x * FA_TILE + kc * 16384, &mapQ, &bar_q_full[x], (2 * it.pair + x) * HD + kc * 64,
+                        it.qt * 128, it.b);
           ++q_loads;
         }
         for (int j = 0; j < it.n && ok; ++j) {
@@ -152,10 +156,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
               ok = false;
               break;
             }
-            mbar_expect_tx(&bar_r_full[slot], FA_TILE);
+            mbar_expect_tx(&bar_r_full[slot], TILE_BYTES);
             uint8_t* dst = sR + slot * FA_TILE;
-            tma_load_3d(dst, &mapK, &bar_r_full[slot], hk * 128, j * 128, it.b);
-            tma_load_3d(dst + 16384, &mapK, &bar_r_full[slot], hk * 128 + 64, j * 128, it.b);
+#pragma unroll
+            for (int kc = 0; kc < KC; ++kc)
+              tma_load_3d(dst + kc * 16384, &mapK, &bar_r_full[slot], hk * HD + kc * 64, j * 128, it.b);
             ++load;
           }
           {
@@ -164,13 +169,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
               ok = false;
               break;
             }
-            mbar_expect_tx(&bar_r_full[slot], FA_TILE);
+            mbar_expect_tx(&bar_r_full[slot], TILE_BYTES);
             uint8_t* dst = sR + slot * FA_TILE;
 #pragma unroll
             for (int kh = 0; kh < 2; ++kh)
 #pragma unroll
-              for (int jn = 0; jn < 2; ++jn)
-                tma_load_3d(dst + kh * 16384 + jn * 8192, &mapV, &bar_r_full[slot], hk * 128 + jn * 64,
+              for (int jn = 0; jn < KC; ++jn)
+                tma_load_3d(dst + kh * (KC * 8192) + jn * 8192, &mapV, &bar_r_full[slot], hk * HD + jn * 64,
                             j * 128 + kh * 64, it.b);
             ++load;
           }
@@ -186,7 +191,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_u = make_idesc_bf16(128, 128, 0, 1);
+      constexpr uint32_t idesc_u = make_idesc_bf16(128, HD, 0, 1);
       bool ok = true;
       uint32_t load = 0;  // ring entries consumed before this item
       uint32_t g = 0;     // key tiles processed before this item (phase of the per-tile barriers)
@@ -201,7 +206,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         const uint32_t q_addr = smem_u32(sQ + x * FA_TILE);
         const uint32_t k_addr = smem_u32(sR + (k_idx % FA_RING) * FA_TILE);
 #pragma unroll
-        for (int kc = 0; kc < 2; ++kc)
+        for (int kc = 0; kc < KC; ++kc)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16(tmem + x * 128, make_smem_desc(q_addr + kc * 16384 + k * 32, 16, 1024),
@@ -215,7 +220,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16_ts(tmem + 256 + x * 128, tmem + x * 128 + (kc * 4 + k) * 8,
-                         make_smem_desc(v_addr + kc * 16384 + k * 2048, 8192, 1024), idesc_u,
+                         make_smem_desc(v_addr + kc * (KC * 8192) + k * 2048, 8192, 1024), idesc_u,
                          (acc || (kc | k) != 0) ? 1u : 0u);
         umma_commit(&bar_u_full[x]);
       };
@@ -332,7 +337,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
             tc_fence_after();
             const float a = grow ? ex2_approx((m_ref - m_new) * sl2) : 1.0f;
 #pragma unroll
-            for (int hh = 0; hh < 4; ++hh) {
+            for (int hh = 0; hh < HD / 32; ++hh) {
               uint32_t r[32];
               tmem_ld_32x32(t_o + hh * 32, r);
               tmem_ld_wait();
@@ -426,9 +431,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       const float inv = 1.0f / l_run;
       const int h = 2 * it.pair + x;
       const long long row_g = static_cast<long long>(it.b) * args.S + it.qt * 128 + row_l;
-      uint4* dst = reinterpret_cast<uint4*>(args.O + (row_g * args.nh + h) * 128);
+      uint4* dst = reinterpret_cast<uint4*>(args.O + (row_g * args.nh + h) * HD);
 #pragma unroll
-      for (int hh = 0; hh < 4; ++hh) {
+      for (int hh = 0; hh < HD / 32; ++hh) {
         uint32_t r[32];
         tmem_ld_32x32(t_o + hh * 32, r);
         tmem_ld_wait();
@@ -457,12 +462,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
 
 using namespace b200;
 
-extern "C" int b200_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int nh,
-                              int nkv, float softmax_scale, int* status, cudaStream_t stream) {
-  if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
-  if (((nh / nkv) & 1) != 0) return -2;  // two query heads of one CTA must share their key/value head
+template <int HD>
+static int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int nh,
+                            int nkv, float softmax_scale, int* status, cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
-  const uint64_t qrow = static_cast<uint64_t>(nh) * 128, krow = static_cast<uint64_t>(nkv) * 128;
+  const uint64_t qrow = static_cast<uint64_t>(nh) * HD, krow = static_cast<uint64_t>(nkv) * HD;
   int rc = make_map(&mq, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
   if (rc == 0) rc = make_map(&mk, k, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
   if (rc == 0) rc = make_map(&mv, v, krow, S, B, krow * 2, krow * 2 * S, 64, 64);
@@ -470,7 +474,8 @@ extern "C" int b200_flash_fwd(const void* q, const void* k, const void* v, void*
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM) !=
+        cudaSuccess)
       return -10;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -485,6 +490,15 @@ extern "C" int b200_flash_fwd(const void* q, const void* k, const void* v, void*
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   a.status = status;
   const int grid = a.items < sms ? a.items : sms;
-  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(mq, mk, mv, a);
+  flash_fwd_kernel<HD><<<grid, FA_THREADS, FA_SMEM, stream>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int b200_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int nh,
+                              int nkv, int head_dim, float softmax_scale, int* status, cudaStream_t stream) {
+  if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
+  if (((nh / nkv) & 1) != 0) return -2;  // two query heads of one CTA must share their key/value head
+  if (head_dim == 128) return launch_flash_fwd<128>(q, k, v, o, lse, B, S, nh, nkv, softmax_scale, status, stream);
+  if (head_dim == 64) return launch_flash_fwd<64>(q, k, v, o, lse, B, S, nh, nkv, softmax_scale, status, stream);
+  return -3;
 }

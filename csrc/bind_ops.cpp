@@ -90,29 +90,31 @@ void qknorm_rope_bwd(const Tensor& dq, const Tensor& dk, const Tensor& dv, const
 // ---------------------------------------------------------------- attention
 void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse, double scale, Tensor& status) {
   bf16c(q, "q"); bf16c(k, "k"); bf16c(v, "v"); bf16c(o, "o"); f32c(lse, "lse"); i32c(status, "status");
-  need(q.dim() == 4 && k.dim() == 4 && q.size(3) == 128 && k.size(3) == 128, "flash attention: [B,S,h,128] expected");
+  need(q.dim() == 4 && k.dim() == 4 && (q.size(3) == 128 || q.size(3) == 64) && k.size(3) == q.size(3),
+       "flash attention: [B,S,h,128] or [B,S,h,64] expected");
   need(k.sizes() == v.sizes() && o.sizes() == q.sizes(), "flash attention: shape mismatch");
   const int B = (int)q.size(0), S = (int)q.size(1), nh = (int)q.size(2), nkv = (int)k.size(2);
   need(k.size(0) == B && k.size(1) == S, "flash attention: k/v batch or length");
   need(lse.numel() == (int64_t)B * nh * S, "flash attention: lse size");
   c10::cuda::CUDAGuard g(q.device());
   rc_ok(b200_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, S, nh, nkv,
-                       (float)scale, status.data_ptr<int>(), stream()), "flash_fwd");
+                       (int)q.size(3), (float)scale, status.data_ptr<int>(), stream()), "flash_fwd");
 }
 
 void flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
                Tensor& delta, Tensor& dq, Tensor& dk, Tensor& dv, double scale, Tensor& status) {
   bf16c(q, "q"); bf16c(k, "k"); bf16c(v, "v"); bf16c(o, "o"); bf16c(d_o, "d_o"); f32c(lse, "lse"); f32c(delta, "delta");
   bf16c(dq, "dq"); bf16c(dk, "dk"); bf16c(dv, "dv"); i32c(status, "status");
-  need(q.dim() == 4 && k.dim() == 4 && q.size(3) == 128 && k.size(3) == 128, "flash attention: [B,S,h,128] expected");
+  need(q.dim() == 4 && k.dim() == 4 && (q.size(3) == 128 || q.size(3) == 64) && k.size(3) == q.size(3),
+       "flash attention: [B,S,h,128] or [B,S,h,64] expected");
   need(k.sizes() == v.sizes() && o.sizes() == q.sizes() && d_o.sizes() == q.sizes() && dq.sizes() == q.sizes() &&
            dk.sizes() == k.sizes() && dv.sizes() == k.sizes(), "flash attention backward: shape mismatch");
   const int B = (int)q.size(0), S = (int)q.size(1), nh = (int)q.size(2), nkv = (int)k.size(2);
   need(lse.numel() == (int64_t)B * nh * S && delta.numel() == lse.numel(), "flash attention backward: statistics size");
   c10::cuda::CUDAGuard g(q.device());
   rc_ok(b200_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
-                       delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, nh, nkv, (float)scale,
-                       status.data_ptr<int>(), stream()), "flash_bwd");
+                       delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, nh, nkv, (int)q.size(3),
+                       (float)scale, status.data_ptr<int>(), stream()), "flash_bwd");
 }
 
 // ------------------------------------------------------------------- router
@@ -378,7 +380,8 @@ void clip_coef(const Tensor& ss, double max_norm, Tensor& coef) {
   rc_ok(b200_clip_coef(ss.data_ptr<float>(), (float)max_norm, coef.data_ptr<float>(), stream()), "clip_coef");
 }
 void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptT& p16, const Tensor& hyper, double beta1,
-           double beta2, double eps, double wd, const OptT& grad_coef, const std::vector<int64_t>& p16_peers) {
+           double beta2, double eps, double wd, const OptT& grad_coef, const std::vector<int64_t>& p16_peers,
+           int64_t p16_mc) {
   f32c(p, "p"); f32c(g, "g"); f32c(m, "m"); f32c(v, "v"); f32c(hyper, "hyper");
   need(hyper.numel() >= 3, "hyper must hold {lr, bc1, bc2}");
   std::vector<void*> peers;
@@ -388,7 +391,7 @@ void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptT& p16, co
   rc_ok(b200_adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
                    optp<void>(p16), p.numel(), hyper.data_ptr<float>(), (float)beta1, (float)beta2, (float)eps,
                    (float)wd, optp<const float>(grad_coef), p16_peers.empty() ? nullptr : peers.data(),
-                   (int)p16_peers.size(), stream()), "adamw");
+                   (int)p16_peers.size(), reinterpret_cast<void*>(p16_mc), stream()), "adamw");
 }
 void cast_bf16(const Tensor& src, Tensor& dst) {
   f32c(src, "src"); bf16c(dst, "dst");
@@ -508,6 +511,7 @@ void bind_ops(pybind11::module_& m) {
   m.def("clip_coef", &clip_coef);
   m.def("adamw", &adamw, pybind11::arg("p"), pybind11::arg("g"), pybind11::arg("m"), pybind11::arg("v"),
         pybind11::arg("p16"), pybind11::arg("hyper"), pybind11::arg("beta1"), pybind11::arg("beta2"), pybind11::arg("eps"),
-        pybind11::arg("wd"), pybind11::arg("grad_coef"), pybind11::arg("p16_peers") = std::vector<int64_t>());
+        pybind11::arg("wd"), pybind11::arg("grad_coef"), pybind11::arg("p16_peers") = std::vector<int64_t>(),
+        pybind11::arg("p16_mc") = 0);
   m.def("cast_bf16", &cast_bf16);
 }

@@ -92,10 +92,11 @@ int b200_sumsq(const float* g, long long n, float* scratch, float* out, int accu
 int b200_clip_coef(const float* sumsq, float max_norm, float* coef, cudaStream_t stream);
 // hyper: device float[3] = {lr, 1 - beta1^t, 1 - beta2^t}
 // p16_peers (optional, `world` entries): the same slice of every rank's bf16 compute copy; when given the
-// new weights are also stored there (sharded optimizer: update + parameter all-gather in one pass)
+// new weights are also stored there (sharded optimizer: update + parameter all-gather in one pass).
+// p16_mc (optional): NVSwitch multicast address of that slice; one `multimem.st` then replaces the peer stores.
 int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, const float* hyper, float beta1,
                float beta2, float eps, float wd, const float* grad_coef, void* const* p16_peers, int world,
-               cudaStream_t stream);
+               void* p16_mc, cudaStream_t stream);
 int b200_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 
 // ---- comm/allreduce.cu

@@ -65,7 +65,8 @@ __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm
 __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                              float* __restrict__ v, __nv_bfloat16* __restrict__ p16, long long n,
                              const float* __restrict__ hyper, float beta1, float beta2, float eps, float wd,
-                             const float* __restrict__ grad_coef, AdamPeers peers, int world) {
+                             const float* __restrict__ grad_coef, AdamPeers peers, int world,
+                             __nv_bfloat16* p16_mc) {
   // hyper = {learning rate, 1 - beta1^t, 1 - beta2^t}: device-resident so that a captured CUDA graph
   // can be replayed with new values
   const float lr = hyper[0], bc1 = hyper[1], bc2 = hyper[2];
@@ -96,8 +97,15 @@ __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
     reinterpret_cast<float4*>(v)[i] = vv;
     const uint2 packed = make_uint2(pack_bf16x2(pv.x, pv.y), pack_bf16x2(pv.z, pv.w));
     if (p16) reinterpret_cast<uint2*>(p16)[i] = packed;
-    // sharded optimizer: the owner of this slice publishes the new bf16 weights to every rank (peer stores)
-    for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(peers.p16[r])[i] = packed;
+    // sharded optimizer: the owner of this slice publishes the new bf16 weights to every rank: one multicast
+    // store that the NVSwitch fans out to all ranks (own copy included), or `world` peer stores
+    if (p16_mc != nullptr) {
+      asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(reinterpret_cast<uint2*>(p16_mc) + i),
+                   "f"(__uint_as_float(packed.x)), "f"(__uint_as_float(packed.y))
+                   : "memory");
+    } else {
+      for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(peers.p16[r])[i] = packed;
+    }
   }
   if (world > 0) __threadfence_system();
   // tail (n not a multiple of 4)
@@ -155,16 +163,18 @@ extern "C" int b200_clip_coef(const float* sumsq, float max_norm, float* coef, c
 
 extern "C" int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long long n, const float* hyper,
                           float beta1, float beta2, float eps, float wd, const float* grad_coef, void* const* p16_peers,
-                          int world, cudaStream_t stream) {
+                          int world, void* p16_mc, cudaStream_t stream) {
   if (n <= 0) return 0;
   AdamPeers peers;
   for (int r = 0; r < 8; ++r) peers.p16[r] = (p16_peers && r < world) ? reinterpret_cast<__nv_bfloat16*>(p16_peers[r]) : nullptr;
   if (p16_peers == nullptr) world = 0;
+  if (world == 0) p16_mc = nullptr;
   if (world > 0 && (n & 3) != 0) return -1;  // published slices are whole float4 groups
+  if (p16_mc != nullptr && (reinterpret_cast<uintptr_t>(p16_mc) & 7) != 0) return -3;
   long long b = (n / 4 + 255) / 256;
   const int grid = static_cast<int>(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
   adamw_kernel<<<grid, 256, 0, stream>>>(p, g, m, v, reinterpret_cast<__nv_bfloat16*>(p16), n, hyper, beta1, beta2,
-                                         eps, wd, grad_coef, peers, world);
+                                         eps, wd, grad_coef, peers, world, reinterpret_cast<__nv_bfloat16*>(p16_mc));
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

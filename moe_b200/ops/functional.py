@@ -393,11 +393,11 @@ def _sdpa(q, k, v):
 
 
 def flash_supported(q, k) -> bool:
-    """Shapes the tcgen05 forward kernel covers: head_dim 128, length a multiple of 128, an even number of
+    """Shapes the tcgen05 kernels cover: head_dim 128 or 64, length a multiple of 128, an even number of
     query heads per key/value head (a CTA works on two query heads that share their key/value tiles)."""
     B, S, nh, hd = q.shape
     nkv = k.shape[2]
-    return (q.is_cuda and q.dtype == BF16 and hd == 128 and S % 128 == 0 and nh % nkv == 0
+    return (q.is_cuda and q.dtype == BF16 and hd in (128, 64) and S % 128 == 0 and nh % nkv == 0
             and (nh // nkv) % 2 == 0)
 
 

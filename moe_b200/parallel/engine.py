@@ -485,7 +485,8 @@ class TrainEngine:
                 e.adamw(self.p32[p_lo:p_hi], self.g32[p_lo:p_hi], self.m[m_lo:m_lo + n], self.v[m_lo:m_lo + n],
                         None if kind == 2 else self.p16[p_lo:p_hi], self._hyper, b1, b2, self.eps, wd,
                         self._coef_ep if kind == 1 else self._coef,
-                        [q + 2 * p_lo for q in self._peers.p16_ptrs] if kind == 2 else [])
+                        [q + 2 * p_lo for q in self._peers.p16_ptrs] if kind == 2 else [],
+                        (self._peers.p16_mc + 2 * p_lo) if kind == 2 and self._peers.p16_mc else 0)
             self.mark("adamw_end")
             if self.sharded:  # every rank's stores into this rank's bf16 copy have landed after this
                 self._fused_ar.param_barrier()

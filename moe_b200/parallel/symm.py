@@ -60,6 +60,7 @@ class PeerBuffers:
         self.group = group
         self.p16 = None
         self.p16_ptrs: list[int] = []
+        self.p16_mc = 0  # multicast address of the bf16 parameter copy (0: peer stores)
         dist.barrier(group)
         # Measurement aid: MOE_B200_COMM_STUB=1 points every "peer" at this rank's own buffers and pre-sets the
         # flag words, so the same kernels run with the same local work but nothing crosses NVLink and nobody
@@ -95,8 +96,14 @@ class PeerBuffers:
         h = sm.rendezvous(self.p16, self.group)
         self._handles = self._handles + (h,)
         self.p16_ptrs = [int(p) for p in h.buffer_ptrs]
+        if self.multicast_ptr:  # NVLS in use for the gradients: publish the weights through the switch as well
+            try:
+                self.p16_mc = int(getattr(h, "multicast_ptr", 0) or 0)
+            except Exception:
+                self.p16_mc = 0
         if getattr(self, "stubbed", False):
             self.p16_ptrs = [self.p16_ptrs[self.rank]] * self.world
+            self.p16_mc = 0
         dist.barrier(self.group)
 
 

@@ -376,31 +376,32 @@ def test_adamw_and_norm(dev):
 
 
 @pytest.mark.parametrize("bwd", ["library", "own"])
+@pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("B,S,nh,nkv,spread", [(1, 128, 2, 1, 1.0), (2, 384, 4, 2, 1.0), (1, 1024, 8, 1, 1.0),
                                                (2, 512, 4, 2, 6.0)])
-def test_flash_attention_forward_and_grads(dev, monkeypatch, B, S, nh, nkv, spread, bwd):
+def test_flash_attention_forward_and_grads(dev, monkeypatch, B, S, nh, nkv, spread, bwd, hd):
     """Own tcgen05 forward (output and log-sum-exp) and the gradients of `ops.attention` against the fp32
     statement; `spread` widens the score range so that the lazy accumulator rescale in TMEM is exercised."""
     from moe_b200.ops import _ext, oracle
     from moe_b200.ops import functional as F
     from moe_b200.ops import gemm as G
 
-    q, k, v = _bf(B, S, nh, 128, scale=spread), _bf(B, S, nkv, 128, scale=spread), _bf(B, S, nkv, 128)
+    q, k, v = _bf(B, S, nh, hd, scale=spread), _bf(B, S, nkv, hd, scale=spread), _bf(B, S, nkv, hd)
     assert F.flash_supported(q, k)
     o = torch.empty_like(q)
     lse2 = torch.empty(B, nh, S, device=dev)
-    _ext.load().flash_fwd(q, k, v, o, lse2, 1 / math.sqrt(128), G.status_word(dev))
+    _ext.load().flash_fwd(q, k, v, o, lse2, 1 / math.sqrt(hd), G.status_word(dev))
     _sync_status()
     qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
     ref = oracle.causal_gqa_attention(qf, kf, vf)
     assert relerr(o, ref) < 1.5e-2
     kk = kf.detach().repeat_interleave(nh // nkv, 2)
-    sc = torch.einsum("bqhd,bkhd->bhqk", qf.detach(), kk) / math.sqrt(128)
+    sc = torch.einsum("bqhd,bkhd->bhqk", qf.detach(), kk) / math.sqrt(hd)
     sc = sc.masked_fill(torch.ones(S, S, dtype=torch.bool, device=dev).triu(1), float("-inf"))
     assert (lse2 * math.log(2) - torch.logsumexp(sc, -1)).abs().max() < 2e-3
     # through autograd: own forward, then the library's or the own backward kernels
     monkeypatch.setenv("MOE_B200_ATTN_BWD", bwd)
-    do = _bf(B, S, nh, 128)
+    do = _bf(B, S, nh, hd)
     q2, k2, v2 = (t.clone().requires_grad_() for t in (q, k, v))
     out = F.attention(q2, k2, v2)
     assert torch.equal(out, o)
