@@ -137,7 +137,7 @@ def case_qknorm_rope(small):
     return dict(shape=[B, S, nh, nkv, hd], ms=ms, bytes=2.0 * qkv.numel() * 2)
 
 
-def case_flash_attn_fwd(small):
+def case_flash_attn_fwd(small, hd=128):
     import math
 
     from moe_b200.ops import _ext
@@ -145,16 +145,20 @@ def case_flash_attn_fwd(small):
 
     e = _ext.load()
     B, S, nh, nkv = (2, 2048, 16, 8) if small else (8, 2048, 16, 8)
-    q, k, v = bf(B, S, nh, 128), bf(B, S, nkv, 128), bf(B, S, nkv, 128)
+    q, k, v = bf(B, S, nh, hd), bf(B, S, nkv, hd), bf(B, S, nkv, hd)
     o, lse = torch.empty_like(q), torch.empty(B, nh, S, device="cuda")
     st = G.status_word(q.device)
-    ms = timeit(lambda: e.flash_fwd(q, k, v, o, lse, 1 / math.sqrt(128), st))
+    ms = timeit(lambda: e.flash_fwd(q, k, v, o, lse, 1 / math.sqrt(hd), st))
     ref = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(
         q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, enable_gqa=True))
-    return dict(shape=[B, S, nh, nkv, 128], ms=ms, flops=2.0 * B * nh * S * S * 128, sdpa_ms=ref)
+    return dict(shape=[B, S, nh, nkv, hd], ms=ms, flops=2.0 * B * nh * S * S * hd, sdpa_ms=ref)
 
 
-def case_flash_attn_bwd(small):
+def case_flash_attn_fwd_hd64(small):
+    return case_flash_attn_fwd(small, hd=64)
+
+
+def case_flash_attn_bwd(small, hd=128):
     import math
 
     from moe_b200.ops import _ext
@@ -162,10 +166,10 @@ def case_flash_attn_bwd(small):
 
     e = _ext.load()
     B, S, nh, nkv = (2, 2048, 16, 8) if small else (8, 2048, 16, 8)
-    q, k, v, do = bf(B, S, nh, 128), bf(B, S, nkv, 128), bf(B, S, nkv, 128), bf(B, S, nh, 128)
+    q, k, v, do = bf(B, S, nh, hd), bf(B, S, nkv, hd), bf(B, S, nkv, hd), bf(B, S, nh, hd)
     o, lse = torch.empty_like(q), torch.empty(B, nh, S, device="cuda")
     st = G.status_word(q.device)
-    sc = 1 / math.sqrt(128)
+    sc = 1 / math.sqrt(hd)
     e.flash_fwd(q, k, v, o, lse, sc, st)
     dq, dk, dv, delta = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v), torch.empty_like(lse)
     ms = timeit(lambda: e.flash_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, sc, st))
@@ -174,7 +178,11 @@ def case_flash_attn_bwd(small):
     ref = timeit(lambda: torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
         do.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), o.transpose(1, 2), lse_nat, z, z,
         None, None, None, S, S, 0.0, True, scale=sc))
-    return dict(shape=[B, S, nh, nkv, 128], ms=ms, flops=5.0 * B * nh * S * S * 128, cudnn_ms=ref)
+    return dict(shape=[B, S, nh, nkv, hd], ms=ms, flops=5.0 * B * nh * S * S * hd, cudnn_ms=ref)
+
+
+def case_flash_attn_bwd_hd64(small):
+    return case_flash_attn_bwd(small, hd=64)
 
 
 def case_allreduce_emulated(small):

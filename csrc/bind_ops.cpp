@@ -393,6 +393,13 @@ void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptT& p16, co
                    (float)wd, optp<const float>(grad_coef), p16_peers.empty() ? nullptr : peers.data(),
                    (int)p16_peers.size(), reinterpret_cast<void*>(p16_mc), stream()), "adamw");
 }
+void sum_partials(const Tensor& part, Tensor& out, bool accumulate) {
+  f32c(part, "part"); f32c(out, "out");
+  need(out.numel() > 0 && part.numel() % out.numel() == 0 && out.numel() < (1ll << 31), "sum_partials sizes");
+  c10::cuda::CUDAGuard gd(part.device());
+  rc_ok(b200_sum_partials(part.data_ptr<float>(), out.data_ptr<float>(), (int)(part.numel() / out.numel()),
+                          (int)out.numel(), accumulate ? 1 : 0, stream()), "sum_partials");
+}
 void cast_bf16(const Tensor& src, Tensor& dst) {
   f32c(src, "src"); bf16c(dst, "dst");
   c10::cuda::CUDAGuard gd(src.device());
@@ -514,4 +521,5 @@ void bind_ops(pybind11::module_& m) {
         pybind11::arg("wd"), pybind11::arg("grad_coef"), pybind11::arg("p16_peers") = std::vector<int64_t>(),
         pybind11::arg("p16_mc") = 0);
   m.def("cast_bf16", &cast_bf16);
+  m.def("sum_partials", &sum_partials);
 }

@@ -173,6 +173,12 @@ __global__ void colsum_kernel(const float* __restrict__ part, float* __restrict_
 
 using namespace b200;
 
+extern "C" int b200_sum_partials(const float* part, float* out, int nparts, int n, int accumulate, cudaStream_t stream) {
+  if (nparts <= 0 || n <= 0) return -1;
+  colsum_kernel<<<(n + 31) / 32, 256, 0, stream>>>(part, out, nparts, n, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 extern "C" int b200_rmsnorm_fwd(const void* x, const void* res, const float* w, void* h_out, void* y, float* rstd,
                                 int T, int H, float eps, cudaStream_t stream) {
   if (H % 8 != 0 || T <= 0) return T == 0 ? 0 : -1;

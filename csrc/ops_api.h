@@ -98,6 +98,8 @@ int b200_adamw(float* p, const float* g, float* m, float* v, void* p16, long lon
                float beta2, float eps, float wd, const float* grad_coef, void* const* p16_peers, int world,
                void* p16_mc, cudaStream_t stream);
 int b200_cast_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
+// out[i] (+)= sum_p part[p * n + i], p in fixed order (split-K partial sums; bitwise reproducible)
+int b200_sum_partials(const float* part, float* out, int nparts, int n, int accumulate, cudaStream_t stream);
 
 // ---- comm/allreduce.cu
 #define B200_MAX_RANKS 8

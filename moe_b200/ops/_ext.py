@@ -36,7 +36,7 @@ _module = None
 KERNELS_PER_CALL = {"gemm": 1, "rmsnorm_fwd": 1, "rmsnorm_bwd": 2, "qknorm_rope_fwd": 1, "qknorm_rope_bwd": 2,
                     "router_fwd": 1, "router_bwd": 1, "moe_plan": 3, "moe_gather": 1, "moe_combine": 1,
                     "moe_combine_bwd": 1, "moe_slot_dot": 1, "moe_row_dot_reduce": 1, "lse_loss": 1, "lce_reduce": 1, "dlogits_": 1, "embed_fwd": 1, "embed_bwd": 1, "embed_sort": 1, "sumsq": 2,
-                    "clip_coef": 1, "adamw": 1, "cast_bf16": 1, "allreduce": 1, "allgather_bf16": 1, "router_colsum": 1, "router_part_reduce": 1, "moe_aux": 1, "peer_barrier": 1, "clip_coef_multi": 1, "ep_exchange": 1, "ep_dispatch": 1}
+                    "clip_coef": 1, "adamw": 1, "cast_bf16": 1, "sum_partials": 1, "allreduce": 1, "allgather_bf16": 1, "router_colsum": 1, "router_part_reduce": 1, "moe_aux": 1, "peer_barrier": 1, "clip_coef_multi": 1, "ep_exchange": 1, "ep_dispatch": 1}
 _launches = 0
 
 

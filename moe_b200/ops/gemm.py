@@ -116,13 +116,44 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
     return out
 
 
+_SPLIT_SEG: dict = {}
+
+
+def _split_k_segments(Kc: int, device) -> torch.Tensor | None:
+    """Segment offsets (int32, on the device) that cut a contraction of `Kc` rows into up to 64 equal pieces
+    of whole 64-row blocks; None when `Kc` does not divide that way.  Cached: built outside graph capture."""
+    key = (Kc, str(device))
+    if key not in _SPLIT_SEG:
+        blocks = Kc // 64
+        parts = 0
+        if Kc % 64 == 0:
+            parts = max((s for s in range(1, 65) if blocks % s == 0), default=0)
+        _SPLIT_SEG[key] = (torch.arange(parts + 1, dtype=torch.int32, device=device) * (Kc // parts)
+                           if parts >= 8 else None)
+    return _SPLIT_SEG[key]
+
+
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, beta: int = 0, bn: int | None = None,
             pair: bool | None = None) -> torch.Tensor:
-    """`out[M,N] (+)= a[Kc,M]^T @ b[Kc,N]`, fp32 output (weight-gradient shape)."""
+    """`out[M,N] (+)= a[Kc,M]^T @ b[Kc,N]`, fp32 output (weight-gradient shape).  A short, wide output with a long
+    contraction (the router's weight gradient: 16 x H over all tokens) has only N / 256 tiles to give to 148 SMs;
+    it is cut along the contraction into partial products (one grouped-by-contraction launch) that a fixed-order
+    sum then folds into `out`."""
     _check2d(a, "a"); _check2d(b, "b")
     Kc, M = a.shape
     N = b.shape[1]
     assert b.shape[0] == Kc and out.dtype == torch.float32 and out.stride(1) == 1
+    if (pair is not False and bn is None and pair_tiles_enabled() and M < 256 and N >= 256 and Kc >= 4096
+            and out.is_contiguous() and M * N % 4 == 0):
+        seg = _split_k_segments(Kc, a.device)
+        if seg is not None:
+            S = seg.numel() - 1
+            part = torch.empty(S, M, N, dtype=torch.float32, device=a.device)
+            _launch(mode=MODE_GROUPED_K, epi=EPI_F32, bn=256, a_mn=1, b_mn=1, M=M, N=N, K=0, A=a, lda=a.stride(0),
+                    a_inner=M, a_rows=Kc, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=N, b_rows=Kc, b_experts=1,
+                    C=part, ldc=N, c_expert_stride=M * N, num_experts=S, seg_off=seg, beta=0, m_fast=0, cta2=1)
+            _ext.load().sum_partials(part, out, bool(beta))
+            return out
     pair = _use_pair(M, N, bn) and out.stride(0) % 4 == 0 and (pair is not False)
     bn = (128 if N <= 128 else 256) if pair else (bn or (128 if N <= 128 else 256))
     _launch(mode=MODE_DENSE, epi=EPI_F32, bn=bn, a_mn=1, b_mn=1, M=M, N=N, K=Kc, A=a, lda=a.stride(0), a_inner=M,

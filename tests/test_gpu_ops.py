@@ -68,6 +68,26 @@ def test_gemm_nn_and_tn(dev, tile_kind, M, N, K):
     assert relerr(out, at.float().T @ bt.float()) < 1e-5
 
 
+@pytest.mark.parametrize("Kc,M,N", [(8192, 16, 1024), (4096, 128, 512), (12288, 8, 264)])
+def test_gemm_tn_short_wide_output_is_split_along_the_contraction(dev, Kc, M, N):
+    """The router's weight-gradient shape: partial products per contraction segment, summed in a fixed order."""
+    from moe_b200.ops import gemm as G
+
+    torch.manual_seed(2)
+    at, bt = _bf(Kc, M), _bf(Kc, N)
+    assert G._split_k_segments(Kc, at.device) is not None
+    out = torch.randn(M, N, device=dev)
+    ref = out + at.float().T @ bt.float()
+    G.gemm_tn(at, bt, out, beta=1)
+    _sync_status()
+    assert relerr(out, ref) < 1e-5
+    G.gemm_tn(at, bt, out, beta=0)
+    again = torch.empty_like(out)
+    G.gemm_tn(at, bt, again, beta=0)
+    _sync_status()
+    assert relerr(out, at.float().T @ bt.float()) < 1e-5 and torch.equal(out, again)
+
+
 def test_rmsnorm_fwd_bwd(dev):
     from moe_b200.ops import functional as F, oracle
 
