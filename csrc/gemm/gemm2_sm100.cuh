@@ -96,7 +96,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
   __shared__ uint64_t bar_empty[STAGES];  // in each CTA: the pair's MMAs have consumed the stage
   __shared__ uint64_t bar_tfull[2];       // in each CTA: accumulator buffer complete
   __shared__ uint64_t bar_tempty[2];      // used in the even CTA: all 8 epilogue warps of the pair have drained it
-  __shared__ uint64_t bar_in[4][2];       // SwiGLU backward: per epilogue warp and buffer, pre-activation tile landed
+  __shared__ uint64_t bar_in[4][3];       // SwiGLU backward: per epilogue warp and buffer, pre-activation tile landed
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5;
@@ -118,7 +118,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
       mbar_init(&bar_tfull[s], 1);
       mbar_init(&bar_tempty[s], 8);
     }
-    for (int s = 0; s < 8; ++s) mbar_init(&bar_in[s >> 1][s & 1], 1);
+    for (int s = 0; s < 12; ++s) mbar_init(&bar_in[s / 3][s % 3], 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -381,6 +381,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         // fetch the first 64-column piece of the stored pre-activations while the MMAs of the tile still run
         if (live && n0 < args.N && lane == 0) {
           uint64_t* b = &bar_in[q][in_buf];
+          bulk_wait_read<1>();  // the store that last read this buffer (three pieces ago) is done with it
           mbar_expect_tx(b, 8192);
           tma_load_3d(ring + in_buf * 8192, &mapC, b, n0, row0, 0);         // gate columns
           tma_load_3d(ring + in_buf * 8192 + 4096, &mapC, b, n0, row0, 1);  // up columns
@@ -575,8 +576,10 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
           }
         }
       } else if constexpr (EPI == EPI_SWIGLU_BWD) {
-        // ring layout of this warp: [buffer 0: gate, up][buffer 1: gate, up][out: d gate, d up]
-        uint8_t* outb = ring + 16384;
+        // ring of this warp: three buffers [gate 32 x 128 B][up 32 x 128 B].  A piece is loaded into a buffer, its
+        // gradients are written over it in place (every thread overwrites exactly the chunks it has read) and
+        // stored from there, so a buffer is free again once the store issued three pieces ago has read it:
+        // neither the load of the next piece nor the stores ever wait for each other.
         bool ok_in = true;
         float wr = 1.f, rdot = 0.f;
         if (args.row_w != nullptr) {
@@ -590,17 +593,16 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         for (int c = 0; c < BN / 64 && ok_in; ++c) {
           const int cbase = n0 + c * 64;
           if (cbase >= args.N) break;
-          const uint8_t* inb = ring + in_buf * 8192;
+          uint8_t* inb = ring + in_buf * 8192;
+          const int nxt = in_buf == 2 ? 0 : in_buf + 1;
           if (live) {
-            __syncwarp();  // everybody is done reading the other buffer (piece c - 1)
-            if (lane == 0) {
-              if (c + 1 < BN / 64 && cbase + 64 < args.N) {  // next piece of this tile into the other buffer
-                uint64_t* b = &bar_in[q][in_buf ^ 1];
-                mbar_expect_tx(b, 8192);
-                tma_load_3d(ring + (in_buf ^ 1) * 8192, &mapC, b, cbase + 64, row0, 0);
-                tma_load_3d(ring + (in_buf ^ 1) * 8192 + 4096, &mapC, b, cbase + 64, row0, 1);
-              }
-              bulk_wait_read<0>();  // the output tiles of the previous piece have been read by their stores
+            __syncwarp();
+            if (lane == 0 && c + 1 < BN / 64 && cbase + 64 < args.N) {  // next piece of this tile
+              uint64_t* b = &bar_in[q][nxt];
+              bulk_wait_read<1>();  // all stores but the latest have read their buffers: `nxt` is free
+              mbar_expect_tx(b, 8192);
+              tma_load_3d(ring + nxt * 8192, &mapC, b, cbase + 64, row0, 0);
+              tma_load_3d(ring + nxt * 8192 + 4096, &mapC, b, cbase + 64, row0, 1);
             }
             ok_in = mbar_wait(&bar_in[q][in_buf], (in_phase >> in_buf) & 1u);
             in_phase ^= 1u << in_buf;
@@ -641,8 +643,8 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                                       d1 * uf.y * s1 * (1.f + gf.y * (1.f - s1)));
                   ou[i] = pack_bf16x2(d0 * gf.x * s0, d1 * gf.y * s1);
                 }
-                stage_write(outb, lane, h * 4 + j, make_uint4(og[0], og[1], og[2], og[3]));
-                stage_write(outb + 4096, lane, h * 4 + j, make_uint4(ou[0], ou[1], ou[2], ou[3]));
+                stage_write(inb, lane, h * 4 + j, make_uint4(og[0], og[1], og[2], og[3]));
+                stage_write(inb + 4096, lane, h * 4 + j, make_uint4(ou[0], ou[1], ou[2], ou[3]));
               }
             }
           }
@@ -650,11 +652,11 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(&mapX, outb, cbase, row0, 0);         // d(pre-activations) [2][rows][I]: gate
-              tma_store_3d(&mapX, outb + 4096, cbase, row0, 1);  // up
+              tma_store_3d(&mapX, inb, cbase, row0, 0);         // d(pre-activations) [2][rows][I]: gate
+              tma_store_3d(&mapX, inb + 4096, cbase, row0, 1);  // up
               bulk_commit();
             }
-            in_buf ^= 1;
+            in_buf = nxt;
           }
         }
         if (args.row_dot != nullptr && row_ok) args.row_dot[row_g * n_tiles + ti.n_idx] = rdot;

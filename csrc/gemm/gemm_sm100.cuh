@@ -121,7 +121,14 @@ __device__ __forceinline__ void decode_tile(const GemmArgs& a, int t, int m_tile
   }
 }
 
-__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// sigmoid(x) = 0.5 tanh(x / 2) + 0.5: one MUFU instruction (tanh.approx, relative error about 2^-11) where
+// 1 / (1 + exp(-x)) takes an exponential, a reciprocal and the division's refinement steps.  The SwiGLU epilogues
+// are bound by instruction issue, and their results are rounded to bf16 (2^-9) anyway.
+__device__ __forceinline__ float sigmoidf_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(t, 0.5f, 0.5f);
+}
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)

@@ -30,7 +30,8 @@ def tiny_cfg(mtype="standard_moe", **kw):
 
 
 @pytest.mark.parametrize("mtype", ["standard_moe", "global_moe", "deepseek_standard_moe", "deepseek_global_moe",
-                                   "dense", "dense-hd64", "standard_moe-all-experts"])
+                                   "dense", "dense-hd64", "standard_moe-hd64", "standard_moe-all-experts",
+                                   "standard_moe-all-experts-wide"])
 def test_forward_backward_matches_oracle(mtype):
     from moe_b200 import ops
     from moe_b200.models import build_model
@@ -39,8 +40,15 @@ def test_forward_backward_matches_oracle(mtype):
     torch.manual_seed(0)
     extra = {}
     exact = False
-    if mtype == "dense-hd64":  # a head size without an own attention kernel: library attention
+    if mtype == "dense-hd64":  # the attention kernels' head_dim 64 instantiation
         mtype, extra = "dense", dict(head_dim=64)
+    elif mtype == "standard_moe-hd64":
+        mtype, extra = "standard_moe", dict(head_dim=64, num_attention_heads=8, num_key_value_heads=2)
+    elif mtype == "standard_moe-all-experts-wide":
+        # experts wide enough for the pair-tile kernels: routing weight applied in the GEMM epilogues, its
+        # gradient taken from the SwiGLU-backward epilogue
+        mtype, extra, exact = "standard_moe", dict(num_experts=8, num_experts_per_tok=8,
+                                                   moe_intermediate_size=192), True
     elif mtype == "standard_moe-all-experts":
         # every token goes to every expert: no routing decision can differ between bf16 and fp32 scores, so
         # each tensor's gradient has to agree closely (a wrong epilogue on a small tensor cannot hide)
