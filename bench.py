@@ -40,6 +40,10 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=None, help="override sequence length")
     ap.add_argument("--no-overlap", action="store_true", help="reduce gradients after backward, not during")
     ap.add_argument("--ep", action="store_true", help="shard the experts over all ranks (expert parallelism)")
+    ap.add_argument("--no-ep", action="store_true", help="keep every expert on every rank even if the config shards them")
+    ap.add_argument("--ep-local", action="store_true",
+                    help="diagnostic, one GPU: run the expert-parallel code path with a single rank (every row is "
+                         "'sent' to the rank itself), which isolates the local cost of that path")
     ap.add_argument("--no-zero", action="store_true",
                     help="replicate Adam moments and the update on every rank (default for N > 1: sharded, ZeRO-1)")
     ap.add_argument("--fsdp", action="store_true",
@@ -198,6 +202,8 @@ def run_ours(args) -> dict:
     ep_size = int(cfg.get("parallel", {}).get("ep_size", 1) or 1)
     if ep_size < 0 or args.ep:
         ep_size = world
+    if args.no_ep:
+        ep_size = 1
     ep = (rank % ep_size, ep_size) if ep_size > 1 else None
     if ep is not None and ep_size != world:
         raise SystemExit("bench.py runs expert parallelism over all ranks (ep_size == number of GPUs)")
@@ -205,6 +211,21 @@ def run_ours(args) -> dict:
     trainer = Trainer(model, tcfg, is_moe=cfg["model"]["type"] != "dense", overlap_grad_reduce=not args.no_overlap,
                       cuda_graph=not args.no_graph,
                       shard_optimizer=(not args.no_zero) and world > 1 and not args.fsdp, shard_params=args.fsdp)
+    if args.ep_local:
+        if world != 1:
+            raise SystemExit("--ep-local is a one-GPU diagnostic")
+        import torch.distributed as dist
+
+        from moe_b200.parallel.ep import EPContext
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", local))
+        trainer.ep = EPContext(model.config.num_experts, None, trainer.device)
+        for name, p in model.named_parameters():
+            if name.endswith("gate_up_proj"):
+                p._ep = trainer.ep
+        trainer.engine.end_step_hooks.append(trainer.ep.end_step)
     n_params = sum(p.numel() * (ep_size if getattr(p, "_ep_shard", None) else 1) for p in model.parameters())
     K, W = args.steps, args.warmup
     host = make_batches(W + 2 * K, B, S, V, rank, cfg["data"].get("seed", 0))

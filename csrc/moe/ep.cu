@@ -114,18 +114,28 @@ ep_exchange_kernel(const int* __restrict__ counts, EpPeers cmat /* int [W][E] pe
     }
     *recv_num_pair_tiles = np;
   }
-  // zero the padding rows (they enter the weight-gradient contraction) and mark them as sourceless
+}
+
+// Zero the padding rows of every local expert segment (they enter the weight-gradient contraction) and mark them
+// as sourceless.  One block per local expert: the ranges are rebuilt from the (by now complete) count matrix, so
+// the layout kernel above, which is a single block on the critical path, does not have to touch the rows.
+__global__ void ep_pad_zero_kernel(const int* __restrict__ cm /* this rank's int [W][E] */,
+                                   const int* __restrict__ recv_seg_off, int rank, int world, int E, int H,
+                                   int capacity, __nv_bfloat16* __restrict__ recv_buf, int* __restrict__ recv_meta) {
+  const int El = E / world;
+  const int el = blockIdx.x;
+  if (el >= El || recv_seg_off[El] > capacity) return;  // refused step: nothing will be read
+  const int e = rank * El + el;
+  int tot = 0;
+  for (int s = 0; s < world; ++s) tot += ld_relaxed_sys(cm + s * E + e);
+  const int lo = recv_seg_off[el] + tot, hi = recv_seg_off[el] + (tot + 127) / 128 * 128;
+  if (lo < 0 || hi > capacity) return;
   const int nch = H >> 3;
-  for (int el = 0; el < El; ++el) {
-    const int e = rank * El + el;
-    const int lo = seg[e] + tot[e], hi = seg[e] + (tot[e] + 127) / 128 * 128;
-    if (hi > total_rows) break;
-    for (int i = threadIdx.x; i < (hi - lo) * nch; i += blockDim.x) {
-      const int r = lo + i / nch, c = i - (i / nch) * nch;
-      reinterpret_cast<uint4*>(recv_buf + static_cast<size_t>(r) * H)[c] = make_uint4(0, 0, 0, 0);
-    }
-    for (int r = lo + threadIdx.x; r < hi; r += blockDim.x) recv_meta[r] = -1;
+  for (int i = threadIdx.x; i < (hi - lo) * nch; i += blockDim.x) {
+    const int r = lo + i / nch, c = i - (i / nch) * nch;
+    reinterpret_cast<uint4*>(recv_buf + static_cast<size_t>(r) * H)[c] = make_uint4(0, 0, 0, 0);
   }
+  for (int r = lo + threadIdx.x; r < hi; r += blockDim.x) recv_meta[r] = -1;
 }
 
 // Push rows to their expert owners.  src row of assignment i is rows[i / K] (scaled by scale[i] if given).
@@ -204,6 +214,9 @@ extern "C" int b200_ep_exchange(const int* counts, void* const* cmat, void* cons
                                                 rank, world, E, H, capacity, send_base, recv_seg_off, recv_tile_expert,
                                                 recv_num_m_tiles, reinterpret_cast<__nv_bfloat16*>(recv_buf), recv_meta,
                                                 status, limit_ns, recv_pair_tiles, max_pairs, recv_num_pair_tiles);
+  ep_pad_zero_kernel<<<E / world, 256, 0, stream>>>(reinterpret_cast<const int*>(cmat[rank]), recv_seg_off, rank, world,
+                                                   E, H, capacity, reinterpret_cast<__nv_bfloat16*>(recv_buf),
+                                                   recv_meta);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

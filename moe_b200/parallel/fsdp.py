@@ -172,6 +172,7 @@ class FsdpEngine(TrainEngine):
         self._hyper_next = 0
         self._coef_ep = torch.ones(1, dtype=torch.float32, device=dev)
         self._ss_scratch = torch.empty(self._ext.sumsq_blocks(max(self.p32.numel(), 1)), dtype=torch.float32, device=dev)
+        self._ss_scratch_comm = torch.empty_like(self._ss_scratch)  # for sums taken on the communication stream
         self._fused_ar = None
         self._comm_stream = torch.cuda.Stream(device=dev)
         self._gather_stream = torch.cuda.Stream(device=dev)
@@ -188,6 +189,7 @@ class FsdpEngine(TrainEngine):
         self._grad_norm = None
         self._pending = []
         self.accumulating = False
+        self._accum_step = False  # this step has reduced a layer unit for more than one micro-batch
         self._micro = 0            # micro-batches reduced into the gradient shard so far this step
         self._root_ready = False   # root unit gathered for the current parameter version
         self._in_backward_of = None
@@ -343,9 +345,15 @@ class FsdpEngine(TrainEngine):
         valid = max(0, min(u.per, u.n - u.per * self.rank))
         with torch.cuda.stream(cs):
             cs.wait_event(ev)
+            # With several micro-batches a layer unit is reduced once per micro-batch and the reduced slices are
+            # added up in the gradient shard: the norm that clipping needs is that of the sum, so these reduces
+            # do not count and `reduce_gradients` takes the squared norm of the accumulated shard instead.
+            split = u is not self.root and (self.accumulating or self._accum_step)
+            if split:
+                self._accum_step = True
             if self._fused_ar is not None:
-                self._fused_ar.reduce(u.g_off, u.n, final, publish=False)
-            else:
+                self._fused_ar.reduce(u.g_off, u.n, final, publish=False, count_norm=not split)
+            elif not split:
                 self._ext.sumsq(self.g32[u.g_off:u.g_off + u.n], self._ss_scratch, self._norm_ss, True)
             if valid > 0:
                 if self._micro == 0 or u is self.root:
@@ -366,6 +374,7 @@ class FsdpEngine(TrainEngine):
             s.param._grad_live = False
             s.param.grad = None
         self._micro = 0
+        self._accum_step = False
         self._norm_ss.zero_()
         self._pending = []
         self.begin_step()
@@ -380,6 +389,8 @@ class FsdpEngine(TrainEngine):
         tail = self.total > self.ep_end
         if self.has_ep:
             self._account_ep_norm_local()
+        if self._accum_step:
+            self._account_accumulated_units()
         self._reduce_unit(self.root, final=not tail and self._fused_ar is not None)
         if tail:
             self._zero_dead(self.ep_end, self.total)
@@ -399,6 +410,20 @@ class FsdpEngine(TrainEngine):
             self._fused_ar.end_step()
         for hook in self.end_step_hooks:
             hook()
+
+    def _account_accumulated_units(self) -> None:
+        """Squared norm of the layer units' accumulated (already averaged) gradient shards; on the communication
+        stream, after the last unit's reduce-scatter and its add into the shard."""
+        with torch.cuda.stream(self._comm_stream):
+            ss = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for u in self.ring_units:
+                valid = max(0, min(u.per, u.n - u.per * self.rank))
+                if valid > 0:
+                    self._ext.sumsq(self.gshard[u.soff:u.soff + valid], self._ss_scratch_comm, ss, True)
+            if self._fused_ar is not None:
+                self._fused_ar.state_f[1:2].add_(ss)
+            else:
+                self._norm_ss.add_(ss)
 
     def _account_ep_norm_local(self) -> None:
         """Expert-parallel shards are complete locally; their share of the squared norm joins the running sum."""

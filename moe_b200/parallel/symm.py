@@ -121,11 +121,19 @@ class FusedAllReduce:
         # CTAs of the reduce kernel: enough loads in flight for NVLink, few enough to leave the SMs to backward
         self.blocks, self.limit_ns = int(os.environ.get("MOE_B200_AR_BLOCKS", blocks)), limit_ns
         self.launched = 0  # buckets since the last `end_step`
+        self._scratch_f = None
 
-    def reduce(self, off: int, n: int, final_bucket: bool, publish: bool = True) -> None:
+    def reduce(self, off: int, n: int, final_bucket: bool, publish: bool = True, count_norm: bool = True) -> None:
+        """`count_norm=False`: the bucket's squared norm goes to a scratch accumulator (the caller accounts for
+        these gradients itself, e.g. after adding several micro-batches' reduced slices)."""
+        if not count_norm and final_bucket:
+            raise ValueError("the final bucket publishes the norm and must count")
+        if not count_norm and self._scratch_f is None:
+            self._scratch_f = torch.zeros_like(self.state_f)
         self.ext.allreduce(self.grad_ptrs, self.flag_ptrs, self.norm_ptrs, self.mc, self.rank, self.world, off, n,
                            1.0 / self.world, self.epoch_base, self.launched, final_bucket, publish, self.mc != 0,
-                           self.blocks, self.state_i, self.state_f, self.status, self.limit_ns)
+                           self.blocks, self.state_i, self.state_f if count_norm else self._scratch_f, self.status,
+                           self.limit_ns)
         self.launched += 1
 
     def param_barrier(self) -> None:

@@ -165,6 +165,9 @@ class Trainer:
         cs.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(cs):
             self._forward_backward(self._static_in)
+            # close the dry run's gradient phase as a step would (no update): the bucket reduces it launched
+            # have added to the running squared norm and taken flag epochs, which the final reduce settles
+            self.engine.reduce_gradients()
             for c, sv in zip(counters, saved):
                 c.copy_(sv)
         torch.cuda.current_stream(self.device).wait_stream(cs)

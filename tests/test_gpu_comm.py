@@ -457,7 +457,7 @@ def test_two_gpu_sharded_parameters_match_replicated_training(tmp_path):
             d = (full - ref).abs()
             assert d.max() < 5e-3 and (d > 2e-4).float().mean() < 2e-2, (mtype, name, float(d.max()),
                                                                          float((d > 2e-4).float().mean()))
-            for x, y in zip(norms, ref_norms):
-                assert abs(x - y) < 3e-2 * y, (mtype, name, norms, ref_norms)
+            for x, y in zip(norms, ref_norms):  # tight: a norm taken per micro-batch or over stale sums is off by more
+                assert abs(x - y) < 3e-3 * y, (mtype, name, norms, ref_norms)
             for x, y in zip(losses, ref_losses):
                 assert abs(x - y) < 1e-2 * abs(y), (mtype, name, losses, ref_losses)
