@@ -125,14 +125,14 @@ template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int grid,
                       cudaStream_t stream) {
   auto kern = gemm_sm100_kernel<BN, A_MN, B_MN, EPI>;
+  constexpr int smem = EPI == EPI_BF16_SCATTER ? GemmCfg<BN>::SMEM_BYTES_SCATTER : GemmCfg<BN>::SMEM_BYTES;
+  static_assert(smem <= 232448, "dynamic shared memory of one CTA");
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES) !=
-        cudaSuccess)
-      return -10;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -10;
     configured = true;
   }
-  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(ma, mb, args);
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(ma, mb, args);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

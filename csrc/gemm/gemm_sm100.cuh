@@ -91,6 +91,8 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  // the row-scatter epilogue stages 32 rows x 256 bytes per epilogue warp behind the operand ring
+  static constexpr int SMEM_BYTES_SCATTER = SMEM_BYTES + 4 * 8192;
 };
 
 __device__ __forceinline__ void decode_tile(const GemmArgs& a, int t, int m_tiles, int n_tiles, TileInfo& ti) {
@@ -343,6 +345,43 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
         if (live)
           crow = reinterpret_cast<__nv_bfloat16*>(args.ep.scatter_dst[(meta >> 28) & 7]) +
                  static_cast<long long>(meta & 0x0fffffff) * args.ldc;
+        if ((args.N & 127) == 0) {
+          // Whole-row pieces: the warp's 32 rows x 128 columns are staged in shared memory (lane = row on the way in),
+          // then every store instruction writes two rows' 256 contiguous bytes (16 lanes x 16 B per row), so a peer
+          // receives 256-byte runs instead of one 16-byte fragment per lane and row.
+          uint8_t* stg = tiles + STAGES * Cfg::STAGE_BYTES + q * 8192;
+          const unsigned long long cptr = reinterpret_cast<unsigned long long>(crow);
+#pragma unroll 1
+          for (int g = 0; g < BN / 128; ++g) {
+            const int colg = n0 + g * 128;
+            if (colg >= args.N) break;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_acc + g * 128 + c4 * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int k = c4 * 4 + j;  // 16-byte chunk of the row, swizzled by the row so that lanes spread over banks
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((k ^ (lane & 15)) << 4)) =
+                    make_uint4(pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                               pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                               pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                               pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+              }
+            }
+            __syncwarp();
+            const int k = lane & 15;
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+              const int row = 2 * i + (lane >> 4);
+              const unsigned long long base = __shfl_sync(0xffffffffu, cptr, row);
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * 256 + ((k ^ (row & 15)) << 4));
+              if (base != 0ull) reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + colg)[k] = v;
+            }
+            __syncwarp();  // the staging buffer is rewritten by the next group
+          }
+        } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           const int col0 = n0 + c * 32;
@@ -365,6 +404,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constan
                 if (col0 + j < args.N) crow[col0 + j] = __float2bfloat16(__uint_as_float(r[j]));
             }
           }
+        }
         }
       } else if constexpr (EPI == EPI_BF16 || EPI == EPI_LSE) {
         __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(args.C) + row_g * args.ldc;
