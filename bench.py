@@ -292,7 +292,7 @@ def run_ours(args) -> dict:
                    "params": n_params, "global_batch": B * world, "micro_batch_per_gpu": B, "seq_len": S,
                    "parallelism": par, "optimizer": "AdamW, clip 1.0, warmup+cosine",
                    "activation_checkpointing": bool(tcfg.gradient_checkpointing),
-                   "l2": "per-step working set (GBs of weights, activations, 5 GB of logits) is far larger than "
+                   "l2": "per-step working set (GBs of weights and activations, 1.2 GB of logits per chunk) is far larger than "
                          "the 126 MB L2; no explicit flush"},
         "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / K, "h2d_bytes_per_step": B * S * 8,
                 "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
