@@ -137,6 +137,25 @@ def case_qknorm_rope(small):
     return dict(shape=[B, S, nh, nkv, hd], ms=ms, bytes=2.0 * qkv.numel() * 2)
 
 
+def case_qknorm_rope_fwd_bwd(small):
+    from moe_b200.ops import functional as F
+
+    B, S, nh, nkv, hd = (2, 2048, 16, 8, 128) if small else (8, 2048, 16, 8, 128)
+    qkv = bf(B, S, (nh + 2 * nkv) * hd).requires_grad_()
+    qw = torch.ones(hd, device="cuda", requires_grad=True)
+    kw = torch.ones(hd, device="cuda", requires_grad=True)
+    gq, gk, gv = bf(B, S, nh, hd), bf(B, S, nkv, hd), bf(B, S, nkv, hd)
+
+    def run():
+        q, k, v = F.qk_norm_rope(qkv, qw, kw, B, S, nh, nkv, hd, 1e6, 1e-6)
+        torch.autograd.backward((q, k, v), (gq.view_as(q), gk.view_as(k), gv.view_as(v)))
+        qkv.grad = qw.grad = kw.grad = None
+
+    ms = timeit(run)
+    # forward reads qkv and writes q, k, v; backward reads the three gradients and the q / k inputs, writes d(qkv)
+    return dict(shape=[B, S, nh, nkv, hd], ms=ms, bytes=(2.0 + 2.75) * qkv.numel() * 2)
+
+
 def case_flash_attn_fwd(small, hd=128):
     import math
 
