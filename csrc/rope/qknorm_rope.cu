@@ -157,20 +157,15 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
     __nv_bfloat16* drow = dqkv + static_cast<size_t>(t) * ld + li * 8;
     for (int p0 = 0; p0 < passes; p0 += U) {
       uint4 graw[U], xraw[U];
-      float rs[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int h = (p0 + u) * L::HPW + sub;
-        rs[u] = 0.f;
         if (p0 + u < passes && h < nall) {
           const __nv_bfloat16* gsrc = h < nh    ? dq + (static_cast<size_t>(t) * nh + h) * HD
                                       : h < nqk ? dk + (static_cast<size_t>(t) * nkv + (h - nh)) * HD
                                                 : dv + (static_cast<size_t>(t) * nkv + (h - nqk)) * HD;
           graw[u] = *reinterpret_cast<const uint4*>(gsrc + li * 8);
-          if (h < nqk) {
-            xraw[u] = *reinterpret_cast<const uint4*>(row + h * HD);
-            rs[u] = rstd_in[t * nqk + h];
-          }
+          if (h < nqk) xraw[u] = *reinterpret_cast<const uint4*>(row + h * HD);
         }
       }
 #pragma unroll
@@ -189,7 +184,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
 #pragma unroll
           for (int i = 0; i < 8; ++i) g[i] = x[i] = 0.f;
         }
-        const float rstd = qk ? rs[u] : 0.f;
+        const float rstd = qk ? rstd_in[t * nqk + h] : 0.f;
         float xh[8], wd[8];
         float dot = 0.f;
 #pragma unroll
