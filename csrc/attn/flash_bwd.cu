@@ -644,16 +644,24 @@ using namespace b200;
 template <int HD>
 static int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                             const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int nh,
-                            int nkv, float softmax_scale, int* status, cudaStream_t stream) {
+                            int nkv, long long ldq, long long ldk, long long ldv, float softmax_scale, int* status,
+                            cudaStream_t stream) {
   CUtensorMap mq, mk, mv, mdo, mq64, mdo64;
   const uint64_t qrow = static_cast<uint64_t>(nh) * HD, krow = static_cast<uint64_t>(nkv) * HD;
-  int rc = make_map(&mq, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
-  if (rc == 0) rc = make_map(&mdo, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
-  if (rc == 0) rc = make_map(&mk, k, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
-  if (rc == 0) rc = make_map(&mv, v, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
-  if (rc == 0) rc = make_map(&mq64, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 64);
-  if (rc == 0) rc = make_map(&mdo64, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 64);
+  const uint64_t pq = (ldq > 0 ? ldq : qrow) * 2, pk = (ldk > 0 ? ldk : krow) * 2, pv = (ldv > 0 ? ldv : krow) * 2;
+  // a failing map is reported as -(100 + 10 * its position + the encoder's code)
+  int rc = make_map(&mq, q, qrow, S, B, pq, pq * S, 64, 128);
   if (rc != 0) return rc - 100;
+  rc = make_map(&mdo, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
+  if (rc != 0) return rc - 110;
+  rc = make_map(&mk, k, krow, S, B, pk, pk * S, 64, 128);
+  if (rc != 0) return rc - 120;
+  rc = make_map(&mv, v, krow, S, B, pv, pv * S, 64, 128);
+  if (rc != 0) return rc - 130;
+  rc = make_map(&mq64, q, qrow, S, B, pq, pq * S, 64, 64);
+  if (rc != 0) return rc - 140;
+  rc = make_map(&mdo64, d_o, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 64);
+  if (rc != 0) return rc - 150;
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
@@ -690,11 +698,14 @@ static int launch_flash_bwd(const void* q, const void* k, const void* v, const v
 
 extern "C" int b200_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                               const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int nh,
-                              int nkv, int head_dim, float softmax_scale, int* status, cudaStream_t stream) {
+                              int nkv, int head_dim, long long ldq, long long ldk, long long ldv, float softmax_scale,
+                              int* status, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
   if (head_dim == 128)
-    return launch_flash_bwd<128>(q, k, v, o, d_o, lse, delta, dq, dk, dv, B, S, nh, nkv, softmax_scale, status, stream);
+    return launch_flash_bwd<128>(q, k, v, o, d_o, lse, delta, dq, dk, dv, B, S, nh, nkv, ldq, ldk, ldv, softmax_scale, status,
+                                 stream);
   if (head_dim == 64)
-    return launch_flash_bwd<64>(q, k, v, o, d_o, lse, delta, dq, dk, dv, B, S, nh, nkv, softmax_scale, status, stream);
+    return launch_flash_bwd<64>(q, k, v, o, d_o, lse, delta, dq, dk, dv, B, S, nh, nkv, ldq, ldk, ldv, softmax_scale, status,
+                                stream);
   return -3;
 }

@@ -464,12 +464,15 @@ using namespace b200;
 
 template <int HD>
 static int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int nh,
-                            int nkv, float softmax_scale, int* status, cudaStream_t stream) {
+                            int nkv, long long ldq, long long ldk, long long ldv, float softmax_scale, int* status,
+                            cudaStream_t stream) {
   CUtensorMap mq, mk, mv;
   const uint64_t qrow = static_cast<uint64_t>(nh) * HD, krow = static_cast<uint64_t>(nkv) * HD;
-  int rc = make_map(&mq, q, qrow, S, B, qrow * 2, qrow * 2 * S, 64, 128);
-  if (rc == 0) rc = make_map(&mk, k, krow, S, B, krow * 2, krow * 2 * S, 64, 128);
-  if (rc == 0) rc = make_map(&mv, v, krow, S, B, krow * 2, krow * 2 * S, 64, 64);
+  // row pitch of each operand in bytes (a token's heads are contiguous; tokens may be further apart)
+  const uint64_t pq = (ldq > 0 ? ldq : qrow) * 2, pk = (ldk > 0 ? ldk : krow) * 2, pv = (ldv > 0 ? ldv : krow) * 2;
+  int rc = make_map(&mq, q, qrow, S, B, pq, pq * S, 64, 128);
+  if (rc == 0) rc = make_map(&mk, k, krow, S, B, pk, pk * S, 64, 128);
+  if (rc == 0) rc = make_map(&mv, v, krow, S, B, pv, pv * S, 64, 64);
   if (rc != 0) return rc - 100;
   static bool configured = false;
   static int sms = 0;
@@ -495,10 +498,11 @@ static int launch_flash_fwd(const void* q, const void* k, const void* v, void* o
 }
 
 extern "C" int b200_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int S, int nh,
-                              int nkv, int head_dim, float softmax_scale, int* status, cudaStream_t stream) {
+                              int nkv, int head_dim, long long ldq, long long ldk, long long ldv, float softmax_scale,
+                              int* status, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || (S & 127) != 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0) return -1;
   if (((nh / nkv) & 1) != 0) return -2;  // two query heads of one CTA must share their key/value head
-  if (head_dim == 128) return launch_flash_fwd<128>(q, k, v, o, lse, B, S, nh, nkv, softmax_scale, status, stream);
-  if (head_dim == 64) return launch_flash_fwd<64>(q, k, v, o, lse, B, S, nh, nkv, softmax_scale, status, stream);
+  if (head_dim == 128) return launch_flash_fwd<128>(q, k, v, o, lse, B, S, nh, nkv, ldq, ldk, ldv, softmax_scale, status, stream);
+  if (head_dim == 64) return launch_flash_fwd<64>(q, k, v, o, lse, B, S, nh, nkv, ldq, ldk, ldv, softmax_scale, status, stream);
   return -3;
 }

@@ -36,7 +36,9 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
              const std::vector<int64_t>& ep_post_flags, int64_t ep_post_index, int64_t ep_post_epoch_off,
              int64_t ep_world, const OptT& ep_counter, int64_t cta2, const OptT& pair_tiles,
              int64_t ep_limit_ns, const OptT& a_gather, const OptT& b_gather, const OptT& row_slot,
-             const OptT& row_w, const OptT& row_dot) {
+             const OptT& row_w, const OptT& row_dot, const OptT& rope_cs, const OptT& rope_w, const OptT& rope_kw,
+             const OptT& rope_rstd,
+             int64_t rope_S, int64_t rope_nh, int64_t rope_nkv, double rope_eps) {
   check_cuda(A, "A");
   check_cuda(B, "B");
   check_cuda(C, "C");
@@ -82,6 +84,20 @@ int64_t gemm(int64_t mode, int64_t epi, int64_t bn, int64_t a_mn, int64_t b_mn, 
     TORCH_CHECK(row_slot->scalar_type() == at::kInt && row_slot->numel() >= M, "row_slot: int32, one entry per row");
   if (d.row_w != nullptr) TORCH_CHECK(row_w->scalar_type() == at::kFloat, "row_w must be fp32");
   if (d.row_dot != nullptr) TORCH_CHECK(row_dot->scalar_type() == at::kFloat, "row_dot must be fp32");
+  d.rope_cs = ptr_or_null<const float>(rope_cs);
+  d.rope_w = ptr_or_null<const float>(rope_w);
+  d.rope_kw = ptr_or_null<const float>(rope_kw);
+  d.rope_rstd = ptr_or_null<float>(rope_rstd);
+  d.rope_S = (int)rope_S; d.rope_nh = (int)rope_nh; d.rope_nkv = (int)rope_nkv; d.rope_eps = (float)rope_eps;
+  if (epi == 6) {
+    TORCH_CHECK(d.rope_cs && d.rope_w && d.rope_kw && d.rope_rstd,
+                "fused QKV epilogue: rope_cs, rope_w, rope_kw and rope_rstd are required");
+    TORCH_CHECK(rope_cs->scalar_type() == at::kFloat && rope_cs->numel() >= rope_S * 128 &&
+                    rope_w->scalar_type() == at::kFloat && rope_w->numel() >= 128 &&
+                    rope_kw->scalar_type() == at::kFloat && rope_kw->numel() >= 128 &&
+                    rope_rstd->scalar_type() == at::kFloat && rope_rstd->numel() >= M * (rope_nh + rope_nkv),
+                "fused QKV epilogue: fp32 table [S,64,2], weights [128] each, rstd [M, nh+nkv]");
+  }
   d.cta2 = (int)cta2;
   d.pair_tiles = ptr_or_null<const int>(pair_tiles);
   d.max_pair_tiles = pair_tiles.has_value() && pair_tiles->defined() ? (int)(pair_tiles->numel() / 2) : 0;
@@ -109,6 +125,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("ep_post_epoch_off") = 0, py::arg("ep_world") = 0, py::arg("ep_counter") = py::none(),
         py::arg("cta2") = 0, py::arg("pair_tiles") = py::none(), py::arg("ep_limit_ns") = 0,
         py::arg("a_gather") = py::none(), py::arg("b_gather") = py::none(), py::arg("row_slot") = py::none(),
-        py::arg("row_w") = py::none(), py::arg("row_dot") = py::none());
+        py::arg("row_w") = py::none(), py::arg("row_dot") = py::none(), py::arg("rope_cs") = py::none(),
+        py::arg("rope_w") = py::none(), py::arg("rope_kw") = py::none(), py::arg("rope_rstd") = py::none(),
+        py::arg("rope_S") = 0,
+        py::arg("rope_nh") = 0, py::arg("rope_nkv") = 0, py::arg("rope_eps") = 0.0);
   bind_ops(m);
 }

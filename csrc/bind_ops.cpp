@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include "ops_api.h"
+#include "common/tma_host.h"
 #include "attn/attn_api.h"
 
 #include <cstring>
@@ -25,13 +26,26 @@ void need(bool ok, const char* what) { TORCH_CHECK(ok, "moe_b200: ", what); }
 void bf16c(const Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), n, ": contiguous CUDA bf16 expected");
 }
+// [B,S,h,hd] bf16 whose heads are contiguous per token while tokens may be further apart (a slice of a wider row);
+// returns the token pitch in elements
+int64_t bf16_rows4(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 4, n, ": 4-D CUDA bf16 expected");
+  TORCH_CHECK(t.stride(3) == 1 && t.stride(2) == t.size(3) && t.stride(1) >= t.size(2) * t.size(3) &&
+                  (t.size(0) == 1 || t.stride(0) == t.stride(1) * t.size(1)) && t.stride(1) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+              n, ": heads must be contiguous per token, tokens evenly spaced, 16-byte aligned");
+  return t.stride(1);
+}
 void f32c(const Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), n, ": contiguous CUDA fp32 expected");
 }
 void i32c(const Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), n, ": contiguous CUDA int32 expected");
 }
-void rc_ok(int rc, const char* fn) { TORCH_CHECK(rc == 0, fn, " rejected its arguments (code ", rc, ")"); }
+void rc_ok(int rc, const char* fn) {
+  TORCH_CHECK(rc == 0, fn, " rejected its arguments (code ", rc, ", last tensor-map encode result ",
+              b200::tma_last_encode_result(), ")");
+}
 
 // ------------------------------------------------------------------ rmsnorm
 void rmsnorm_fwd(const Tensor& x, const OptT& res, const Tensor& w, const OptT& h_out, Tensor& y, const OptT& rstd,
@@ -89,7 +103,8 @@ void qknorm_rope_bwd(const Tensor& dq, const Tensor& dk, const Tensor& dv, const
 
 // ---------------------------------------------------------------- attention
 void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse, double scale, Tensor& status) {
-  bf16c(q, "q"); bf16c(k, "k"); bf16c(v, "v"); bf16c(o, "o"); f32c(lse, "lse"); i32c(status, "status");
+  const int64_t ldq = bf16_rows4(q, "q"), ldk = bf16_rows4(k, "k"), ldv = bf16_rows4(v, "v");
+  bf16c(o, "o"); f32c(lse, "lse"); i32c(status, "status");
   need(q.dim() == 4 && k.dim() == 4 && (q.size(3) == 128 || q.size(3) == 64) && k.size(3) == q.size(3),
        "flash attention: [B,S,h,128] or [B,S,h,64] expected");
   need(k.sizes() == v.sizes() && o.sizes() == q.sizes(), "flash attention: shape mismatch");
@@ -98,12 +113,13 @@ void flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Ten
   need(lse.numel() == (int64_t)B * nh * S, "flash attention: lse size");
   c10::cuda::CUDAGuard g(q.device());
   rc_ok(b200_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, S, nh, nkv,
-                       (int)q.size(3), (float)scale, status.data_ptr<int>(), stream()), "flash_fwd");
+                       (int)q.size(3), ldq, ldk, ldv, (float)scale, status.data_ptr<int>(), stream()), "flash_fwd");
 }
 
 void flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
                Tensor& delta, Tensor& dq, Tensor& dk, Tensor& dv, double scale, Tensor& status) {
-  bf16c(q, "q"); bf16c(k, "k"); bf16c(v, "v"); bf16c(o, "o"); bf16c(d_o, "d_o"); f32c(lse, "lse"); f32c(delta, "delta");
+  const int64_t ldq = bf16_rows4(q, "q"), ldk = bf16_rows4(k, "k"), ldv = bf16_rows4(v, "v");
+  bf16c(o, "o"); bf16c(d_o, "d_o"); f32c(lse, "lse"); f32c(delta, "delta");
   bf16c(dq, "dq"); bf16c(dk, "dk"); bf16c(dv, "dv"); i32c(status, "status");
   need(q.dim() == 4 && k.dim() == 4 && (q.size(3) == 128 || q.size(3) == 64) && k.size(3) == q.size(3),
        "flash attention: [B,S,h,128] or [B,S,h,64] expected");
@@ -114,7 +130,7 @@ void flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& 
   c10::cuda::CUDAGuard g(q.device());
   rc_ok(b200_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
                        delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, S, nh, nkv, (int)q.size(3),
-                       (float)scale, status.data_ptr<int>(), stream()), "flash_bwd");
+                       ldq, ldk, ldv, (float)scale, status.data_ptr<int>(), stream()), "flash_bwd");
 }
 
 // ------------------------------------------------------------------- router

@@ -11,4 +11,7 @@ namespace b200 {
 int make_map(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes,
              uint64_t s2_bytes, uint32_t b0, uint32_t b1);
 
+// CUresult of the last encode that failed (0 if none has): part of the error text of the entry points
+int tma_last_encode_result();
+
 }  // namespace b200

@@ -28,7 +28,7 @@ struct Gemm2Cfg {
   // 4 KB staging buffers (32 rows x 128 B) per epilogue warp.  The SwiGLU backward also stages its INPUT
   // (the stored pre-activations) through shared memory: two double-buffered 4 KB tiles (gate, up) that TMA
   // fetches one 64-column piece ahead, plus two output tiles.
-  static constexpr int RING = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD) ? 6 : 2;
+  static constexpr int RING = (EPI == EPI_SWIGLU) ? 3 : (EPI == EPI_SWIGLU_BWD) ? 6 : (EPI == EPI_QKROPE) ? 4 : 2;
   static constexpr int EPI_BYTES = 4 * RING * 4096;
   static constexpr int STAGES_FIT = (232448 - 1024 - 512 - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
@@ -485,6 +485,111 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
           if (row_ok) {
             float2* part = reinterpret_cast<float2*>(args.aux0);
             part[row_g * n_tiles + ti.n_idx] = make_float2(run_max, run_sum);
+          }
+        }
+      } else if constexpr (EPI == EPI_QKROPE) {
+        // A 256-column tile is two heads of 128.  Per head: (a) the raw projection goes out as in the bf16 epilogue
+        // while the sum of squares of the stored (bf16-rounded) values is taken; (b) for q and k heads the columns
+        // are read from TMEM again in rotate-half pairs (i, i + 64), normalised, weighted and rotated, and the
+        // result is stored to the second output; v heads are copied there from the same staging buffers.
+        const int nqk = args.rope_nh + args.rope_nkv;
+        const int pos = row_ok ? static_cast<int>(row_g % args.rope_S) : 0;
+#pragma unroll 1
+        for (int hh = 0; hh < BN / 128; ++hh) {
+          const int cb = n0 + hh * 128;
+          if (cb >= args.N) break;
+          const int head = cb >> 7;
+          const bool is_v = head >= nqk;
+          float ss = 0.f;
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            uint8_t* buf = ring + slot * 4096;
+            if (live) {
+              if (lane == 0) bulk_wait_read<RING - 1>();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int c2 = 0; c2 < 2; ++c2) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_acc + hh * 128 + half * 64 + c2 * 32, r);
+              tmem_ld_wait();
+              uint32_t p[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                p[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                const float2 f = unpack_bf16x2(p[j]);
+                ss = fmaf(f.x, f.x, ss);
+                ss = fmaf(f.y, f.y, ss);
+              }
+              if (live) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  stage_write(buf, lane, c2 * 4 + j, make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]));
+              }
+            }
+            if (live) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&mapC, buf, cb + half * 64, row0, 0);
+                if (is_v) tma_store_3d(&mapX, buf, cb + half * 64, row0, 0);
+                bulk_commit();
+              }
+              slot = (slot + 1 == RING) ? 0 : slot + 1;
+            }
+          }
+          if (is_v) continue;
+          const float rstd = rsqrtf(ss * (1.0f / 128.0f) + args.rope_eps);
+          if (row_ok) args.rope_rstd[row_g * nqk + head] = rstd;
+          const float* wv = head < args.rope_nh ? args.rope_w : args.rope_kw;
+          const float* csr = args.rope_cs + static_cast<size_t>(pos) * 128;  // 64 (cos, sin) pairs
+          uint8_t* buf_lo = ring + slot * 4096;
+          const int slot_hi = (slot + 1 == RING) ? 0 : slot + 1;
+          uint8_t* buf_hi = ring + slot_hi * 4096;
+          if (live) {
+            if (lane == 0) bulk_wait_read<RING - 2>();
+            __syncwarp();
+          }
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t lo[32], hi[32];
+            tmem_ld_32x32(t_acc + hh * 128 + c * 32, lo);
+            tmem_ld_32x32(t_acc + hh * 128 + 64 + c * 32, hi);
+            tmem_ld_wait();
+            uint32_t plo[16], phi[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int i = c * 32 + 2 * j;  // frequency index of the pair's first element
+              // values as stored (bf16), normalised and rounded again, then weighted: the unfused module sequence
+              const float2 xl = unpack_bf16x2(pack_bf16x2(__uint_as_float(lo[2 * j]), __uint_as_float(lo[2 * j + 1])));
+              const float2 xh = unpack_bf16x2(pack_bf16x2(__uint_as_float(hi[2 * j]), __uint_as_float(hi[2 * j + 1])));
+              const float2 nl = unpack_bf16x2(pack_bf16x2(xl.x * rstd, xl.y * rstd));
+              const float2 nh2 = unpack_bf16x2(pack_bf16x2(xh.x * rstd, xh.y * rstd));
+              const float2 wl = *reinterpret_cast<const float2*>(wv + i);
+              const float2 wh = *reinterpret_cast<const float2*>(wv + 64 + i);
+              const float4 cs4 = *reinterpret_cast<const float4*>(csr + 2 * i);  // cos_i, sin_i, cos_i+1, sin_i+1
+              const float l0 = nl.x * wl.x, l1 = nl.y * wl.y, h0 = nh2.x * wh.x, h1 = nh2.y * wh.y;
+              plo[j] = pack_bf16x2(l0 * cs4.x - h0 * cs4.y, l1 * cs4.z - h1 * cs4.w);
+              phi[j] = pack_bf16x2(h0 * cs4.x + l0 * cs4.y, h1 * cs4.z + l1 * cs4.w);
+            }
+            if (live) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                stage_write(buf_lo, lane, c * 4 + j, make_uint4(plo[4 * j], plo[4 * j + 1], plo[4 * j + 2], plo[4 * j + 3]));
+                stage_write(buf_hi, lane, c * 4 + j, make_uint4(phi[4 * j], phi[4 * j + 1], phi[4 * j + 2], phi[4 * j + 3]));
+              }
+            }
+          }
+          if (live) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&mapX, buf_lo, cb, row0, 0);
+              bulk_commit();
+              tma_store_3d(&mapX, buf_hi, cb + 64, row0, 0);
+              bulk_commit();
+            }
+            slot = (slot_hi + 1 == RING) ? 0 : slot_hi + 1;
           }
         }
       } else if constexpr (EPI == EPI_F32) {

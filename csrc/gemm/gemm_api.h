@@ -9,7 +9,8 @@ extern "C" {
 // Problem modes / epilogues: numeric values match b200::GemmMode / b200::GemmEpi.
 typedef struct B200GemmDesc {
   int mode;  // 0 dense, 1 grouped by rows (padded expert segments), 2 grouped by contraction (per-expert dW)
-  int epi;   // 0 bf16, 1 fp32 (beta), 2 swiglu, 3 swiglu backward, 4 bf16 + softmax partials, 5 bf16 scatter to peers
+  int epi;   // 0 bf16, 1 fp32 (beta), 2 swiglu, 3 swiglu backward, 4 bf16 + softmax partials, 5 bf16 scatter to peers,
+             // 6 fused QKV projection: raw bf16 output + per-head RMSNorm and RoPE of the q / k heads (pair-tile kernel)
   int bn;    // tile width: 256, 128 or 64
   int cta2;  // 1: pair-tile kernel (two CTAs per 256-row tile, TMA-store epilogue); bn 256 or 128
   int a_mn;  // A stored with the M index contiguous (rows = contraction index)
@@ -46,6 +47,15 @@ typedef struct B200GemmDesc {
   const int* row_slot;
   const float* row_w;
   float* row_dot;
+  // epi 6 (head_dim 128; C = raw projection [M, N], aux0 = same layout with q / k heads normalised and rotated, v
+  // heads copied): rope_cs [S, 64, 2] fp32 (cos, sin), rope_w / rope_kw [128] fp32 (q-norm / k-norm weight), rope_rstd
+  // [M, nh + nkv] fp32 receives the reciprocal RMS of every q / k head; the position of row r is r % rope_S
+  const float* rope_cs;
+  const float* rope_w;
+  const float* rope_kw;
+  float* rope_rstd;
+  int rope_S, rope_nh, rope_nkv;
+  float rope_eps;
   void* C;
   long long ldc, c_expert_stride;
   void* aux0;

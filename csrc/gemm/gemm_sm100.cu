@@ -41,6 +41,9 @@ struct MapKeyHash {
 };
 
 // bf16 tensor, up to 3 dims (inner first), 128B swizzle, zero fill out of bounds.
+static int g_last_encode_result = 0;
+int tma_last_encode_result() { return g_last_encode_result; }
+
 int make_map(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes,
                     uint64_t s2_bytes, uint32_t b0, uint32_t b1) {
   static std::mutex mu;
@@ -65,10 +68,22 @@ int make_map(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint6
   cuuint64_t strides[2] = {s1_bytes, s2_bytes};
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return -3;
+  auto encode = [&] {
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // The encoder is a driver call and wants a current context; a thread that has not made a runtime call yet (an
+    // autograd worker whose first node lands here) has none bound.  Any runtime call binds the primary context.
+    (void)cudaFree(nullptr);
+    r = encode();
+  }
+  if (r != CUDA_SUCCESS) {
+    g_last_encode_result = static_cast<int>(r);
+    return -3;
+  }
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);
@@ -101,10 +116,20 @@ int make_store_map(CUtensorMap* out, int elem_bytes, const void* base, uint64_t 
   cuuint64_t strides[2] = {s1_bytes, s2_bytes > 0 ? s2_bytes : s1_bytes * d1};
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
-                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return -3;
+  auto encode = [&] {
+    return fn(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {  // see make_map
+    (void)cudaFree(nullptr);
+    r = encode();
+  }
+  if (r != CUDA_SUCCESS) {
+    g_last_encode_result = static_cast<int>(r);
+    return -3;
+  }
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);
@@ -195,6 +220,19 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
   a.row_slot = d->row_slot;
   a.row_w = d->row_w;
   a.row_dot = d->row_dot;
+  a.rope_cs = d->rope_cs;
+  a.rope_w = d->rope_w;
+  a.rope_kw = d->rope_kw;
+  a.rope_rstd = d->rope_rstd;
+  a.rope_S = d->rope_S;
+  a.rope_nh = d->rope_nh;
+  a.rope_nkv = d->rope_nkv;
+  a.rope_eps = d->rope_eps;
+  if (d->epi == EPI_QKROPE) {
+    if (!d->cta2 || d->bn != 256 || d->a_mn || d->b_mn || d->mode != MODE_DENSE) return -24;
+    if (!d->rope_cs || !d->rope_w || !d->rope_kw || !d->rope_rstd || !d->aux0 || d->rope_S <= 0) return -24;
+    if (d->N != (d->rope_nh + 2 * d->rope_nkv) * 128) return -24;
+  }
   if ((a.a_gather || a.b_gather || a.row_w || a.row_dot) && !d->cta2) return -23;
   if ((a.row_w != nullptr) != (a.row_slot != nullptr)) return -23;
   a.C = d->C; a.ldc = d->ldc; a.c_expert_stride = d->c_expert_stride;
@@ -261,7 +299,11 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
                           static_cast<uint64_t>(d->c_expert_stride) * (f32 ? 4 : 2), f32 ? 32 : 64, 32);
       if (rc) return rc - 6;
     }
-    if (d->epi == EPI_SWIGLU || d->epi == EPI_SWIGLU_BWD) {
+    if (d->epi == EPI_QKROPE) {
+      rc = make_store_map(&mx, 2, d->aux0, static_cast<uint64_t>(d->N), static_cast<uint64_t>(d->M), 1,
+                          static_cast<uint64_t>(d->ld_aux0) * 2, static_cast<uint64_t>(d->ld_aux0) * 2 * d->M, 64, 32);
+      if (rc) return rc - 9;
+    } else if (d->epi == EPI_SWIGLU || d->epi == EPI_SWIGLU_BWD) {
       // [2][rows][I] view of the pre-activation tensor: plane 0 = gate columns, plane 1 = up columns
       void* xb = d->epi == EPI_SWIGLU ? d->aux0 : d->aux1;
       const long long ldx = d->epi == EPI_SWIGLU ? d->ld_aux0 : d->ld_aux1;
@@ -291,6 +333,7 @@ extern "C" int b200_gemm(const B200GemmDesc* d, cudaStream_t stream) {
     B200_CASE2(256, 0, 0, EPI_SWIGLU)
     B200_CASE2(256, 0, 1, EPI_SWIGLU_BWD)
     B200_CASE2(256, 0, 0, EPI_LSE)
+    B200_CASE2(256, 0, 0, EPI_QKROPE)
 #undef B200_CASE2
     return -21;
   }

@@ -25,6 +25,7 @@ enum GemmEpi : int {
   EPI_SWIGLU_BWD = 3,  // acc = d(act); aux0 = pre-activations; aux1 = d(pre-activations)
   EPI_LSE = 4,         // C bf16 = acc, aux0 = per (row, n-tile) (max, sum exp) partials
   EPI_BF16_SCATTER = 5,  // bf16 rows stored into peers' buffers: row r -> scatter_dst[src(r)] + slot(r) * ldc
+  EPI_QKROPE = 6,        // C bf16 = acc (raw QKV projection); aux0 = q / k heads RMS-normalised + rotated, v copied
 };
 
 // Expert-parallel hooks (all optional; null pointers switch them off).
@@ -68,6 +69,14 @@ struct GemmArgs {
   const int* row_slot;
   const float* row_w;
   float* row_dot;
+  // EPI_QKROPE (head_dim 128): cos/sin table [S, 64, 2], norm weights [128] of q and of k, reciprocal RMS out
+  // [M, nh + nkv]; row r sits at position r % rope_S
+  const float* rope_cs;
+  const float* rope_w;
+  const float* rope_kw;
+  float* rope_rstd;
+  int rope_S, rope_nh, rope_nkv;
+  float rope_eps;
   void* C;
   long long ldc;
   long long c_expert_stride;  // grouped_k: elements between experts in C

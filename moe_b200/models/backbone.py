@@ -78,9 +78,9 @@ class Attention(nn.Module):
 
     def forward(self, x):
         B, S, _ = x.shape
-        qkv = ops.linear(x, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, fused=self._fused_qkv)
-        q, k, v = ops.qk_norm_rope(qkv, self.q_norm.weight, self.k_norm.weight, B, S, self.num_heads,
-                                   self.num_kv_heads, self.head_dim, self.rope_theta, self.eps)
+        q, k, v = ops.qkv_proj_norm_rope(x, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self._fused_qkv,
+                                         self.q_norm.weight, self.k_norm.weight, B, S, self.num_heads,
+                                         self.num_kv_heads, self.head_dim, self.rope_theta, self.eps)
         o = ops.attention(q, k, v)
         return self.o_proj(o.reshape(B, S, self.num_heads * self.head_dim))
 

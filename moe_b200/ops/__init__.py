@@ -72,6 +72,14 @@ def qk_norm_rope(qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps):
     return q, k, v
 
 
+def qkv_proj_norm_rope(x, wq, wk, wv, fused, q_norm_w, k_norm_w, B, S, nh, nkv, hd, theta, eps):
+    """Hidden states -> (q, k, v) `[B,S,h,hd]`: QKV projection, per-head RMSNorm of q and k, RoPE."""
+    if _k(x):
+        return _f().qkv_proj_norm_rope(x, wq, wk, wv, fused, q_norm_w, k_norm_w, B, S, nh, nkv, hd, theta, eps)
+    qkv = linear(x, wq, wk, wv, fused=fused)
+    return qk_norm_rope(qkv, q_norm_w, k_norm_w, B, S, nh, nkv, hd, theta, eps)
+
+
 def attention(q, k, v):
     if _k(q):
         return _f().attention(q, k, v)

@@ -181,7 +181,7 @@ class LinearFn(torch.autograd.Function):
     """y = x @ W^T with W given as one or several row-adjacent parameters (e.g. q, k, v projections)."""
 
     @staticmethod
-    def forward(ctx, x, fused, *weights):
+    def forward(ctx, x, fused, rope, *weights):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         if x2.dtype != BF16:
@@ -193,7 +193,15 @@ class LinearFn(torch.autograd.Function):
             wmat = w16(weights[0])
         else:
             wmat = torch.cat([w16(w) for w in weights], dim=0)
-        y = G.gemm_nt(x2, wmat)
+        if rope is not None and rope.usable(x2.shape[0], wmat.shape[0], K):
+            # QKV projection: the per-head RMSNorm + RoPE of q and k runs in the GEMM's epilogue; the raw projection
+            # (this function's output, what the norm's backward needs) is written beside the rotated one
+            cs = rope_table(rope.S, rope.hd, rope.theta, x2.device)
+            y, rope.rot, rope.rstd = G.gemm_nt_qkrope(x2, wmat, cs, w32(rope.q_w), w32(rope.k_w), rope.S, rope.nh,
+                                                      rope.nkv, rope.eps)
+            rope.cs = cs
+        else:
+            y = G.gemm_nt(x2, wmat)
         ctx.save_for_backward(x2)
         ctx.wmat = wmat
         ctx.fused = fused
@@ -220,12 +228,12 @@ class LinearFn(torch.autograd.Function):
             G.gemm_tn(dy2, x2, grad_view, beta=beta)
             for w in weights:
                 w._grad_live = True
-            return (dx, None) + (None,) * len(weights)
+            return (dx, None, None) + (None,) * len(weights)
         if len(weights) == 1:
             sink = GradSink(weights[0])
             tgt, beta = sink.target()
             G.gemm_tn(dy2, x2, tgt, beta=beta)
-            return dx, None, sink.done(tgt)
+            return dx, None, None, sink.done(tgt)
         full = torch.empty(N, K, dtype=torch.float32, device=dy2.device)
         G.gemm_tn(dy2, x2, full)
         outs, r = [], 0
@@ -243,11 +251,33 @@ class LinearFn(torch.autograd.Function):
                 outs.append(None)
             else:
                 outs.append(piece.to(w.dtype))
-        return (dx, None, *outs)
+        return (dx, None, None, *outs)
 
 
 def linear(x, *weights, fused=None):
-    return LinearFn.apply(x, fused, *weights)
+    return LinearFn.apply(x, fused, None, *weights)
+
+
+class RopeSpec:
+    """What the QKV projection needs to apply QK-norm + RoPE in its epilogue, and where it leaves the results."""
+
+    def __init__(self, q_w, k_w, B, S, nh, nkv, hd, theta, eps):
+        self.q_w, self.k_w = q_w, k_w
+        self.B, self.S, self.nh, self.nkv, self.hd, self.theta, self.eps = B, S, nh, nkv, hd, theta, eps
+        self.rot = self.rstd = self.cs = None
+
+    def usable(self, M: int, N: int, K: int) -> bool:
+        return (M == self.B * self.S and N == (self.nh + 2 * self.nkv) * self.hd
+                and G.qkv_rope_supported(M, N, K, self.hd))
+
+
+def qkv_proj_norm_rope(x, wq, wk, wv, fused, q_norm_w, k_norm_w, B, S, nh, nkv, hd, theta, eps):
+    """(q, k, v) `[B,S,h,hd]` from the hidden states: fused QKV projection, per-head RMSNorm of q and k, RoPE.
+    Where the pair-tile GEMM applies (head_dim 128) norm and rotation run in the projection's epilogue and q, k, v
+    are slices of one `[B*S, (nh + 2 nkv) * hd]` buffer; otherwise a separate kernel follows the GEMM."""
+    spec = RopeSpec(q_norm_w, k_norm_w, B, S, nh, nkv, hd, theta, eps)
+    qkv = LinearFn.apply(x, fused, spec, wq, wk, wv)
+    return QKNormRopeFn.apply(qkv, q_norm_w, k_norm_w, B, S, nh, nkv, hd, theta, eps, spec if spec.rot is not None else None)
 
 
 # ------------------------------------------------------------ dense SwiGLU MLP
@@ -339,16 +369,20 @@ class QKNormRopeFn(torch.autograd.Function):
     """Fused QKV projection output -> (q, k, v) in `[B, S, heads, hd]`, with per-head RMSNorm and RoPE on q, k."""
 
     @staticmethod
-    def forward(ctx, qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps):
+    def forward(ctx, qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps, pre=None):
         qkv2 = qkv.reshape(B * S, (nh + 2 * nkv) * hd).contiguous()
         T = B * S
         dev = qkv2.device
-        cs = rope_table(S, hd, theta, dev)
-        q = torch.empty(B, S, nh, hd, dtype=BF16, device=dev)
-        k = torch.empty(B, S, nkv, hd, dtype=BF16, device=dev)
-        v = torch.empty(B, S, nkv, hd, dtype=BF16, device=dev)
-        rstd = torch.empty(T * (nh + nkv), dtype=torch.float32, device=dev)
-        ext().qknorm_rope_fwd(qkv2, w32(q_w), w32(k_w), cs, q, k, v, rstd, S, nh, nkv, hd, eps)
+        if pre is not None:  # already computed by the projection's epilogue (`RopeSpec`): hand out the slices
+            cs, rstd = pre.cs, pre.rstd.view(-1)
+            q, k, v = pre.rot.view(B, S, nh + 2 * nkv, hd).split([nh, nkv, nkv], dim=2)
+        else:
+            cs = rope_table(S, hd, theta, dev)
+            q = torch.empty(B, S, nh, hd, dtype=BF16, device=dev)
+            k = torch.empty(B, S, nkv, hd, dtype=BF16, device=dev)
+            v = torch.empty(B, S, nkv, hd, dtype=BF16, device=dev)
+            rstd = torch.empty(T * (nh + nkv), dtype=torch.float32, device=dev)
+            ext().qknorm_rope_fwd(qkv2, w32(q_w), w32(k_w), cs, q, k, v, rstd, S, nh, nkv, hd, eps)
         ctx.save_for_backward(qkv2, rstd, cs)
         ctx.q_w, ctx.k_w = q_w, k_w
         ctx.dims = (B, S, nh, nkv, hd)
@@ -378,11 +412,11 @@ class QKNormRopeFn(torch.autograd.Function):
         dqkv = torch.empty_like(qkv2)
         e.qknorm_rope_bwd(dq.contiguous(), dk.contiguous(), dv.contiguous(), qkv2, rstd, w32(ctx.q_w), w32(ctx.k_w), cs,
                           dqkv, part, tq, tk, bool(bq), S, nh, nkv, hd)
-        return dqkv.view(ctx.qkv_shape), sq.done(tq), sk.done(tk), None, None, None, None, None, None, None
+        return dqkv.view(ctx.qkv_shape), sq.done(tq), sk.done(tk), None, None, None, None, None, None, None, None
 
 
 def qk_norm_rope(qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps):
-    return QKNormRopeFn.apply(qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps)
+    return QKNormRopeFn.apply(qkv, q_w, k_w, B, S, nh, nkv, hd, theta, eps, None)
 
 
 # ------------------------------------------------------------------- attention
@@ -404,6 +438,15 @@ def flash_supported(q, k) -> bool:
 _ATTN_STATE = {"library_backward_ok": None, "dummy": {}}
 
 
+def _rows4(t: torch.Tensor) -> torch.Tensor:
+    """`[B,S,h,hd]` as the attention kernels take it: heads contiguous per token, tokens evenly spaced (a slice of
+    the fused QKV activation qualifies as it is); anything else is made contiguous."""
+    B, S, h, hd = t.shape
+    ok = (t.stride(3) == 1 and t.stride(2) == hd and t.stride(1) % 8 == 0 and t.stride(1) >= h * hd
+          and (B == 1 or t.stride(0) == S * t.stride(1)) and t.data_ptr() % 16 == 0)
+    return t if ok else t.contiguous()
+
+
 class FlashAttnFn(torch.autograd.Function):
     """Causal GQA attention.  Forward: `csrc/attn/flash_fwd.cu` (returns the base-2 log-sum-exp per row).
     Backward: `csrc/attn/flash_bwd.cu` (delta, dQ and dK/dV kernels).  MOE_B200_ATTN_BWD=library switches
@@ -415,8 +458,8 @@ class FlashAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v):
         B, S, nh, hd = q.shape
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o = torch.empty_like(q)
+        q, k, v = _rows4(q), _rows4(k), _rows4(v)
+        o = torch.empty(B, S, nh, hd, dtype=q.dtype, device=q.device)
         lse2 = torch.empty(B, nh, S, dtype=torch.float32, device=q.device)
         scale = 1.0 / math.sqrt(hd)
         ext().flash_fwd(q, k, v, o, lse2, scale, G.status_word(q.device))
@@ -430,7 +473,7 @@ class FlashAttnFn(torch.autograd.Function):
         B, S, nh, hd = q.shape
         do = do.contiguous()
         if os.environ.get("MOE_B200_ATTN_BWD", "own") != "library":
-            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (q, k, v))
             delta = torch.empty_like(lse2)
             ext().flash_bwd(q, k, v, o, do, lse2, delta, dq, dk, dv, ctx.scale, G.status_word(q.device))
             return dq, dk, dv

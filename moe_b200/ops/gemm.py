@@ -14,7 +14,7 @@ import torch
 from . import _ext
 
 MODE_DENSE, MODE_GROUPED_M, MODE_GROUPED_K = 0, 1, 2
-EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD, EPI_LSE, EPI_BF16_SCATTER = 0, 1, 2, 3, 4, 5
+EPI_BF16, EPI_F32, EPI_SWIGLU, EPI_SWIGLU_BWD, EPI_LSE, EPI_BF16_SCATTER, EPI_QKROPE = 0, 1, 2, 3, 4, 5, 6
 
 _status_words: dict[int, torch.Tensor] = {}
 
@@ -66,12 +66,14 @@ def _pick_bn(n: int) -> int:
 def _launch(*, mode, epi, bn, a_mn, b_mn, M, N, K, A, lda, a_inner, a_rows, B, ldb, b_expert_stride, b_inner,
             b_rows, b_experts, C, ldc, num_experts=1, m_fast=1, beta=0, n_half=0, tile_expert=None,
             num_m_tiles=None, seg_off=None, c_expert_stride=0, aux0=None, ld_aux0=0, aux1=None, ld_aux1=0, ep=None,
-            cta2=0, pair_tiles=None, a_gather=None, b_gather=None, row_slot=None, row_w=None, row_dot=None):
+            cta2=0, pair_tiles=None, a_gather=None, b_gather=None, row_slot=None, row_w=None, row_dot=None,
+            rope=None):
     ext = _ext.load()
     ext.gemm(mode, epi, bn, a_mn, b_mn, M, N, K, num_experts, m_fast, beta, n_half, A, lda, a_inner, a_rows, B, ldb,
              b_expert_stride, b_inner, b_rows, b_experts, tile_expert, num_m_tiles, seg_off, C, ldc,
              c_expert_stride, aux0, ld_aux0, aux1, ld_aux1, status_word(A.device), cta2=cta2, pair_tiles=pair_tiles,
-             a_gather=a_gather, b_gather=b_gather, row_slot=row_slot, row_w=row_w, row_dot=row_dot, **(ep or {}))
+             a_gather=a_gather, b_gather=b_gather, row_slot=row_slot, row_w=row_w, row_dot=row_dot, **(rope or {}),
+             **(ep or {}))
 
 
 def _check2d(t: torch.Tensor, name: str) -> None:
@@ -97,6 +99,32 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *
             M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K, a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0,
             b_inner=K, b_rows=N, b_experts=1, C=out, ldc=out.stride(0), beta=beta, m_fast=m_fast, cta2=int(pair))
     return out
+
+
+def qkv_rope_supported(M: int, N: int, K: int, hd: int) -> bool:
+    """Whether the QKV projection can apply the per-head RMSNorm and RoPE in its epilogue (pair-tile kernel,
+    head_dim 128: a 256-column tile is two heads).  MOE_B200_QKV_FUSED=0 keeps the separate kernel."""
+    return (pair_tiles_enabled() and hd == 128 and M >= 256 and N % 128 == 0 and K % 8 == 0
+            and os.environ.get("MOE_B200_QKV_FUSED", "1") != "0")
+
+
+def gemm_nt_qkrope(a: torch.Tensor, b: torch.Tensor, cs: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor, S: int,
+                   nh: int, nkv: int, eps: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Fused QKV projection `a[M,K] @ b[N,K]^T` with N = (nh + 2 nkv) * 128.  Returns the raw projection `[M,N]`
+    (what backward needs), the same layout with the q / k heads RMS-normalised (fp32 weights `qw`, `kw` `[128]`),
+    rotated by the table `cs [S,64,2]` (row r at position r % S) and the v heads copied, and the reciprocal RMS
+    `[M, nh + nkv]` of every q / k head."""
+    _check2d(a, "a"); _check2d(b, "b")
+    M, K = a.shape
+    N = b.shape[0]
+    raw = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    rot = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    rstd = torch.empty(M, nh + nkv, dtype=torch.float32, device=a.device)
+    _launch(mode=MODE_DENSE, epi=EPI_QKROPE, bn=256, a_mn=0, b_mn=0, M=M, N=N, K=K, A=a, lda=a.stride(0), a_inner=K,
+            a_rows=M, B=b, ldb=b.stride(0), b_expert_stride=0, b_inner=K, b_rows=N, b_experts=1, C=raw, ldc=N,
+            aux0=rot, ld_aux0=N, cta2=1,
+            rope=dict(rope_cs=cs, rope_w=qw, rope_kw=kw, rope_rstd=rstd, rope_S=S, rope_nh=nh, rope_nkv=nkv, rope_eps=eps))
+    return raw, rot, rstd
 
 
 def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, *, bn: int | None = None,

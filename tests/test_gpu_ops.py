@@ -88,6 +88,54 @@ def test_gemm_tn_short_wide_output_is_split_along_the_contraction(dev, Kc, M, N)
     assert relerr(out, at.float().T @ bt.float()) < 1e-5 and torch.equal(out, again)
 
 
+@pytest.mark.parametrize("B,S,nh,nkv,H", [(2, 128, 4, 2, 256), (1, 384, 16, 8, 1024), (3, 256, 3, 1, 512)])
+def test_qkv_projection_with_norm_and_rope_in_the_epilogue(dev, B, S, nh, nkv, H):
+    """The fused QKV epilogue against the GEMM followed by the stand-alone QK-norm + RoPE kernel (same arithmetic),
+    then through autograd against the fp32 statement, with attention reading the slices in place."""
+    from moe_b200 import ops
+    from moe_b200.ops import functional as F
+    from moe_b200.ops import gemm as G
+
+    torch.manual_seed(7)
+    hd, T, N = 128, B * S, (nh + 2 * nkv) * 128
+    assert G.qkv_rope_supported(T, N, H, hd)
+    x, w = _bf(T, H), _bf(N, H, scale=0.05)
+    qw, kw = 1 + 0.1 * torch.randn(hd, device=dev), 1 + 0.1 * torch.randn(hd, device=dev)
+    cs = F.rope_table(S, hd, 1e6, x.device)
+    raw, rot, rstd = G.gemm_nt_qkrope(x, w, cs, qw, kw, S, nh, nkv, 1e-6)
+    ref_raw = G.gemm_nt(x, w)
+    q, k, v = F.qk_norm_rope(ref_raw.view(B, S, N), qw, kw, B, S, nh, nkv, hd, 1e6, 1e-6)
+    _sync_status()
+    assert torch.equal(raw, ref_raw)
+    got = rot.view(B, S, nh + 2 * nkv, hd)
+    assert torch.equal(got[:, :, nh + nkv:], v)
+    assert relerr(got[:, :, :nh], q) < 4e-3 and relerr(got[:, :, nh:nh + nkv], k) < 4e-3
+    # module-level: projection + norm + rope + attention, kernels against the oracle
+    xs = _bf(B, S, H).requires_grad_()
+    ws = [(_bf(n, H, scale=0.05)).float().requires_grad_() for n in (nh * hd, nkv * hd, nkv * hd)]
+    nq, nk = qw.clone().requires_grad_(), kw.clone().requires_grad_()
+
+    def run(xi, wi, a, b):
+        qq, kk, vv = ops.qkv_proj_norm_rope(xi, *wi, None, a, b, B, S, nh, nkv, hd, 1e6, 1e-6)
+        return ops.attention(qq, kk, vv) if (nh // nkv) % 2 == 0 else torch.cat(
+            [qq.reshape(B, S, -1), kk.reshape(B, S, -1), vv.reshape(B, S, -1)], -1)
+
+    out = run(xs, ws, nq, nk)
+    g = torch.randn_like(out.float()).to(out.dtype)
+    out.backward(g)
+    xo = xs.detach().float().requires_grad_()
+    wo = [t.detach().bfloat16().float().requires_grad_() for t in ws]
+    ao, bo = nq.detach().clone().requires_grad_(), nk.detach().clone().requires_grad_()
+    with ops.force_oracle():
+        out2 = run(xo, wo, ao, bo)
+    out2.backward(g.float())
+    _sync_status()
+    assert relerr(out, out2) < 2e-2
+    assert relerr(xs.grad, xo.grad) < 4e-2
+    for a_, b_ in zip(ws + [nq, nk], wo + [ao, bo]):
+        assert relerr(a_.grad, b_.grad) < 4e-2
+
+
 def test_rmsnorm_fwd_bwd(dev):
     from moe_b200.ops import functional as F, oracle
 
