@@ -137,6 +137,26 @@ def case_qknorm_rope(small):
     return dict(shape=[B, S, nh, nkv, hd], ms=ms, bytes=2.0 * qkv.numel() * 2)
 
 
+def case_gemm_qkv_rope(small):
+    """QKV projection with QK-norm + RoPE in the epilogue, against the plain GEMM followed by the stand-alone kernel."""
+    from moe_b200.ops import functional as F
+    from moe_b200.ops import gemm as G
+
+    B, S, nh, nkv, hd, H = (2, 2048, 16, 8, 128, 1024) if small else (8, 2048, 16, 8, 128, 1024)
+    T, N = B * S, (nh + 2 * nkv) * hd
+    x, w = bf(T, H), bf(N, H, scale=0.05)
+    qw, kw = torch.ones(hd, device="cuda"), torch.ones(hd, device="cuda")
+    cs = F.rope_table(S, hd, 1e6, x.device)
+    ms = timeit(lambda: G.gemm_nt_qkrope(x, w, cs, qw, kw, S, nh, nkv, 1e-6))
+
+    def separate():
+        qkv = G.gemm_nt(x, w)
+        F.qk_norm_rope(qkv.view(B, S, N), qw, kw, B, S, nh, nkv, hd, 1e6, 1e-6)
+
+    ref = timeit(separate)
+    return dict(shape=[T, N, H], ms=ms, flops=2.0 * T * N * H, separate_ms=ref)
+
+
 def case_qknorm_rope_fwd_bwd(small):
     from moe_b200.ops import functional as F
 
