@@ -76,3 +76,25 @@ def test_modal_app_matches_the_cluster_spec(monkeypatch):
     assert ("secret", "huggingface-secret") in appkw["secrets"]
     assert any(e[0] == "image.apt_install" and "libibverbs1" in e[1] for e in log)
     assert callable(train) and callable(download)
+
+
+def test_torchrun_options_model_validates_and_round_trips():
+    """The typed model of torchrun's options (built from torchrun's own parser): unknown and mistyped options
+    are rejected before anything starts, and the generated command line parses back to the same values."""
+    import pytest
+    from torch.distributed.run import get_args_parser
+
+    from moe_b200 import launch
+
+    model = launch.options_model()
+    opts = model(nproc_per_node="8", nnodes=2, node_rank=1, master_addr="10.0.0.1", master_port=1234)
+    argv = opts.to_argv("train.py", ["--config", "x.yaml", "--auto_resume"])
+    assert argv[-4:] == ["train.py", "--config", "x.yaml", "--auto_resume"] and "--nproc-per-node=8" in argv
+    args = get_args_parser().parse_args(argv)
+    assert (args.nnodes, args.node_rank, args.master_addr, args.master_port) == ("2", 1, "10.0.0.1", 1234)
+    assert args.training_script == "train.py" and args.training_script_args == ["--config", "x.yaml", "--auto_resume"]
+    assert "--standalone" in model(standalone=True).to_argv("t.py") and model().to_argv("t.py") == ["t.py"]
+    with pytest.raises(Exception):
+        model(nproc_pernode=8)  # misspelt option
+    with pytest.raises(Exception):
+        model(master_port="not-a-port")
