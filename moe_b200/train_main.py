@@ -47,6 +47,8 @@ def parse_args(argv=None):
     p.add_argument("--max_checkpoints", type=int, default=0, help="Checkpoints to keep (0 = all)")
     p.add_argument("--device", default=None, choices=["cpu", "cuda"], help="default: cuda when available")
     p.add_argument("--max_steps", type=int, default=None, help="Override training.max_steps")
+    p.add_argument("--parallel_mode", default=None, choices=["ddp", "zero", "fsdp"],
+                   help="Override parallel.mode (the reference picks between its DDP and FSDP launcher files)")
     p.add_argument("--profile", action="store_true",
                    help="NVTX ranges per step and per phase (attn, moe, lce, comm); runs eagerly, without the CUDA graph")
     return p.parse_args(argv)
@@ -138,6 +140,8 @@ def main(argv=None) -> None:
     if args.max_steps is not None:
         tdict["max_steps"] = args.max_steps
     tcfg = TrainingConfig.from_dict(tdict)
+    if args.parallel_mode:
+        cfg.setdefault("parallel", {})["mode"] = args.parallel_mode
     resume_from = args.resume or cfg.get("checkpoint", {}).get("resume_from")
     if args.auto_resume and not resume_from:
         resume_from = find_latest_checkpoint(tcfg.output_dir)

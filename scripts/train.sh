@@ -4,6 +4,7 @@
 #   ./scripts/train.sh <config.yaml> [--resume DIR] [--auto_resume] [--max_checkpoints N] ...
 #   NPROC=2 ./scripts/train.sh configs/bench/xs_standard.yaml --max_steps 20
 #   DEVICE=cpu NPROC=2 ./scripts/train.sh configs/bench/tiny_cpu.yaml      # gloo, no GPU needed
+#   ./scripts/train.sh configs/scaling/l_standard.yaml --parallel_mode fsdp  # ddp | zero | fsdp (default: config / zero)
 #
 # Everything after the config path is passed to train.py unchanged.
 set -euo pipefail
